@@ -1,0 +1,454 @@
+"""Benchmark of the HSA forward (and HKV retrieval) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5]
+
+Workload "c2" (default): one HSA layer forward, bf16, B=1, 12 heads x 128, a 4680-token query chunk
+over a 32760-token KV cache, 128x128 blocks, per-head top-k drawn from {4, 8, 16, 32} (seed 1),
+q/k/v ~ N(0,1)/sqrt(128) (seed 1).  One "step" is one chunk through `HSAAttention.forward` with
+the compressed cache supplied, as the causal pipeline calls it.  Metric: chunks per second
+(`ms_per_step` is the ms/chunk figure).  Prints one JSON line on rank 0.
+
+N > 1 shards the same chunk (strong scaling): heads are split over 2 / 4 GPUs, the KV range is
+sharded over 8 (or any N that does not divide the heads) with a log-sum-exp merge over NCCL.
+`--impl reference` times the CPU restatement of the reference algorithm on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+HEADS, HEAD_DIM = 12, 128
+FRAME_TOKENS = 1560
+WORKLOADS = {
+    # name: (q frames, kv frames, block, top-k policy)
+    "c2": dict(q_frames=3, kv_frames=21, block=128, topk="adaptive", seed=1, scale=1.0 / math.sqrt(HEAD_DIM)),
+    "c5": dict(q_frames=3, kv_frames=480, block=64, topk=32, seed=4, scale=1.0),
+}
+L2_FLUSH_BYTES = 256 << 20
+
+
+# ------------------------------------------------------------------------------------------------
+# workload construction (host side, seeded)
+# ------------------------------------------------------------------------------------------------
+def draw_topk(spec, heads=HEADS):
+    if spec["topk"] == "adaptive":
+        g = torch.Generator().manual_seed(spec["seed"])
+        return torch.tensor([4, 8, 16, 32])[torch.randint(0, 4, (heads,), generator=g)].to(torch.int32)
+    return torch.full((heads,), int(spec["topk"]), dtype=torch.int32)
+
+
+def host_inputs(spec, pin: bool):
+    """q, k, v as bf16 host tensors `[1, L, H, D]` from the workload's seed."""
+    g = torch.Generator().manual_seed(spec["seed"])
+    q_len, kv_len = spec["q_frames"] * FRAME_TOKENS, spec["kv_frames"] * FRAME_TOKENS
+
+    def draw(n):
+        out = torch.empty((1, n, HEADS, HEAD_DIM), dtype=torch.bfloat16, pin_memory=pin)
+        step = 65536
+        for s in range(0, n, step):
+            e = min(n, s + step)
+            out[:, s:e] = (torch.randn((1, e - s, HEADS, HEAD_DIM), generator=g) * spec["scale"]).to(torch.bfloat16)
+        return out
+    return draw(q_len), draw(kv_len), draw(kv_len)
+
+
+def gate_params(seed=7):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn((HEAD_DIM, HEAD_DIM), generator=g) * 0.02, torch.zeros(HEAD_DIM)
+
+
+def block_average_projection(block):
+    rank = math.ceil(FRAME_TOKENS / block)
+    e = torch.zeros((rank, FRAME_TOKENS))
+    for r in range(rank):
+        lo, hi = r * block, min((r + 1) * block, FRAME_TOKENS)
+        e[r, lo:hi] = 1.0 / (hi - lo)
+    return e.to(torch.bfloat16)
+
+
+def algorithmic_flops(num: np.ndarray, index: np.ndarray, q_len, kv_len, block, lc, head_dim=HEAD_DIM):
+    """Sparse 4*D*sum(rows_i * selected tokens), linear 4*D*H*Lq*Lc, gate 2*Lq*H*D^2."""
+    nq, nkv = math.ceil(q_len / block), math.ceil(kv_len / block)
+    rows = np.full((nq,), block, np.int64)
+    rows[-1] = q_len - (nq - 1) * block
+    sizes = np.full((nkv,), block, np.int64)
+    sizes[-1] = kv_len - (nkv - 1) * block
+    slots = np.arange(index.shape[-1])[None, None, None, :] < num[..., None]
+    tokens = (sizes[np.clip(index, 0, nkv - 1)] * slots).sum(-1)           # [B, H, Nq]
+    sparse = 4.0 * head_dim * float((tokens * rows[None, None, :]).sum())
+    heads = num.shape[1]
+    linear = 4.0 * head_dim * heads * q_len * lc
+    gate = 2.0 * q_len * heads * head_dim * head_dim
+    return sparse, linear, gate
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks sampler
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.samples, self.proc, self.thread = [], None, None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the numpy restatement of the reference algorithm, on a bounded sample of the workload
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_setup(spec, n_heads_sample):
+    from oracle import hsa_oracle as O
+    q, k, v = host_inputs(spec, pin=False)
+    block = spec["block"]
+    topk = draw_topk(spec).numpy()
+    heads = list(range(n_heads_sample))
+    qs, ks, vs = (x[:, :, heads].float().numpy() for x in (q, k, v))
+    ek = block_average_projection(block).float().numpy()
+    gw, gb = gate_params()
+    kc, vc = O.compress_kv(np.ascontiguousarray(ks.transpose(0, 2, 1, 3)), np.ascontiguousarray(vs.transpose(0, 2, 1, 3)),
+                           segment_len=FRAME_TOKENS, k_proj_mat=ek, v_proj_mat=ek, block_size=block, dtype="bf16")
+    kc, vc = kc.transpose(0, 2, 1, 3), vc.transpose(0, 2, 1, 3)
+    # fraction of the whole chunk's algorithmic work that the sample covers (sparse term scales with k_h)
+    q_len, kv_len = q.shape[1], k.shape[1]
+    per_head = 4.0 * HEAD_DIM * q_len * (np.minimum(topk, math.ceil(kv_len / block)) * block) \
+        + 4.0 * HEAD_DIM * q_len * kc.shape[1] + 2.0 * q_len * HEAD_DIM * HEAD_DIM
+    frac = float(per_head[heads].sum() / per_head.sum())
+
+    def step():
+        return O.hsa_attention(qs, ks, vs, k_coarse=kc, v_coarse=vc, k_proj_mat=ek, v_proj_mat=ek,
+                               gate_weight=gw.numpy(), gate_bias=gb.numpy(), block_size=block,
+                               proj_segment_len=FRAME_TOKENS, dtype="bf16", topk_per_head=topk[heads])
+    return step, frac, f"heads 0..{n_heads_sample - 1} of {HEADS}, whole chunk ({q_len} q x {kv_len} kv tokens); " \
+                       f"value scaled by the sample's share of algorithmic FLOPs ({frac:.3f})"
+
+
+def run_cpu(spec, steps, warmup, n_heads_sample):
+    step, frac, what = cpu_sample_setup(spec, n_heads_sample)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    chunk_s = dt / frac
+    return 1.0 / chunk_s, chunk_s * 1e3, what
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    spec = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    steps, warmup = max(1, min(args.steps, 6)), max(1, min(args.warmup, 1))
+    value, ms, what = run_cpu(spec, steps, warmup, n_heads_sample=2 if args.workload == "c2" else 1)
+    line = {
+        "impl": "reference", "metric": "hsa_fwd_chunks_per_s", "value": value, "unit": "chunks/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.workload, 1),
+        "cpu_baseline": {"value": value, "unit": "chunks/s", "cores": cores, "kind": "port", "sample": what},
+        "e2e": {"value": value, "unit": "chunks/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "reference's own implementation is Python/PyTorch and does not travel to the GPU box; this arm times "
+                "the numpy restatement of the same algorithm (oracle/) on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, n_gpus):
+    spec = WORKLOADS[name]
+    sharding = "none" if n_gpus == 1 else ("head-split" if HEADS % n_gpus == 0 and n_gpus <= 4 else "kv-shard+lse-merge")
+    return {
+        "workload": f"{name}: HSA layer forward, B=1 H={HEADS} D={HEAD_DIM}, q={spec['q_frames'] * FRAME_TOKENS} "
+                    f"kv={spec['kv_frames'] * FRAME_TOKENS} tokens, block {spec['block']}, top-k {spec['topk']}, seed {spec['seed']}",
+        "compressed_cache": "precomputed (maintained incrementally, as the causal pipeline does)",
+        "sharding": sharding,
+        "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between timed steps",
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--force-generic", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+
+    import worldattention_b200 as wa
+    from worldattention_b200 import sharded
+    from worldattention_b200.hsa.attention import _compress_blhd
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = wa._lib.lib()
+    spec = WORKLOADS[args.workload]
+    block = spec["block"]
+    topk_all = draw_topk(spec)
+
+    # ---- inputs: seeded on the host, page-locked, copied once into HBM -------------------------
+    q_h, k_h, v_h = host_inputs(spec, pin=True)
+    q_len, kv_len = q_h.shape[1], k_h.shape[1]
+    hsa = wa.hsa.HSAAttention(HEADS, HEAD_DIM, block_size=block, proj_segment_len=FRAME_TOKENS).to(dev)
+    gw, gb = gate_params()
+    with torch.no_grad():
+        proj = block_average_projection(block)
+        hsa.k_proj_mat.copy_(proj); hsa.v_proj_mat.copy_(proj)
+        hsa.gate_lin.weight.copy_(gw); hsa.gate_lin.bias.copy_(gb)
+
+    mode = "single"
+    if world > 1:
+        mode = "heads" if (HEADS % world == 0 and world <= 4) else "kv"
+    if mode == "heads":
+        plan = sharded.plan_head_split(HEADS, world, topk_all.tolist())
+        mine = plan[rank]
+        q_h, k_h, v_h = (x[:, :, mine].contiguous().pin_memory() for x in (q_h, k_h, v_h))
+        topk = topk_all[mine].contiguous()
+    else:
+        topk = topk_all
+    q, k, v = (x.to(dev, non_blocking=True) for x in (q_h, k_h, v_h))
+    torch.cuda.synchronize()
+
+    if mode == "kv":
+        shards = sharded.plan_kv_shards(kv_len, block, world, FRAME_TOKENS)
+        lo, hi = shards[rank]
+        k_loc, v_loc = k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous()
+        seg_lo, seg_hi = math.ceil(lo / FRAME_TOKENS), math.ceil(hi / FRAME_TOKENS) if rank < world - 1 else spec["kv_frames"]
+        kc_all, vc_all = _compress_blhd(k, v, segment_len=FRAME_TOKENS, k_proj_mat=hsa.k_proj_mat,
+                                        v_proj_mat=hsa.v_proj_mat, block_size=block)
+        r = hsa.proj_rank
+        kc, vc = kc_all[:, seg_lo * r: seg_hi * r].contiguous(), vc_all[:, seg_lo * r: seg_hi * r].contiguous()
+        del kc_all, vc_all
+    else:
+        kc, vc = hsa.compress_kv_cache(k, v)
+    hsa.topk_per_head = topk.to(dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    def forward():
+        with torch.no_grad():
+            if mode == "single":
+                return wa.hsa.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat,
+                                            v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=block,
+                                            proj_segment_len=FRAME_TOKENS, topk_per_head=hsa.topk_per_head,
+                                            force_generic=args.force_generic)
+            if mode == "heads":
+                return sharded.hsa_attention_head_split(hsa, q, k, v, k_coarse=kc, v_coarse=vc,
+                                                        topk_local=hsa.topk_per_head, head_plan=plan)
+            return sharded.hsa_attention_kv_sharded(hsa, q, k_loc, v_loc, kc, vc, kv_len=kv_len, shards=shards,
+                                                    topk_per_head=hsa.topk_per_head)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- routing statistics for the FLOP count (untimed) ---------------------------------------
+    used_tuned = False
+    if mode in ("single", "heads"):
+        with torch.no_grad():
+            _, (index, num, _, used_tuned) = wa.hsa.hsa_attention(
+                q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat,
+                gate_lin=hsa.gate_lin, block_size=block, proj_segment_len=FRAME_TOKENS,
+                topk_per_head=hsa.topk_per_head, return_routing=True, force_generic=args.force_generic)
+        sparse_f, linear_f, gate_f = algorithmic_flops(num.cpu().numpy(), index.cpu().numpy(), q_len, kv_len, block,
+                                                       kc.shape[1])
+    else:
+        nkv = math.ceil(kv_len / block)
+        sparse_f = 4.0 * HEAD_DIM * q_len * block * float(torch.clamp(topk_all, max=nkv).sum()) / world
+        linear_f, gate_f = 4.0 * HEAD_DIM * HEADS * q_len * kc.shape[1], 0.0
+
+    # ---- device-resident timing ------------------------------------------------------------------
+    for _ in range(args.warmup):
+        forward()
+    barrier()
+    lib.wa_profile_enable(1)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.wa_launch_count()
+    step_ms, kern_ms = [], []
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    wall0 = time.perf_counter()
+    import ctypes
+    for _ in range(args.steps):
+        flush.zero_()
+        if world > 1:
+            dist.barrier()
+        ev0.record()
+        forward()
+        ev1.record()
+        ev1.synchronize()
+        step_ms.append(ev0.elapsed_time(ev1))
+        ms = ctypes.c_float(0.0)
+        if lib.wa_profile_attention_ms(ctypes.byref(ms)) == 0:
+            kern_ms.append(ms.value)
+    barrier()
+    wall = time.perf_counter() - wall0
+    launches = lib.wa_launch_count() - launches0
+    lib.wa_profile_enable(0)
+    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    ms_per_step = total_ms / args.steps
+
+    # ---- end to end through the public API with host buffers ------------------------------------
+    # Per step: the chunk's q and its new K/V rows arrive from page-locked host memory, the rows
+    # are written at the tail of the resident cache and compressed into the tail of the compressed
+    # cache, the layer runs, and the output returns to page-locked host memory.
+    new = q_len
+    out_h = torch.empty(tuple(forward().shape), dtype=torch.bfloat16, pin_memory=True)
+    q_new_h, k_new_h, v_new_h = q_h, k_h[:, kv_len - new:].contiguous().pin_memory(), v_h[:, kv_len - new:].contiguous().pin_memory()
+    h2d = (q_new_h.numel() + (k_new_h.numel() + v_new_h.numel() if mode != "kv" else 0)) * 2
+    d2h = out_h.numel() * 2
+    rank_r = hsa.proj_rank
+
+    def e2e_step():
+        q.copy_(q_new_h, non_blocking=True)
+        if mode != "kv":
+            k[:, kv_len - new:].copy_(k_new_h, non_blocking=True)
+            v[:, kv_len - new:].copy_(v_new_h, non_blocking=True)
+            with torch.no_grad():
+                kn, vn = _compress_blhd(k[:, kv_len - new:], v[:, kv_len - new:], segment_len=FRAME_TOKENS,
+                                        k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, block_size=block)
+            kc[:, kc.shape[1] - kn.shape[1]:].copy_(kn)
+            vc[:, vc.shape[1] - vn.shape[1]:].copy_(vn)
+        out = forward()
+        out_h.copy_(out, non_blocking=True)
+
+    e2e_ms = []
+    for it in range(2 + args.steps):
+        flush.zero_()
+        if world > 1:
+            dist.barrier()
+        ev0.record()
+        e2e_step()
+        ev1.record()
+        ev1.synchronize()
+        if it >= 2:
+            e2e_ms.append(ev0.elapsed_time(ev1))
+    e2e_total = torch.tensor([sum(e2e_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_total, op=dist.ReduceOp.MAX)
+    e2e_value = args.steps / (float(e2e_total.item()) * 1e-3)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak_tf, peak_gbs, peak_src = measured_peaks()
+    flops = sparse_f + (linear_f + gate_f if used_tuned else 0.0)
+    kernel_ms = float(np.mean(kern_ms)) if kern_ms else None
+    achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms else None
+    line = {
+        "metric": "hsa_fwd_chunks_per_s", "value": args.steps / (total_ms * 1e-3), "unit": "chunks/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, world),
+        "roofline": {
+            "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": (achieved / peak_tf) if achieved else None, "traffic": None, "peak_source": peak_src,
+            "kernel": "hsa_fwd_sm100 (tcgen05: sparse + linear + gate)" if used_tuned else "generic_attention_kernel (SIMT sparse branch)",
+            "kernel_ms": kernel_ms,
+            "flops": {"sparse": sparse_f, "linear": linear_f, "gate": gate_f, "counted": flops},
+            "sparse_only_frac": (sparse_f / (kernel_ms * 1e-3) / 1e12 / peak_tf) if kernel_ms else None,
+        },
+        "e2e": {"value": e2e_value, "unit": "chunks/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": float(e2e_total.item()) / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "wall_s": wall,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        value, ms, what = run_cpu(spec, steps=2, warmup=1, n_heads_sample=2 if args.workload == "c2" else 1)
+        line["cpu_baseline"] = {"value": value, "unit": "chunks/s", "cores": cores, "kind": "port", "sample": what,
+                                "ms_per_chunk": ms}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,202 @@
+/*
+ * worldattention_b200 -- C ABI of the sm_100a HSA / HKV kernels.
+ *
+ * One shared library (libwa_b200.so), plain C linkage, raw device pointers and sizes only.  The
+ * caller owns every buffer (inputs, outputs, workspace); the library allocates no device memory.
+ * All launches go to the CUDA stream passed as `stream` (a cudaStream_t cast to void*; NULL is
+ * the legacy default stream).  No entry point synchronises the host.
+ *
+ * Return value of every int function: 0 = success, < 0 = rejected argument (WA_ERR_*), > 0 = a
+ * cudaError_t raised by a launch.  `wa_last_error()` returns the message of the calling thread's
+ * most recent failure.  Nothing here throws, traps or aborts.
+ *
+ * Each entry point names the reference interface it stands in for; paths are relative to the
+ * WorldAttention project (wan/modules/hsa/..., pipeline/hkv/...).
+ */
+#ifndef WORLDATTENTION_B200_H_
+#define WORLDATTENTION_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WA_ABI_VERSION 1
+
+/* element types */
+#define WA_F32 0
+#define WA_BF16 1
+
+/* argument errors */
+#define WA_ERR_ARG (-1)         /* null pointer, non-positive size, bad dtype            */
+#define WA_ERR_UNSUPPORTED (-2) /* shape outside what the kernels implement              */
+#define WA_ERR_WORKSPACE (-3)   /* workspace missing or too small                        */
+#define WA_ERR_ALIGN (-4)       /* pointer / stride alignment the kernel needs is absent */
+#define WA_ERR_DEVICE (-5)      /* device is not sm_100 or driver entry point missing    */
+
+/* flags for wa_hsa_forward */
+#define WA_HSA_FORCE_GENERIC 1  /* skip the tcgen05 kernel even when the shape qualifies  */
+#define WA_HSA_REQUIRE_TUNED 2  /* fail with WA_ERR_UNSUPPORTED instead of using the generic kernels */
+
+/* A strided view of a `[B, L, H, D]` tensor whose last axis is contiguous.  Strides count
+ * elements.  `[B, H, N, D]` tensors are described by swapping stride_l / stride_h. */
+typedef struct wa_tensor4 {
+    void *ptr;
+    int32_t dtype; /* WA_F32 | WA_BF16 */
+    int32_t reserved;
+    int64_t stride_b, stride_l, stride_h;
+} wa_tensor4;
+
+int wa_abi_version(void);
+const char *wa_last_error(void);
+
+/* Measurement aids (no reference counterpart).  wa_launch_count: kernels this library has
+ * launched in this process.  wa_profile_enable(1) makes wa_hsa_forward bracket its attention
+ * kernel (the tcgen05 kernel, or the SIMT sparse kernel on the generic path) with CUDA events on
+ * the launch stream; wa_profile_attention_ms waits for the last bracketed launch and returns its
+ * duration.  Profiling is off by default and is the only place the library synchronises. */
+unsigned long long wa_launch_count(void);
+int wa_profile_enable(int on);
+int wa_profile_attention_ms(float *ms);
+
+/* ---------------------------------------------------------------------------------------------
+ * Routing -- wan/modules/hsa/routing.py
+ * ------------------------------------------------------------------------------------------- */
+
+/* block_mean_pool (routing.py:45-61).  Reads the unpadded `[B, L, H, D]` view once and writes
+ * float32 `[B, H, ceil(L/block_size), D]`.  Aligned L: mean rounded to the input dtype; ragged L:
+ * sum rounded to the input dtype, divided by the real block size in float32. */
+int wa_pool_blocks(const wa_tensor4 *x, int B, int L, int H, int D, int block_size, float *pooled,
+                   void *stream);
+
+/* block_attention_map (routing.py:64-68).  float32 `[B,H,Nq,D]` x `[B,H,Nkv,D]` ->
+ * softmax over Nkv, float32 `[B,H,Nq,Nkv]`; float64 accumulation, one rounding per value. */
+int wa_route_scores(const float *q_pooled, const float *k_pooled, int B, int H, int Nq, int Nkv,
+                    int D, float *block_attn, void *stream);
+
+/* build_block_routing (routing.py:71-118).  Descending order with equal values by ascending id,
+ * Gini -> per-head threshold -> cumulative-mass count.  `fixed_num_per_head` (device `[H]`, may
+ * be NULL) replaces the count by min(k_h, Nkv).  `mask` (bytes `[B,H,Nq,Nkv]`) may be NULL.
+ * `gini_scratch` is caller-provided device memory of B*H*Nq floats. */
+int wa_route_select(const float *block_attn, int B, int H, int Nq, int Nkv, double tau_min,
+                    double tau_max, const int32_t *fixed_num_per_head, int32_t *index,
+                    int32_t *num, uint8_t *mask, float *thresholds, float *gini_scratch,
+                    void *stream);
+
+/* map_to_index (block_sparse_triton.py:20-57).  Byte mask -> ascending ids (-1 filled) + count. */
+int wa_map_to_index(const uint8_t *mask, int B, int H, int Nq, int Nkv, int32_t *index,
+                    int32_t *num, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Attention branches -- wan/modules/hsa/block_sparse_torch.py, block_sparse_triton.py,
+ * attention.py
+ * ------------------------------------------------------------------------------------------- */
+
+/* block_sparse_attention_reference (block_sparse_torch.py:16-64) and the inference branch of
+ * block_sparse_attention (block_sparse_triton.py:371-382).  `Lq`/`Lkv` are the real lengths;
+ * rows of the last query block beyond Lq are not written.  `index` rows are `index_stride` ints
+ * apart; only the first num[b,h,i] entries are read and ids are clamped to [0, Nkv-1].
+ * `block_sizes` (device `[Nkv]`) may be NULL, meaning min(block_size, Lkv - id*block_size).
+ * Inputs are rounded to bf16 on load when `round_inputs_bf16` (attention.py:225-227); the result
+ * is rounded to bf16 when `round_output_bf16`.  `lse` (float32 `[B,H,Lq]`, natural log, -inf for
+ * an empty selection) may be NULL.  All-SIMT kernel for any D <= 256. */
+int wa_block_sparse_forward(const wa_tensor4 *q, const wa_tensor4 *k, const wa_tensor4 *v,
+                            const wa_tensor4 *out, int B, int H, int Lq, int Lkv, int D,
+                            int block_size, const int32_t *index, const int32_t *num,
+                            int index_stride, const int32_t *block_sizes, int round_inputs_bf16,
+                            int round_output_bf16, float *lse, void *stream);
+
+/* compress_kv (attention.py:64-110) on `[B, L, H, D]` views.  out_k/out_v receive
+ * `[B, sum_seg rank_seg, H, D]`; `proj_*` are `[proj_rank, proj_cols]` row-major. */
+int wa_compress_kv(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *out_k,
+                   const wa_tensor4 *out_v, int B, int L, int H, int D, int segment_len,
+                   int block_size, const void *k_proj, const void *v_proj, int proj_dtype,
+                   int proj_rank, int proj_cols, void *stream);
+
+/* _linear_branch (attention.py:113-118): dense softmax attention of q over Lc compressed slots.
+ * Output rounded to bf16 when `round_output_bf16`; `lse` as above, may be NULL. */
+int wa_linear_branch(const wa_tensor4 *q, const wa_tensor4 *k_coarse, const wa_tensor4 *v_coarse,
+                     const wa_tensor4 *out, int B, int H, int Lq, int Lc, int D,
+                     int round_output_bf16, float *lse, void *stream);
+
+/* Gate and combine (attention.py:246-259): out = sparse + linear * sigmoid(q W^T + b), or
+ * sigmoid(q) when gate_w is NULL.  W is `[D, D]` row-major (nn.Linear weight), b `[D]` or NULL. */
+int wa_gate_combine(const wa_tensor4 *q, const wa_tensor4 *sparse, const wa_tensor4 *linear,
+                    const wa_tensor4 *out, int B, int L, int H, int D, const void *gate_w,
+                    const void *gate_b, int gate_dtype, int round_gate_bf16, void *stream);
+
+/* Merge G shard partials of one branch: out = sum_g exp(lse_g - LSE) out_g (float32, natural
+ * log).  `outs` is `[G, rows, D]`, `lses` `[G, rows]`.  Used by the KV-sharded multi-GPU path;
+ * the reference has no sharded attention (its softmax, block_sparse_torch.py:62-64, is the G=1
+ * case). */
+int wa_merge_partials(const float *outs, const float *lses, int G, int64_t rows, int D,
+                      float *out, float *lse, void *stream);
+
+/* hsa_attention (attention.py:153-259), the whole forward in one call. */
+typedef struct wa_hsa_params {
+    int32_t B, H, D, Lq, Lkv, Lc; /* Lc = compressed slots supplied (0: compress inline)       */
+    int32_t block_size;
+    int32_t proj_segment_len, proj_rank, proj_cols, proj_dtype;
+    int32_t gate_dtype; /* dtype of gate_w / gate_b                                            */
+    int32_t flags;      /* WA_HSA_*                                                            */
+    int32_t reserved;
+    double tau_min, tau_max;
+    wa_tensor4 q, k, v, k_coarse, v_coarse, out;
+    const void *k_proj, *v_proj;         /* `[proj_rank, proj_cols]`; unused when Lc > 0        */
+    const void *gate_w, *gate_b;         /* NULL gate_w: gate = sigmoid(q)                      */
+    const int32_t *topk_per_head;        /* device `[H]` or NULL (cumulative-mass routing)      */
+    int32_t *index_out;                  /* optional `[B,H,Nq,Nkv]`, NULL: kept in workspace    */
+    int32_t *num_out;                    /* optional `[B,H,Nq]`                                 */
+    float *thresholds_out;               /* optional `[H]`                                      */
+    void *workspace;
+    size_t workspace_bytes;
+} wa_hsa_params;
+
+/* Bytes of workspace wa_hsa_forward needs for these sizes (pointers in `p` are ignored). */
+size_t wa_hsa_workspace_bytes(const wa_hsa_params *p);
+/* Returns through *used_tuned (may be NULL) whether the tcgen05 kernel ran. */
+int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * HKV retrieval -- pipeline/hkv/retrieval.py, rope.py, cache.py
+ * ------------------------------------------------------------------------------------------- */
+
+/* page_key_index + derope_temporal (retrieval.py:50-72, rope.py:70-82).  keys `[B, T, H, D]`;
+ * `spans` device int32 `[P, 2]` (start, end) token ranges; `derope` device float `[F, nt, 2]`
+ * = complex64 conj-rotation of frame f = t / frame_seq_length (NULL: no rotation).  Writes
+ * float32 `[P, H*D]`: mean over the page's tokens, then over the batch. */
+int wa_hkv_page_centroids(const wa_tensor4 *keys, int B, int T, int H, int D, const int32_t *spans,
+                          int P, const float *derope, int n_frames, int n_temporal,
+                          int frame_seq_length, float *page_index, void *stream);
+
+/* score_pages + top-k (retrieval.py:75-89, 105-126).  `page_index` float32 `[P, G*Dg]`, `query`
+ * `[G*Dg]`; G = 1 scores whole vectors (the reference), G = H scores each head's slice and
+ * selects per head.  scores `[G, P]` = dot / scale (scale <= 0: no division).  top_ids /
+ * top_scores `[G, topk]`: highest first, equal scores by lower id. */
+int wa_hkv_score_topk(const float *page_index, const float *query, int P, int G, int Dg,
+                      float scale, int topk, float *scores, int32_t *top_ids, float *top_scores,
+                      void *stream);
+
+/* One page copy of the install step (cache.py:229-246).  `row_elems` contiguous elements per
+ * token (H*D for whole-token pages, D for one head), token rows `src_stride` / `dst_stride`
+ * elements apart.  `rot` >= 0 selects `rotations[rot]` (shift_temporal_rope, rope.py:50-67) and
+ * applies it to the first 2*n_temporal elements of every head_dim-sized group; rot < 0 copies. */
+typedef struct wa_page_copy {
+    const void *src;
+    void *dst;
+    int64_t src_stride, dst_stride;
+    int32_t n_tokens;
+    int32_t rot;
+} wa_page_copy;
+
+/* `copies` is a device array of `n` records; `rotations` device float `[R, nt, 2]`. */
+int wa_hkv_gather_pages(const wa_page_copy *copies, int n, int max_tokens, int row_elems,
+                        int head_dim, int dtype, const float *rotations, int n_temporal,
+                        void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WORLDATTENTION_B200_H_ */

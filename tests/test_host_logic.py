@@ -1,0 +1,152 @@
+"""Host-side logic that needs no GPU: shape helpers, parameter contract, tier manager, sharding plans."""
+import math
+import shutil
+import tempfile
+
+import pytest
+import torch
+
+import worldattention_b200 as wa
+from worldattention_b200 import sharded
+from worldattention_b200.hsa.routing import block_counts, pad_to_len, variable_block_sizes
+
+
+def test_block_helpers():
+    assert block_counts(1560, 4680, 64) == (1600, 4736, 25, 74)
+    assert block_counts(4680, 32760, 128) == (4736, 32768, 37, 256)
+    sizes = variable_block_sizes(4680, 4736, 64, "cpu")
+    assert sizes.dtype == torch.int32 and sizes[-1] == 8 and (sizes[:-1] == 64).all()
+    x = torch.ones(1, 10, 2, 4)
+    assert pad_to_len(x, 16).shape == (1, 16, 2, 4) and pad_to_len(x, 16)[:, 10:].abs().sum() == 0
+    assert pad_to_len(x, 8) is x
+
+
+def test_module_contract():
+    hsa = wa.hsa.HSAAttention(num_heads=12, head_dim=128)
+    assert hsa.proj_rank == 25 and hsa.k_proj_mat.shape == (25, 1560) and hsa.k_proj_mat.dtype == torch.bfloat16
+    assert sorted(wa.hsa.hsa_parameter_names(hsa)) == ["gate_lin.bias", "gate_lin.weight", "k_proj_mat", "v_proj_mat"]
+    assert all(torch.count_nonzero(p) == 0 for p in hsa.parameters())
+    assert wa.hsa_stage.init_hsa_parameters(hsa) == 1
+    row = hsa.k_proj_mat[0]
+    assert int((row != 0).sum()) == 64 and abs(row[0].item() - 1 / 64) < 1e-3
+    last = hsa.k_proj_mat[24]
+    assert int((last != 0).sum()) == 1560 - 24 * 64
+    hsa.reset_parameters()
+    assert torch.count_nonzero(hsa.k_proj_mat) == 0
+    assert hsa.coarse_cache_size(0) == 0 and hsa.coarse_cache_size(32760) == 21 * 25
+    assert hsa.token_range_to_coarse(1560, 4680) == (25, 75)
+    with pytest.raises(ValueError):
+        hsa.token_range_to_coarse(0, 1561)
+    with pytest.raises(ValueError):
+        wa.hsa.HSAAttention(num_heads=1, head_dim=8, block_size=32)
+    with pytest.raises(ValueError):
+        wa.hsa.HSAAttention(num_heads=1, head_dim=8, proj_segment_len=0)
+    assert wa.hsa.HSAAttention(num_heads=1, head_dim=8, block_size=128).proj_rank == 13
+    wa.hsa.require_trained_hsa([], "ckpt.pt")
+    wa.hsa.require_trained_hsa(["blocks.0.self_attn.q.weight"])
+    with pytest.raises(RuntimeError, match="HSA training") as err:
+        wa.hsa.require_trained_hsa(["blocks.0.self_attn.hsa_attention.k_proj_mat"], "ckpt.pt")
+    assert "ckpt.pt" in str(err.value)
+    assert wa.hsa.resolve_backend("torch") == "torch" and wa.hsa.resolve_backend("triton") == "triton"
+    assert wa.hsa.resolve_backend("auto") in ("torch", "triton")
+    with pytest.raises(ValueError):
+        wa.hsa.resolve_backend("nope")
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    hsa = wa.hsa.HSAAttention(num_heads=2, head_dim=16, proj_segment_len=50)
+    q = torch.randn(1, 8, 2, 16)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        hsa(q, q, q)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        wa.hsa.build_block_routing(torch.rand(1, 1, 2, 4), 0.35, 1.0)
+
+
+def test_reference_import_paths_resolve():
+    wa.install_reference_aliases()
+    from wan.modules.hsa import HSAAttention                      # noqa: F401
+    from wan.modules.hsa.attention import _linear_branch          # noqa: F401
+    from wan.modules.hsa.routing import block_counts as bc        # noqa: F401
+    from pipeline.hkv import HKVCache, HKVTierManager             # noqa: F401
+    from pipeline.hkv.rope import temporal_band                   # noqa: F401
+    from trainer.hsa_stage import init_hsa_parameters             # noqa: F401
+    assert HSAAttention is wa.hsa.HSAAttention and HKVCache is wa.hkv.HKVCache
+
+
+def _blob(tag):
+    return {"k": [torch.full((1, 4, 1, 2), float(tag))], "v": [torch.full((1, 4, 1, 2), -float(tag))]}
+
+
+def test_tier_manager_lru_spill_and_reload():
+    tmp = tempfile.mkdtemp()
+    try:
+        tier = wa.hkv.HKVTierManager(cpu_max_chunks=2, nvme_enabled=True, nvme_dir=tmp)
+        for c in range(3):
+            tier.put(c, _blob(c))
+        assert [tier.location(c) for c in range(3)] == ["nvme", "cpu", "cpu"]
+        assert tier.stats()["n_spills"] == 1 and tier.stats()["backups"] == 1
+        blob = tier.get(0)                                  # reload evicts the least recently used (1)
+        assert blob["k"][0][0, 0, 0, 0] == 0.0 and tier.stats()["n_loads"] == 1
+        assert [tier.location(c) for c in range(3)] == ["cpu", "nvme", "cpu"]
+        tier.get(2); tier.put(3, _blob(3))                   # 0 is now the oldest -> re-spilled without rewriting
+        assert tier.location(0) == "nvme" and tier.stats()["backups"] == 2 and tier.stats()["n_spills"] == 3
+        assert tier.get(42) is None and tier.location(42) == "absent"
+        tier.cleanup()
+        assert tier.stats()["cpu_resident"] == 0 and tier.location(0) == "absent"
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    drop = wa.hkv.HKVTierManager(cpu_max_chunks=0)           # capacity floors at 1
+    drop.put(0, _blob(0)); drop.put(1, _blob(1))
+    assert drop.location(0) == "absent" and drop.stats()["n_drops"] == 1 and drop.get(0) is None
+    with pytest.raises(ValueError):
+        wa.hkv.HKVTierManager(cpu_max_chunks=1, nvme_enabled=True)
+
+
+def test_temporal_band_sizes():
+    assert wa.hkv.temporal_complex_dims(128) == 22
+    assert wa.hkv.temporal_complex_dims(24) == 4
+    assert wa.hkv.temporal_band(torch.zeros(1024, 64), 128).shape == (1024, 22)
+
+
+def test_head_split_plans():
+    assert sharded.plan_head_split(12, 2) == [list(range(6)), list(range(6, 12))]
+    assert [len(x) for x in sharded.plan_head_split(12, 8)] == [2, 2, 2, 2, 1, 1, 1, 1]
+    k = [8, 32, 4, 4, 32, 8, 32, 8, 32, 4, 4, 8]
+    for world in (2, 4):
+        plan = sharded.plan_head_split(12, world, k)
+        assert sorted(h for p in plan for h in p) == list(range(12))
+        assert all(len(p) == 12 // world for p in plan)
+        loads = [sum(k[h] for h in p) for p in plan]
+        assert max(loads) - min(loads) <= 8, loads
+    with pytest.raises(ValueError):
+        sharded.plan_head_split(4, 8)
+
+
+def test_kv_shard_plans_cut_at_block_boundaries():
+    for kv_len, bs, world, page in ((748_800, 64, 8, 1560), (32_760, 128, 8, 1560), (1000, 64, 4, 0), (100, 64, 8, 0)):
+        shards = sharded.plan_kv_shards(kv_len, bs, world, page)
+        assert len(shards) == world and shards[0][0] == 0 and shards[-1][1] == kv_len
+        for (a, b), (c, d) in zip(shards, shards[1:]):
+            assert b == c and a <= b and b % bs == 0
+        assert sum(math.ceil((b - a) / bs) for a, b in shards) == math.ceil(kv_len / bs)
+
+
+def test_local_selection_partitions_the_global_selection():
+    torch.manual_seed(0)
+    nkv = 37
+    index = torch.stack([torch.randperm(nkv) for _ in range(6)]).view(1, 2, 3, nkv).int()
+    num = torch.randint(0, nkv + 1, (1, 2, 3)).int()
+    bounds = [0, 5, 5, 20, 37]
+    seen = torch.zeros(1, 2, 3, nkv, dtype=torch.int32)
+    for lo, hi in zip(bounds, bounds[1:]):
+        li, ln = sharded.local_selection(index, num, lo, hi)
+        for h in range(2):
+            for i in range(3):
+                ids = li[0, h, i, : int(ln[0, h, i])].tolist()
+                assert ids == sorted(ids) and all(0 <= x < hi - lo for x in ids)
+                seen[0, h, i, [x + lo for x in ids]] += 1
+    want = torch.zeros_like(seen)
+    for h in range(2):
+        for i in range(3):
+            want[0, h, i, index[0, h, i, : int(num[0, h, i])].long()] = 1
+    assert torch.equal(seen, want)

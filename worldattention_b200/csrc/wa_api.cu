@@ -1,0 +1,205 @@
+// C-ABI glue: error buffer, version, and the whole-forward entry point wa_hsa_forward, which
+// sequences routing -> sparse branch -> compressed branch -> gate/combine on one stream.
+// Mirrors hsa_attention, wan/modules/hsa/attention.py:153-259.
+#include "wa_common.cuh"
+#include "wa_internal.cuh"
+
+namespace wa {
+char *last_error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+unsigned long long &launch_counter() {
+    static unsigned long long n = 0;
+    return n;
+}
+
+// Optional timing of the attention kernel inside wa_hsa_forward (for roofline measurement).
+static bool g_profile = false;
+static cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
+static bool g_ev_valid = false;
+
+void profile_mark(bool begin, cudaStream_t stream) {
+    if (!g_profile) return;
+    if (!g_ev0) {
+        if (cudaEventCreate(&g_ev0) != cudaSuccess || cudaEventCreate(&g_ev1) != cudaSuccess) {
+            g_ev0 = g_ev1 = nullptr;
+            return;
+        }
+    }
+    cudaEventRecord(begin ? g_ev0 : g_ev1, stream);
+    if (!begin) g_ev_valid = true;
+}
+}  // namespace wa
+
+using namespace wa;
+
+extern "C" int wa_abi_version(void) { return WA_ABI_VERSION; }
+extern "C" unsigned long long wa_launch_count(void) { return launch_counter(); }
+extern "C" int wa_profile_enable(int on) {
+    g_profile = on != 0;
+    g_ev_valid = false;
+    return 0;
+}
+extern "C" int wa_profile_attention_ms(float *ms) {
+    WA_REQUIRE(ms, WA_ERR_ARG, "wa_profile_attention_ms: null pointer");
+    WA_REQUIRE(g_ev_valid, WA_ERR_ARG, "wa_profile_attention_ms: no profiled launch recorded");
+    cudaError_t e = cudaEventSynchronize(g_ev1);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(ms, g_ev0, g_ev1);
+    if (e != cudaSuccess) return fail((int)e, "wa_profile_attention_ms: %s", cudaGetErrorString(e));
+    return 0;
+}
+extern "C" const char *wa_last_error(void) { return last_error_buffer(); }
+
+namespace {
+
+struct Workspace {
+    size_t q_pooled, k_pooled, block_attn, index, num, gini, thresholds, kc, vc, sparse, linear, tuned, total;
+    int Nq, Nkv, Lc_inline;
+};
+
+size_t take(size_t &cursor, size_t bytes) {
+    const size_t at = cursor;
+    cursor = align_up(cursor + bytes, 256);
+    return at;
+}
+
+int inline_coarse_len(const wa_hsa_params *p) {
+    const int seg = p->proj_segment_len > 0 ? p->proj_segment_len : p->Lkv;
+    int total = 0;
+    for (int start = 0; start < p->Lkv; start += seg) {
+        const int n = p->Lkv - start < seg ? p->Lkv - start : seg;
+        const int r = ceil_div(n, p->block_size);
+        total += r < p->proj_rank ? r : p->proj_rank;
+    }
+    return total;
+}
+
+Workspace plan(const wa_hsa_params *p) {
+    Workspace w{};
+    w.Nq = ceil_div(p->Lq, p->block_size);
+    w.Nkv = ceil_div(p->Lkv, p->block_size);
+    w.Lc_inline = p->Lc > 0 ? 0 : inline_coarse_len(p);
+    const size_t bh = (size_t)p->B * p->H;
+    size_t c = 0;
+    w.q_pooled = take(c, bh * w.Nq * p->D * sizeof(float));
+    w.k_pooled = take(c, bh * w.Nkv * p->D * sizeof(float));
+    w.block_attn = take(c, bh * w.Nq * w.Nkv * sizeof(float));
+    w.index = take(c, bh * w.Nq * w.Nkv * sizeof(int32_t));
+    w.num = take(c, bh * w.Nq * sizeof(int32_t));
+    w.gini = take(c, bh * w.Nq * sizeof(float));
+    w.thresholds = take(c, (size_t)p->H * sizeof(float));
+    const size_t kvsz = dtype_size(p->k.dtype);
+    w.kc = take(c, (size_t)p->B * w.Lc_inline * p->H * p->D * kvsz);
+    w.vc = take(c, (size_t)p->B * w.Lc_inline * p->H * p->D * kvsz);
+    const size_t tokens = (size_t)p->B * p->Lq * p->H * p->D;
+    w.sparse = take(c, tokens * sizeof(__nv_bfloat16));
+    w.linear = take(c, tokens * sizeof(float));
+    w.tuned = take(c, hsa_sm100_workspace_bytes(p));
+    w.total = c;
+    return w;
+}
+
+int validate(const wa_hsa_params *p) {
+    const char *what = "wa_hsa_forward";
+    WA_REQUIRE(p, WA_ERR_ARG, "%s: null params", what);
+    WA_REQUIRE(p->B > 0 && p->H > 0 && p->D > 0, WA_ERR_ARG, "%s: B, H, D must be positive", what);
+    WA_REQUIRE(p->Lq > 0 && p->Lkv > 0, WA_ERR_ARG, "%s: q_len and kv_len must be positive", what);
+    WA_REQUIRE(p->block_size > 0, WA_ERR_ARG, "%s: block_size must be positive", what);
+    WA_REQUIRE(p->Lc >= 0, WA_ERR_ARG, "%s: negative compressed length", what);
+    WA_REQUIRE(valid_dtype(p->q.dtype) && valid_dtype(p->k.dtype) && p->k.dtype == p->v.dtype &&
+                   valid_dtype(p->out.dtype),
+               WA_ERR_ARG, "%s: bad or mismatched q/k/v/out dtypes", what);
+    if (p->Lc > 0) {
+        WA_REQUIRE(p->k_coarse.ptr && p->v_coarse.ptr, WA_ERR_ARG, "%s: compressed cache pointers are null", what);
+        WA_REQUIRE(valid_dtype(p->k_coarse.dtype) && p->k_coarse.dtype == p->v_coarse.dtype, WA_ERR_ARG,
+                   "%s: bad compressed cache dtype", what);
+    } else {
+        WA_REQUIRE(p->k_proj && p->v_proj && p->proj_rank > 0 && p->proj_cols > 0 && valid_dtype(p->proj_dtype),
+                   WA_ERR_ARG, "%s: projection matrices required when no compressed cache is given", what);
+    }
+    WA_REQUIRE(!p->gate_w || valid_dtype(p->gate_dtype), WA_ERR_ARG, "%s: bad gate dtype", what);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" size_t wa_hsa_workspace_bytes(const wa_hsa_params *p) {
+    if (!p || p->B <= 0 || p->H <= 0 || p->D <= 0 || p->Lq <= 0 || p->Lkv <= 0 || p->block_size <= 0) return 0;
+    return plan(p).total;
+}
+
+extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *stream_) {
+    const char *what = "wa_hsa_forward";
+    int rc = validate(p);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const Workspace w = plan(p);
+    WA_REQUIRE(p->workspace && p->workspace_bytes >= w.total, WA_ERR_WORKSPACE,
+               "%s: workspace of %zu bytes required, got %zu", what, w.total, p->workspace_bytes);
+    WA_REQUIRE((uintptr_t)p->workspace % 256 == 0, WA_ERR_ALIGN, "%s: workspace must be 256-byte aligned", what);
+    char *ws = (char *)p->workspace;
+    float *q_pooled = (float *)(ws + w.q_pooled), *k_pooled = (float *)(ws + w.k_pooled);
+    float *block_attn = (float *)(ws + w.block_attn);
+    int32_t *index = p->index_out ? p->index_out : (int32_t *)(ws + w.index);
+    int32_t *num = p->num_out ? p->num_out : (int32_t *)(ws + w.num);
+    float *thresholds = p->thresholds_out ? p->thresholds_out : (float *)(ws + w.thresholds);
+    float *gini = (float *)(ws + w.gini);
+    if (used_tuned) *used_tuned = 0;
+
+    // ---- routing (routing.py:45-118) ---------------------------------------------------------
+    if ((rc = wa_pool_blocks(&p->q, p->B, p->Lq, p->H, p->D, p->block_size, q_pooled, stream))) return rc;
+    if ((rc = wa_pool_blocks(&p->k, p->B, p->Lkv, p->H, p->D, p->block_size, k_pooled, stream))) return rc;
+    if ((rc = wa_route_scores(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, block_attn, stream))) return rc;
+    if ((rc = wa_route_select(block_attn, p->B, p->H, w.Nq, w.Nkv, p->tau_min, p->tau_max, p->topk_per_head, index,
+                              num, nullptr, thresholds, gini, stream)))
+        return rc;
+
+    // ---- compressed cache (attention.py:186-200) ----------------------------------------------
+    wa_tensor4 kc = p->k_coarse, vc = p->v_coarse;
+    int Lc = p->Lc;
+    if (Lc == 0) {
+        Lc = w.Lc_inline;
+        kc.ptr = ws + w.kc; vc.ptr = ws + w.vc;
+        kc.dtype = vc.dtype = p->k.dtype;
+        kc.stride_h = vc.stride_h = p->D;
+        kc.stride_l = vc.stride_l = (int64_t)p->H * p->D;
+        kc.stride_b = vc.stride_b = (int64_t)Lc * p->H * p->D;
+        if ((rc = wa_compress_kv(&p->k, &p->v, &kc, &vc, p->B, p->Lkv, p->H, p->D, p->proj_segment_len,
+                                 p->block_size, p->k_proj, p->v_proj, p->proj_dtype, p->proj_rank, p->proj_cols,
+                                 stream)))
+            return rc;
+    }
+    const int lin_dtype = vc.dtype;
+
+    // ---- tuned tcgen05 path -------------------------------------------------------------------
+    const bool want_tuned = !(p->flags & WA_HSA_FORCE_GENERIC);
+    if (want_tuned && hsa_sm100_supported(p, Lc, &kc, &vc)) {
+        profile_mark(true, stream);
+        rc = hsa_sm100_launch(p, Lc, &kc, &vc, index, num, w.Nq, w.Nkv, ws + w.tuned, stream);
+        profile_mark(false, stream);
+        if (rc) return rc;
+        if (used_tuned) *used_tuned = 1;
+        return 0;
+    }
+    WA_REQUIRE(!(p->flags & WA_HSA_REQUIRE_TUNED), WA_ERR_UNSUPPORTED,
+               "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 128)", what);
+
+    // ---- generic SIMT path --------------------------------------------------------------------
+    wa_tensor4 sparse{}, linear{};
+    sparse.ptr = ws + w.sparse; sparse.dtype = WA_BF16;
+    linear.ptr = ws + w.linear; linear.dtype = lin_dtype;
+    sparse.stride_h = linear.stride_h = p->D;
+    sparse.stride_l = linear.stride_l = (int64_t)p->H * p->D;
+    sparse.stride_b = linear.stride_b = (int64_t)p->Lq * p->H * p->D;
+    profile_mark(true, stream);
+    rc = wa_block_sparse_forward(&p->q, &p->k, &p->v, &sparse, p->B, p->H, p->Lq, p->Lkv, p->D, p->block_size, index,
+                                 num, w.Nkv, nullptr, /*round_in=*/1, /*round_out=*/1, nullptr, stream);
+    profile_mark(false, stream);
+    if (rc) return rc;
+    if ((rc = wa_linear_branch(&p->q, &kc, &vc, &linear, p->B, p->H, p->Lq, Lc, p->D, lin_dtype == WA_BF16, nullptr,
+                               stream)))
+        return rc;
+    return wa_gate_combine(&p->q, &sparse, &linear, &p->out, p->B, p->Lq, p->H, p->D, p->gate_w, p->gate_b,
+                           p->gate_dtype, lin_dtype == WA_BF16, stream);
+}

@@ -1,0 +1,311 @@
+// Hierarchical KV cache retrieval on the GPU: page centroids, page scoring + top-k, page install.
+//
+// Stand-ins for pipeline/hkv/retrieval.py:50-126, pipeline/hkv/rope.py:33-82 and the copy loop of
+// pipeline/hkv/cache.py:229-246.  All three are byte-moving, HBM-bound kernels: 128-bit coalesced
+// accesses, warp-shuffle reductions, no tensor cores.
+#include "wa_common.cuh"
+
+namespace wa {
+
+// ------------------------------------------------------------------------------------------------
+// Page centroids with the temporal rotation removed.
+// grid (pair tiles, pages); block (CT_TX complex pairs, CT_TY token rows).
+// ------------------------------------------------------------------------------------------------
+constexpr int CT_TX = 64, CT_TY = 4;
+
+__global__ void __launch_bounds__(CT_TX *CT_TY)
+page_centroid_kernel(View4 keys, int B, int H, int D, const int32_t *__restrict__ spans,
+                     const float2 *__restrict__ derope, int n_frames, int nt, int frame_seq_length,
+                     float *__restrict__ page_index) {
+    __shared__ double sre[CT_TY][CT_TX], sim[CT_TY][CT_TX];
+    const int page = blockIdx.y;
+    const int pair = blockIdx.x * CT_TX + threadIdx.x;   // complex pair within the H*D row
+    const int ty = threadIdx.y;
+    const int start = spans[2 * page], end = spans[2 * page + 1];
+    const int n_tok = max(0, end - start);
+    const bool active = pair < (H * D) / 2;
+    const int h = active ? (2 * pair) / D : 0;
+    const int dpair = active ? ((2 * pair) % D) / 2 : 0;
+    const bool rotate = derope != nullptr && dpair < nt;
+
+    double out_re = 0.0, out_im = 0.0;   // running sum over the batch of per-item token means
+    for (int b = 0; b < B; ++b) {
+        double acc_re = 0.0, acc_im = 0.0;
+        if (active) {
+            const long long base = (long long)b * keys.sb + (long long)h * keys.sh + 2 * dpair;
+            for (int t = start + ty; t < end; t += CT_TY) {
+                const long long off = base + (long long)t * keys.sl;
+                float a = load_elem(keys.ptr, keys.dtype, off);
+                float c = load_elem(keys.ptr, keys.dtype, off + 1);
+                if (rotate) {
+                    const int f = min(max(t / frame_seq_length, 0), n_frames - 1);
+                    const float2 w = derope[(long long)f * nt + dpair];
+                    const float re = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(c, w.y));
+                    const float im = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(c, w.x));
+                    a = re;
+                    c = im;
+                    if (keys.dtype == WA_BF16) {
+                        a = bf16_round_f(a);
+                        c = bf16_round_f(c);
+                    }
+                }
+                acc_re += (double)a;
+                acc_im += (double)c;
+            }
+        }
+        sre[ty][threadIdx.x] = acc_re;
+        sim[ty][threadIdx.x] = acc_im;
+        __syncthreads();
+        if (ty == 0 && active) {
+            double r = 0.0, i = 0.0;
+            for (int y = 0; y < CT_TY; ++y) {
+                r += sre[y][threadIdx.x];
+                i += sim[y][threadIdx.x];
+            }
+            out_re += (double)(float)(r / (double)max(n_tok, 1));
+            out_im += (double)(float)(i / (double)max(n_tok, 1));
+        }
+        __syncthreads();
+    }
+    if (ty == 0 && active) {
+        float *dst = page_index + (long long)page * H * D + 2 * pair;
+        dst[0] = (float)(out_re / (double)B);
+        dst[1] = (float)(out_im / (double)B);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Page scores and top-k.  One CTA per score group (1 = whole vector, H = per head).
+// ------------------------------------------------------------------------------------------------
+constexpr int ST_THREADS = 256;
+
+__device__ __forceinline__ unsigned long long rank_key(float s, int id) {
+    if (s == 0.0f) s = 0.0f;
+    uint32_t u = __float_as_uint(s);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)(~u) << 32) | (unsigned)id;   // ascending key = descending score, ascending id
+}
+
+__global__ void __launch_bounds__(ST_THREADS)
+score_topk_kernel(const float *__restrict__ page_index, const float *__restrict__ query, int P, int G, int Dg,
+                  float scale, int topk, float *__restrict__ scores, int32_t *__restrict__ top_ids,
+                  float *__restrict__ top_scores) {
+    __shared__ unsigned long long red[ST_THREADS / 32];
+    __shared__ unsigned long long prev_s;
+    const int g = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *q = query + (long long)g * Dg;
+    float *sc = scores + (long long)g * P;
+
+    for (int p = warp; p < P; p += ST_THREADS / 32) {
+        const float *row = page_index + ((long long)p * G + g) * Dg;
+        double acc = 0.0;
+        for (int d = lane; d < Dg; d += 32) acc = fma((double)row[d], (double)q[d], acc);
+        acc = warp_sum_d(acc);
+        if (lane == 0) {
+            float s = (float)acc;
+            if (scale > 0.f) s = __fdiv_rn(s, scale);
+            sc[p] = s;
+        }
+    }
+    __syncthreads();
+    if (topk <= 0) return;
+
+    unsigned long long prev = 0ull;
+    bool first = true;
+    for (int r = 0; r < topk; ++r) {
+        unsigned long long best = 0xFFFFFFFFFFFFFFFFull;
+        for (int p = threadIdx.x; p < P; p += ST_THREADS) {
+            const unsigned long long key = rank_key(sc[p], p);
+            if ((first || key > prev) && key < best) best = key;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other < best ? other : best;
+        }
+        if (lane == 0) red[warp] = best;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long bb = red[0];
+            for (int w = 1; w < ST_THREADS / 32; ++w) bb = red[w] < bb ? red[w] : bb;
+            prev_s = bb;
+            const long long o = (long long)g * topk + r;
+            if (bb != 0xFFFFFFFFFFFFFFFFull) {
+                const int id = (int)(bb & 0xFFFFFFFFull);
+                top_ids[o] = id;
+                top_scores[o] = sc[id];
+            } else {
+                top_ids[o] = -1;
+                top_scores[o] = -INFINITY;
+            }
+        }
+        __syncthreads();
+        prev = prev_s;
+        first = false;
+        if (prev == 0xFFFFFFFFFFFFFFFFull) {
+            // fewer than topk pages: fill the tail
+            for (int rr = r + 1 + threadIdx.x; rr < topk; rr += ST_THREADS) {
+                top_ids[(long long)g * topk + rr] = -1;
+                top_scores[(long long)g * topk + rr] = -INFINITY;
+            }
+            return;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Page install: strided row copy with an optional per-page temporal rotation of the keys.
+// grid (token tiles, records).  16-byte vectors when every address allows it.
+// ------------------------------------------------------------------------------------------------
+constexpr int GP_THREADS = 256;
+constexpr int GP_UNROLL = 4;
+
+template <typename T, int VE>   // VE elements per 16-byte vector
+__device__ __forceinline__ void rotate_vec(uint4 &raw, int elem0, int head_dim, int nt, const float2 *rot) {
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < VE; i += 2) {
+        const int dpair = ((elem0 + i) % head_dim) >> 1;
+        if (dpair < nt) {
+            const float2 w = rot[dpair];
+            float a, c;
+            if (sizeof(T) == 2) {
+                a = __bfloat162float(reinterpret_cast<__nv_bfloat16 *>(e)[i]);
+                c = __bfloat162float(reinterpret_cast<__nv_bfloat16 *>(e)[i + 1]);
+            } else {
+                a = reinterpret_cast<float *>(e)[i];
+                c = reinterpret_cast<float *>(e)[i + 1];
+            }
+            const float re = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(c, w.y));
+            const float im = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(c, w.x));
+            if (sizeof(T) == 2) {
+                reinterpret_cast<__nv_bfloat16 *>(e)[i] = __float2bfloat16_rn(re);
+                reinterpret_cast<__nv_bfloat16 *>(e)[i + 1] = __float2bfloat16_rn(im);
+            } else {
+                reinterpret_cast<float *>(e)[i] = re;
+                reinterpret_cast<float *>(e)[i + 1] = im;
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(GP_THREADS)
+gather_pages_kernel(const wa_page_copy *__restrict__ copies, int row_elems, int head_dim,
+                    const float2 *__restrict__ rotations, int nt) {
+    constexpr int VE = 16 / sizeof(T);
+    const wa_page_copy rec = copies[blockIdx.y];
+    const T *src = reinterpret_cast<const T *>(rec.src);
+    T *dst = reinterpret_cast<T *>(rec.dst);
+    const float2 *rot = (rec.rot >= 0 && rotations) ? rotations + (long long)rec.rot * nt : nullptr;
+    const bool vec_ok = (row_elems % VE == 0) && (rec.src_stride % VE == 0) && (rec.dst_stride % VE == 0) &&
+                        (reinterpret_cast<uintptr_t>(src) % 16 == 0) && (reinterpret_cast<uintptr_t>(dst) % 16 == 0) &&
+                        (head_dim % VE == 0 || rot == nullptr);
+    if (vec_ok) {
+        const int vpr = row_elems / VE;
+        const long long total = (long long)rec.n_tokens * vpr;
+        const long long base = (long long)blockIdx.x * GP_THREADS * GP_UNROLL + threadIdx.x;
+        uint4 buf[GP_UNROLL];
+        long long tok[GP_UNROLL];
+        int c[GP_UNROLL];
+#pragma unroll
+        for (int u = 0; u < GP_UNROLL; ++u) {
+            const long long e = base + (long long)u * GP_THREADS;
+            if (e < total) {
+                tok[u] = e / vpr;
+                c[u] = (int)(e % vpr) * VE;
+                buf[u] = *reinterpret_cast<const uint4 *>(src + tok[u] * rec.src_stride + c[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < GP_UNROLL; ++u) {
+            const long long e = base + (long long)u * GP_THREADS;
+            if (e < total) {
+                if (rot) rotate_vec<T, VE>(buf[u], c[u], head_dim, nt, rot);
+                *reinterpret_cast<uint4 *>(dst + tok[u] * rec.dst_stride + c[u]) = buf[u];
+            }
+        }
+    } else {
+        // element pairs
+        const int ppr = row_elems / 2;
+        const long long total = (long long)rec.n_tokens * ppr;
+        for (int u = 0; u < GP_UNROLL * 4; ++u) {
+            const long long e = ((long long)blockIdx.x * GP_UNROLL * 4 + u) * GP_THREADS + threadIdx.x;
+            if (e >= total) break;
+            const long long t = e / ppr;
+            const int col = (int)(e % ppr) * 2;
+            float a = load_elem(src, sizeof(T) == 2 ? WA_BF16 : WA_F32, t * rec.src_stride + col);
+            float b = load_elem(src, sizeof(T) == 2 ? WA_BF16 : WA_F32, t * rec.src_stride + col + 1);
+            const int dpair = (col % head_dim) >> 1;
+            if (rot && dpair < nt) {
+                const float2 w = rot[dpair];
+                const float re = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+                const float im = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+                a = re;
+                b = im;
+            }
+            store_elem(dst, sizeof(T) == 2 ? WA_BF16 : WA_F32, t * rec.dst_stride + col, a);
+            store_elem(dst, sizeof(T) == 2 ? WA_BF16 : WA_F32, t * rec.dst_stride + col + 1, b);
+        }
+    }
+}
+
+}  // namespace wa
+
+using namespace wa;
+
+extern "C" int wa_hkv_page_centroids(const wa_tensor4 *keys, int B, int T, int H, int D, const int32_t *spans,
+                                     int P, const float *derope, int n_frames, int n_temporal,
+                                     int frame_seq_length, float *page_index, void *stream) {
+    const char *what = "wa_hkv_page_centroids";
+    WA_REQUIRE(keys && keys->ptr && spans && page_index, WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(valid_dtype(keys->dtype), WA_ERR_ARG, "%s: bad dtype", what);
+    WA_REQUIRE(B > 0 && T > 0 && H > 0 && D > 0 && P > 0, WA_ERR_ARG, "%s: sizes must be positive", what);
+    WA_REQUIRE(D % 2 == 0, WA_ERR_UNSUPPORTED, "%s: head_dim must be even", what);
+    WA_REQUIRE(!derope || (n_frames > 0 && n_temporal >= 0 && 2 * n_temporal <= D && frame_seq_length > 0),
+               WA_ERR_ARG, "%s: bad rotation table arguments", what);
+    WA_REQUIRE(P <= 65535, WA_ERR_UNSUPPORTED, "%s: at most 65535 pages per call", what);
+    dim3 grid(ceil_div(H * D / 2, CT_TX), P), block(CT_TX, CT_TY);
+    page_centroid_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
+        make_view(keys), B, H, D, spans, reinterpret_cast<const float2 *>(derope), n_frames, n_temporal,
+        frame_seq_length, page_index);
+    return check_launch(what);
+}
+
+extern "C" int wa_hkv_score_topk(const float *page_index, const float *query, int P, int G, int Dg, float scale,
+                                 int topk, float *scores, int32_t *top_ids, float *top_scores, void *stream) {
+    const char *what = "wa_hkv_score_topk";
+    WA_REQUIRE(page_index && query && scores, WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(topk <= 0 || (top_ids && top_scores), WA_ERR_ARG, "%s: top-k outputs are null", what);
+    WA_REQUIRE(P > 0 && G > 0 && Dg > 0, WA_ERR_ARG, "%s: sizes must be positive", what);
+    score_topk_kernel<<<G, ST_THREADS, 0, (cudaStream_t)stream>>>(page_index, query, P, G, Dg, scale, topk, scores,
+                                                                  top_ids, top_scores);
+    return check_launch(what);
+}
+
+extern "C" int wa_hkv_gather_pages(const wa_page_copy *copies, int n, int max_tokens, int row_elems, int head_dim,
+                                   int dtype, const float *rotations, int n_temporal, void *stream) {
+    const char *what = "wa_hkv_gather_pages";
+    WA_REQUIRE(copies, WA_ERR_ARG, "%s: null record array", what);
+    WA_REQUIRE(valid_dtype(dtype), WA_ERR_ARG, "%s: bad dtype", what);
+    WA_REQUIRE(n > 0 && max_tokens > 0 && row_elems > 0 && head_dim > 0, WA_ERR_ARG, "%s: sizes must be positive",
+               what);
+    WA_REQUIRE(row_elems % 2 == 0 && head_dim % 2 == 0 && row_elems % head_dim == 0, WA_ERR_UNSUPPORTED,
+               "%s: row_elems must be a multiple of an even head_dim", what);
+    WA_REQUIRE(n <= 65535, WA_ERR_UNSUPPORTED, "%s: at most 65535 records per call", what);
+    WA_REQUIRE(2 * n_temporal <= head_dim, WA_ERR_ARG, "%s: temporal band wider than head_dim", what);
+    const int ve = dtype == WA_BF16 ? 8 : 4;
+    // tiles sized for the vector path; the pair path covers 4x as many (smaller) items per CTA
+    const long long vecs = (long long)max_tokens * ceil_div(row_elems, ve);
+    const long long tiles = (vecs + GP_THREADS * GP_UNROLL - 1) / (GP_THREADS * GP_UNROLL);
+    WA_REQUIRE(tiles < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: page too large", what);
+    dim3 grid((unsigned)tiles, n);
+    if (dtype == WA_BF16)
+        gather_pages_kernel<__nv_bfloat16><<<grid, GP_THREADS, 0, (cudaStream_t)stream>>>(
+            copies, row_elems, head_dim, reinterpret_cast<const float2 *>(rotations), n_temporal);
+    else
+        gather_pages_kernel<float><<<grid, GP_THREADS, 0, (cudaStream_t)stream>>>(
+            copies, row_elems, head_dim, reinterpret_cast<const float2 *>(rotations), n_temporal);
+    return check_launch(what);
+}

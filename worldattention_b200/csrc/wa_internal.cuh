@@ -1,0 +1,14 @@
+// Internal (non-ABI) declarations shared between translation units.
+#pragma once
+#include "wa_common.cuh"
+
+namespace wa {
+
+// tcgen05 fused HSA kernel (wa_hsa_sm100.cu)
+size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p);
+bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc);
+int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc,
+                     const int32_t *index, const int32_t *num, int Nq, int Nkv, void *workspace,
+                     cudaStream_t stream);
+
+}  // namespace wa

@@ -1,0 +1,320 @@
+"""Hierarchical KV Cache (HKV) on B200 (reference: pipeline/hkv/cache.py).
+
+The history of an autoregressive rollout is kept outside the online cache as *chunks* split into
+fixed-size *pages*; a prompt switch retrieves the most relevant pages and installs exactly those
+into the online cache.  Interface, page/span arithmetic, re-rotation plan and soft-failure
+behaviour follow the reference.  What changes is where the bytes move:
+
+* `store` copies the populated cache device-to-device (hot tier) or into page-locked host memory
+  on a side stream, and builds the page index from layer 0's keys with one pooling kernel that
+  removes the temporal rotation on the fly;
+* `retrieve` scores and selects pages in one kernel launch and reads back only the chosen ids;
+* `apply` installs all pages of all layers with one page-copy kernel launch (keys re-rotated in
+  flight, values verbatim), promoting host-resident pages through page-locked async copies on a
+  side stream, clears only the tail of the cache beyond the installed span, and rebuilds the
+  compressed tier with the compress kernel writing straight into the cache slots.
+
+Online cache contract: a list with one dict per transformer block holding `k`, `v`
+(`[B, capacity, H, D]`), scalar tensors `global_end_index`, `local_end_index`, and optionally
+`k_coarse`, `v_coarse`.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _lib
+from .retrieval import page_key_index, prompt_index, score_and_topk, select_top_chunks
+from .rope import rotation_table, temporal_complex_dims
+from .tiering import HKVTierManager
+
+__all__ = ["HKVCache"]
+
+
+class HKVCache:
+    """KV bank with two-stage page retrieval and multi-tier residency.
+
+    Args (reference: cache.py:39-71):
+        frame_seq_length: tokens per latent frame.
+        page_size_frames: frames per page.
+        topk_pages: page budget installed per retrieval.
+        stage1_topk_chunks: how many prompt-similar chunks feed stage 2.
+        cpu_max_chunks: host-resident chunk capacity.
+        nvme_enabled, nvme_dir: enable and locate the NVMe tier.
+        rerope: re-rotate retrieved keys to the cache slots they are replayed at.
+        hbm_max_chunks: (addition) chunks kept on the GPU in front of the host tier.
+    """
+
+    def __init__(self, *, frame_seq_length: int, page_size_frames: int = 8, topk_pages: int = 4,
+                 stage1_topk_chunks: int = 1, cpu_max_chunks: int = 64, nvme_enabled: bool = False,
+                 nvme_dir: Optional[str] = None, rerope: bool = True, hbm_max_chunks: int = 0):
+        self.frame_seq_length = int(frame_seq_length)
+        self.page_size_frames = int(page_size_frames)
+        self.topk_pages = int(topk_pages)
+        self.stage1_topk_chunks = int(stage1_topk_chunks)
+        self.rerope = bool(rerope)
+        self._tier_kwargs = dict(cpu_max_chunks=cpu_max_chunks, nvme_enabled=nvme_enabled, nvme_dir=nvme_dir,
+                                 hbm_max_chunks=hbm_max_chunks)
+        self.reset()
+
+    def reset(self) -> None:
+        """Drop the bank and start a fresh rollout."""
+        self.chunks: List[dict] = []
+        self.prompt_bank: List[torch.Tensor] = []
+        self.tier = HKVTierManager(**self._tier_kwargs)
+
+    def __len__(self) -> int:
+        return len(self.chunks)
+
+    @property
+    def page_tokens(self) -> int:
+        return self.page_size_frames * self.frame_seq_length
+
+    # ------------------------------------------------------------------ store
+    def store(self, kv_cache: Sequence[dict], *, prompt_embeds: torch.Tensor, current_start_frame: int,
+              temporal_freqs: torch.Tensor) -> int:
+        """Write the populated part of the online cache into the bank as a new chunk (cache.py:87-133).
+
+        Returns the new chunk id, or -1 when the cache holds nothing to store.
+        """
+        valid_tokens = int(kv_cache[0]["local_end_index"].item())
+        if valid_tokens <= 0:
+            return -1
+        _lib.require_cuda(kv_cache[0]["k"])
+
+        chunk_id = len(self.chunks)
+        blob = {"k": [], "v": []}
+        for block in kv_cache:
+            blob["k"].append(block["k"][:, :valid_tokens].detach().clone())
+            blob["v"].append(block["v"][:, :valid_tokens].detach().clone())
+
+        page_spans = [(start, min(start + self.page_tokens, valid_tokens))
+                      for start in range(0, valid_tokens, self.page_tokens)]
+        start_frame = int(current_start_frame - valid_tokens // self.frame_seq_length)
+        page_index = page_key_index(blob["k"][0], page_spans, frame_seq_length=self.frame_seq_length,
+                                    start_frame=start_frame, temporal_freqs=temporal_freqs)
+        self.chunks.append({
+            "chunk_id": chunk_id,
+            "valid_tokens": valid_tokens,
+            "page_spans": page_spans,
+            "start_frame": start_frame,
+            "page_index": page_index,
+            "heads": int(kv_cache[0]["k"].shape[2]),
+        })
+        self.prompt_bank.append(prompt_index(prompt_embeds).detach().to(page_index.device))
+        self.tier.put(chunk_id, blob)
+        return chunk_id
+
+    # ------------------------------------------------------------------ retrieve
+    def retrieve(self, *, prompt_embeds: torch.Tensor, query_vec: torch.Tensor,
+                 per_head: bool = False):
+        """Select the pages to install for the incoming prompt (cache.py:135-178).
+
+        Returns `(chunk_id, page_id)` pairs in chronological order.  With `per_head=True` (an
+        addition) the page vectors are scored per head and a list of such lists, one per head,
+        is returned.
+        """
+        if not self.chunks:
+            return []
+        bank = torch.stack(self.prompt_bank, dim=0)
+        candidates = select_top_chunks(prompt_index(prompt_embeds).detach(), bank, self.stage1_topk_chunks)
+
+        owners: List[Tuple[int, int]] = []
+        vectors = []
+        for chunk_id in candidates:
+            page_index = self.chunks[chunk_id].get("page_index")
+            if page_index is None or page_index.numel() == 0:
+                continue
+            vectors.append(page_index)
+            owners.extend((chunk_id, page_id) for page_id in range(page_index.shape[0]))
+        if not owners:
+            return []
+        pool = vectors[0] if len(vectors) == 1 else torch.cat(vectors, dim=0)
+
+        query = query_vec.reshape(-1)
+        if query.shape[0] != pool.shape[1]:
+            raise ValueError(f"query dim {query.shape[0]} does not match page index dim {pool.shape[1]}")
+
+        def chronological(pairs):
+            return sorted(pairs, key=lambda pair: (self.chunks[pair[0]]["start_frame"],
+                                                   self.chunks[pair[0]]["page_spans"][pair[1]][0]))
+
+        if per_head:
+            heads = self.chunks[owners[0][0]].get("heads", 1)
+            _, ids, _ = score_and_topk(query, pool, self.topk_pages, groups=heads)
+            return [chronological([owners[i] for i in row]) for row in ids.tolist()]
+        if self.topk_pages <= 0:
+            return []
+        _, ids, _ = score_and_topk(query, pool, self.topk_pages)
+        return chronological([owners[i] for i in ids[0].tolist()])
+
+    # ------------------------------------------------------------------ apply
+    def apply(self, kv_cache: Sequence[dict], selected_pairs: Sequence[Tuple[int, int]], *,
+              current_start_frame: int, temporal_freqs: torch.Tensor,
+              hsa_modules: Optional[Sequence] = None) -> int:
+        """Install the selected pages into the online cache, replacing its contents (cache.py:180-254).
+
+        Returns the number of tokens installed; 0 (cache untouched) when nothing resolves.
+        """
+        entries, blobs = self._resolve_pages(selected_pairs)
+        if not entries:
+            return 0
+
+        k0 = kv_cache[0]["k"]
+        dev = _lib.require_cuda(k0)
+        bsz, capacity, heads, head_dim = k0.shape
+        dtype = k0.dtype
+
+        budget = capacity
+        installed: List[Tuple[int, int, int]] = []
+        for chunk_id, start, end in entries:
+            if budget <= 0:
+                break
+            take = min(end - start, budget)
+            installed.append((chunk_id, start, start + take))
+            budget -= take
+        total_tokens = sum(end - start for _, start, end in installed)
+
+        frame_moves = self._plan_rerope(installed, current_start_frame) if self.rerope else None
+
+        has_coarse = "k_coarse" in kv_cache[0] and "v_coarse" in kv_cache[0]
+        if has_coarse and hsa_modules is None:
+            raise ValueError(
+                "the online cache carries a compressed tier, so hsa_modules must be supplied so it "
+                "can be rebuilt for the installed pages"
+            )
+
+        if total_tokens > 0:
+            self._install(kv_cache, installed, blobs, frame_moves, temporal_freqs, dev, dtype)
+
+        for block_idx, block in enumerate(kv_cache):
+            block["k"][:, total_tokens:].zero_()
+            block["v"][:, total_tokens:].zero_()
+            if has_coarse:
+                coarse_end = 0
+                if total_tokens > 0:
+                    coarse_end = self._write_coarse(block, hsa_modules[block_idx], total_tokens)
+                block["k_coarse"][:, coarse_end:].zero_()
+                block["v_coarse"][:, coarse_end:].zero_()
+            block["global_end_index"].fill_(current_start_frame * self.frame_seq_length)
+            block["local_end_index"].fill_(total_tokens)
+        return total_tokens
+
+    def _install(self, kv_cache, installed, blobs, frame_moves, temporal_freqs, dev, dtype) -> None:
+        """One page-copy launch for every (layer, page, K|V, batch item)."""
+        k0 = kv_cache[0]["k"]
+        bsz, capacity, heads, head_dim = k0.shape
+        row_elems = heads * head_dim
+        esize = k0.element_size()
+        nt = temporal_complex_dims(head_dim)
+        rot = None
+        if frame_moves is not None:
+            rot = rotation_table(temporal_freqs, [m[1] for m in frame_moves], [m[0] for m in frame_moves], nt)
+
+        main = torch.cuda.current_stream(dev)
+        side = self.tier.side_stream(dev)
+        staged = []          # keeps promoted pages alive until the copy kernel has consumed them
+        promoted = False
+        records = []
+        longest = 1
+        for layer, block in enumerate(kv_cache):
+            for name, rotate in (("k", True), ("v", False)):
+                dst = block[name]
+                if dst.stride(3) != 1 or dst.stride(2) != head_dim or dst.stride(1) != row_elems:
+                    raise ValueError("online cache tensors must be contiguous [B, capacity, H, D]")
+                offset = 0
+                for i, (chunk_id, start, end) in enumerate(installed):
+                    src = blobs[chunk_id][name][layer]
+                    n = end - start
+                    page = src[:, start:end]
+                    if not page.is_cuda:
+                        # cold page: page-locked async copy on the side stream
+                        with torch.cuda.stream(side):
+                            hot = torch.empty(page.shape, dtype=page.dtype, device=dev)
+                            hot.copy_(page, non_blocking=True)
+                        promoted = True
+                        page = hot
+                    if page.dtype != dtype:
+                        page = page.to(dtype)
+                    if page.stride(3) != 1 or page.stride(2) != head_dim:
+                        page = page.contiguous()
+                    staged.append(page)
+                    for b in range(bsz):
+                        records.append(_lib.PageCopy(
+                            page.data_ptr() + b * page.stride(0) * esize,
+                            dst.data_ptr() + (b * dst.stride(0) + offset * row_elems) * esize,
+                            page.stride(1), row_elems, n,
+                            i if (rotate and rot is not None) else -1))
+                    longest = max(longest, n)
+                    offset += n
+        if promoted:
+            main.wait_stream(side)
+        arr = (_lib.PageCopy * len(records))(*records)
+        dev_records = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev)
+        rot_dev = torch.from_numpy(np.ascontiguousarray(rot)).to(dev) if rot is not None else None
+        _lib.check(_lib.lib().wa_hkv_gather_pages(
+            dev_records.data_ptr(), len(records), longest, row_elems, head_dim, _lib.dtype_code(dtype),
+            _lib.ptr(rot_dev), nt, main.cuda_stream))
+        for page in staged:
+            if page.is_cuda:
+                page.record_stream(main)
+
+    def _resolve_pages(self, selected_pairs):
+        """Turn `(chunk, page)` pairs into token spans, skipping anything unresolvable (cache.py:256-271)."""
+        entries, blobs = [], {}
+        for chunk_id, page_id in selected_pairs:
+            if not (0 <= chunk_id < len(self.chunks)):
+                continue
+            spans = self.chunks[chunk_id]["page_spans"]
+            if not (0 <= page_id < len(spans)):
+                continue
+            if chunk_id not in blobs:
+                blob = self.tier.get(chunk_id)
+                if blob is None:
+                    continue
+                blobs[chunk_id] = blob
+            start, end = spans[page_id]
+            entries.append((chunk_id, start, end))
+        return entries, blobs
+
+    def _plan_rerope(self, installed, current_start_frame):
+        """Frame each installed page moves from and to (cache.py:273-287).
+
+        Installed pages occupy consecutive frames ending at `current_start_frame`.
+        """
+        moves = []
+        base = current_start_frame - sum(e - s for _, s, e in installed) // self.frame_seq_length
+        offset = 0
+        for chunk_id, start, end in installed:
+            orig_frame = self.chunks[chunk_id]["start_frame"] + start // self.frame_seq_length
+            moves.append((orig_frame, base + offset // self.frame_seq_length))
+            offset += end - start
+        return moves
+
+    @staticmethod
+    def _write_coarse(block: dict, hsa, total_tokens: int) -> int:
+        """Rebuild the compressed tier from the tokens installed at cache offset 0 (cache.py:289-299).
+
+        The compress kernel writes directly into the cache's compressed slots.
+        """
+        k, v = block["k"][:, :total_tokens], block["v"][:, :total_tokens]
+        dev = k.device
+        bsz, _, heads, head_dim = k.shape
+        coarse_start, coarse_end = hsa.token_range_to_coarse(0, int(total_tokens))
+        kc, vc = block["k_coarse"], block["v_coarse"]
+        if kc.dtype != k.dtype or vc.dtype != k.dtype or kc.stride() != vc.stride() or kc.stride(3) != 1:
+            k_new, v_new = hsa.compress_kv_cache(k, v)
+            kc[:, coarse_start:coarse_end] = k_new.to(kc.dtype)
+            vc[:, coarse_start:coarse_end] = v_new.to(vc.dtype)
+            return coarse_end
+        if coarse_end > kc.shape[1]:
+            raise ValueError("compressed cache is too small for the installed pages")
+        pk = hsa.k_proj_mat.detach().to(device=dev).contiguous()
+        pv = hsa.v_proj_mat.detach().to(device=dev, dtype=pk.dtype).contiguous()
+        _lib.check(_lib.lib().wa_compress_kv(
+            _lib.t4_blhd(k), _lib.t4_blhd(v), _lib.t4_blhd(kc), _lib.t4_blhd(vc), bsz, int(total_tokens), heads,
+            head_dim, hsa.proj_segment_len, hsa.block_size, pk.data_ptr(), pv.data_ptr(), _lib.dtype_code(pk.dtype),
+            pk.shape[0], pk.shape[1], _lib.stream_ptr(dev)))
+        return coarse_end

@@ -1,0 +1,214 @@
+"""Multi-GPU execution of the HSA forward on one NVSwitch box.
+
+The reference runs HSA on a single device.  Two shardings are provided, both one process per GPU
+over `torch.distributed` (NCCL on GPUs; the planning and exchange logic also runs under gloo):
+
+* **head split** (2 / 4 GPUs): every quantity in HSA is per head (pooling, block map, the Gini
+  mean over (batch, query block), both softmaxes; the projections and the gate are shared and
+  replicated), so a rank runs the ordinary forward on its heads.  No data-path collective is
+  needed; `gather_heads` all-gathers the outputs for a consumer that wants every head.
+* **KV shard** (8 GPUs; 12 heads do not divide by 8): the key range is cut at attention-block
+  boundaries.  Ranks all-gather their pooled keys, take the identical global routing decision,
+  attend to the selected blocks and compressed slots they own, and all-gather per-branch partial
+  outputs with log-sum-exp normalisers that `merge_partials` combines before the gate.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .hsa import branches
+from .hsa.routing import block_attention_map, block_mean_pool, build_block_routing  # noqa: F401
+
+__all__ = ["plan_head_split", "plan_kv_shards", "local_selection", "gather_heads", "all_gather_cat",
+           "merge_partials", "hsa_attention_head_split", "hsa_attention_kv_sharded"]
+
+merge_partials = branches.merge_partials
+
+
+# --------------------------------------------------------------------------- planning (pure host logic)
+def plan_head_split(num_heads: int, world: int, cost_per_head: Optional[Sequence[float]] = None) -> List[List[int]]:
+    """Assign heads to ranks: longest-processing-time greedy on `cost_per_head` (e.g. k_h), sorted ids per rank.
+
+    With no costs the split is contiguous and even.  Every rank receives `num_heads // world` or
+    one more head.
+    """
+    if world <= 0 or num_heads < world:
+        raise ValueError(f"cannot split {num_heads} heads over {world} ranks")
+    if cost_per_head is None:
+        base, extra = divmod(num_heads, world)
+        out, h = [], 0
+        for r in range(world):
+            n = base + (1 if r < extra else 0)
+            out.append(list(range(h, h + n)))
+            h += n
+        return out
+    if len(cost_per_head) != num_heads:
+        raise ValueError("cost_per_head must have one entry per head")
+    cap = math.ceil(num_heads / world)
+    loads = [0.0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for h in sorted(range(num_heads), key=lambda i: (-float(cost_per_head[i]), i)):
+        r = min((r for r in range(world) if len(out[r]) < cap), key=lambda r: (loads[r], r))
+        out[r].append(h)
+        loads[r] += float(cost_per_head[h])
+    return [sorted(x) for x in out]
+
+
+def plan_kv_shards(kv_len: int, block_size: int, world: int, page_tokens: int = 0) -> List[Tuple[int, int]]:
+    """Contiguous token ranges `[lo, hi)` per rank, cut at attention-block boundaries.
+
+    With `page_tokens > 0` each cut is the block boundary nearest to a page boundary, so a shard
+    holds (almost) whole pages even though pages and blocks do not align.
+    """
+    if world <= 0:
+        raise ValueError("world must be positive")
+    n_blocks = math.ceil(kv_len / block_size)
+    cuts = [0]
+    for r in range(1, world):
+        target = kv_len * r / world
+        if page_tokens > 0:
+            target = round(target / page_tokens) * page_tokens
+        blk = min(max(int(round(target / block_size)), cuts[-1] // block_size), n_blocks)
+        cuts.append(blk * block_size)
+    cuts.append(kv_len)
+    return [(cuts[r], max(cuts[r], cuts[r + 1])) for r in range(world)]
+
+
+def local_selection(index: torch.Tensor, num: torch.Tensor, block_lo: int, block_hi: int):
+    """Restrict a global routing `(index, num)` to the key blocks `[block_lo, block_hi)`.
+
+    Returns `(local_index int32 [..., Nkv_local], local_num int32 [...])`, ids rebased to the
+    shard and listed in ascending order.  The union over a partition of the block range is the
+    global selection.
+    """
+    nkv = index.shape[-1]
+    slots = torch.arange(nkv, device=index.device).view(*([1] * (index.dim() - 1)), nkv)
+    selected = slots < num.unsqueeze(-1).long()
+    ids = index.long().clamp(0, nkv - 1)
+    owned = selected & (ids >= block_lo) & (ids < block_hi)
+    width = max(block_hi - block_lo, 1)
+    hits = torch.zeros(index.shape[:-1] + (width,), dtype=torch.int32, device=index.device)
+    hits.scatter_add_(-1, (ids - block_lo).clamp(0, width - 1), owned.to(torch.int32))
+    member = hits > 0
+    # duplicates in the global list (allowed by the reference) collapse to one visit here
+    local_num = member.sum(-1).to(torch.int32)
+    order = torch.argsort((~member).to(torch.int8), dim=-1, stable=True)
+    return order.to(torch.int32).contiguous(), local_num.contiguous()
+
+
+# --------------------------------------------------------------------------- exchange
+def all_gather_cat(t: torch.Tensor, dim: int, group=None, sizes: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """All-gather tensors that may differ in `dim` (sizes per rank given) and concatenate along it."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return t
+    t = t.contiguous()
+    if sizes is None:
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t, group=group)
+        return torch.cat(parts, dim=dim)
+    longest = max(sizes)
+    pad_shape = list(t.shape)
+    pad_shape[dim] = longest
+    padded = torch.zeros(pad_shape, dtype=t.dtype, device=t.device)
+    padded.narrow(dim, 0, t.shape[dim]).copy_(t)
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([p.narrow(dim, 0, n) for p, n in zip(parts, sizes)], dim=dim)
+
+
+def gather_heads(out_local: torch.Tensor, head_plan: List[List[int]], group=None) -> torch.Tensor:
+    """All-gather `[B, L, H_local, D]` head-split outputs into `[B, L, H, D]` in head order."""
+    sizes = [len(h) for h in head_plan]
+    cat = all_gather_cat(out_local, 2, group=group, sizes=sizes)
+    order = [h for heads in head_plan for h in heads]
+    inverse = torch.empty(len(order), dtype=torch.long)
+    inverse[torch.tensor(order)] = torch.arange(len(order))
+    return cat.index_select(2, inverse.to(cat.device))
+
+
+# --------------------------------------------------------------------------- forwards
+def hsa_attention_head_split(hsa_module, q_local, k_local, v_local, *, k_coarse=None, v_coarse=None,
+                             topk_local=None, head_plan=None, group=None, gather: bool = True):
+    """Head-split forward: each rank holds its heads of q/k/v (and of the compressed cache)."""
+    from .hsa.attention import hsa_attention
+    out = hsa_attention(
+        q_local, k_local, v_local, k_coarse=k_coarse, v_coarse=v_coarse,
+        k_proj_mat=hsa_module.k_proj_mat, v_proj_mat=hsa_module.v_proj_mat, gate_lin=hsa_module.gate_lin,
+        block_size=hsa_module.block_size, tau_min=hsa_module.tau_min, tau_max=hsa_module.tau_max,
+        proj_segment_len=hsa_module.proj_segment_len, topk_per_head=topk_local)
+    if gather and head_plan is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        return gather_heads(out, head_plan, group=group)
+    return out
+
+
+def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local, *, kv_len: int,
+                             shards: List[Tuple[int, int]], topk_per_head=None, group=None):
+    """KV-sharded forward.  `q` is replicated; `k_local`/`v_local` hold this rank's token range.
+
+    `kc_local`/`vc_local` are the compressed slots of the segments this rank owns.  Returns the
+    full `[B, Lq, H, D]` output on every rank.
+    """
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    bs = hsa_module.block_size
+    bsz, q_len, heads, head_dim = q.shape
+    lo, hi = shards[rank]
+    n_local = hi - lo
+
+    # routing: pooled keys are exchanged, the decision is taken identically everywhere
+    nq = math.ceil(q_len / bs)
+    q_pooled = _pool_blhd(q, bs)
+    k_pooled_local = _pool_blhd(k_local, bs) if n_local > 0 else q_pooled.new_zeros((bsz, heads, 0, head_dim))
+    blocks_per_rank = [math.ceil((b - a) / bs) for a, b in shards]
+    k_pooled = all_gather_cat(k_pooled_local, 2, group=group, sizes=blocks_per_rank) if world > 1 else k_pooled_local
+    routing = build_block_routing(block_attention_map(q_pooled, k_pooled), hsa_module.tau_min, hsa_module.tau_max,
+                                  topk_per_head=topk_per_head)
+    block_lo = sum(blocks_per_rank[:rank])
+    index_l, num_l = local_selection(routing.index, routing.num, block_lo, block_lo + blocks_per_rank[rank])
+
+    # partials over what this rank owns
+    if n_local > 0:
+        o_s, l_s = branches.sparse_branch(q, k_local, v_local, index_l, num_l, bs, kv_len=n_local)
+    else:
+        o_s = q.new_zeros((bsz, q_len, heads, head_dim), dtype=torch.float32)
+        l_s = q.new_full((bsz, heads, q_len), float("-inf"), dtype=torch.float32)
+    if kc_local is not None and kc_local.shape[1] > 0:
+        o_l, l_l = branches.linear_branch(q, kc_local, vc_local)
+    else:
+        o_l = torch.zeros_like(o_s)
+        l_l = torch.full_like(l_s, float("-inf"))
+
+    # exchange + merge (rows ordered [B, H, Lq] to match the normalisers)
+    def rows(o):
+        return o.permute(0, 2, 1, 3).reshape(1, bsz * heads * q_len, head_dim)
+
+    packed_o = torch.cat([rows(o_s), rows(o_l)], dim=1)                    # [1, 2R, D]
+    packed_l = torch.cat([l_s.reshape(1, -1), l_l.reshape(1, -1)], dim=1)  # [1, 2R]
+    if world > 1:
+        packed_o = all_gather_cat(packed_o, 0, group=group)
+        packed_l = all_gather_cat(packed_l, 0, group=group)
+    merged, _ = merge_partials(packed_o, packed_l)
+    r = bsz * heads * q_len
+    sparse = merged[:r].view(bsz, heads, q_len, head_dim).permute(0, 2, 1, 3)
+    linear = merged[r:].view(bsz, heads, q_len, head_dim).permute(0, 2, 1, 3)
+    sparse = sparse.to(torch.bfloat16).contiguous()       # the reference stores the sparse branch in bf16
+    return branches.gate_combine(q, sparse, linear.contiguous(), hsa_module.gate_lin,
+                                 round_bf16=q.dtype == torch.bfloat16)
+
+
+def _pool_blhd(x: torch.Tensor, block_size: int) -> torch.Tensor:
+    """Pool an unpadded `[B, L, H, D]` tensor -> float32 `[B, H, Nb, D]` (one C-ABI call)."""
+    from . import _lib
+    dev = _lib.require_cuda(x)
+    bsz, length, heads, head_dim = x.shape
+    nb = math.ceil(length / block_size)
+    pooled = torch.empty((bsz, heads, nb, head_dim), device=dev, dtype=torch.float32)
+    x = x if x.stride(-1) == 1 else x.contiguous()
+    _lib.check(_lib.lib().wa_pool_blocks(_lib.t4_blhd(x), bsz, length, heads, head_dim, block_size,
+                                         pooled.data_ptr(), _lib.stream_ptr(dev)))
+    return pooled
