@@ -158,6 +158,12 @@ typedef struct wa_hsa_params {
 size_t wa_hsa_workspace_bytes(const wa_hsa_params *p);
 /* Returns through *used_tuned (may be NULL) whether the tcgen05 kernel ran. */
 int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *stream);
+/* Failure detection for the tcgen05 kernel.  Every wait inside it is bounded; a wait that runs
+ * out records its site (1..10) in the workspace, the kernel releases its tensor memory and
+ * returns.  wa_hsa_status waits for `stream` and copies that flag to *status (0 = the last tuned
+ * launch on this workspace completed normally).  `p` must be the params of that launch.  The
+ * reference has no counterpart (its kernels cannot time out). */
+int wa_hsa_status(const wa_hsa_params *p, int *status, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * HKV retrieval -- pipeline/hkv/retrieval.py, rope.py, cache.py

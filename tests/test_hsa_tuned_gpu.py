@@ -1,0 +1,130 @@
+"""The tcgen05 fused kernel (bf16, head_dim 128, 128-token blocks) against the oracle and the SIMT kernels.
+
+Routing ids/counts are produced by the same routing kernels on both paths and must be identical;
+outputs meet max-abs 2e-2 / mean-rel 1e-2 against the oracle (the tolerance BASELINE states) and
+are much closer to the library's own generic path.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hsa_oracle as O
+from tests.helpers import attention_error, dev, to_gpu, to_np
+
+pytestmark = pytest.mark.gpu
+MAX_ABS, MEAN_REL = 2e-2, 1e-2
+D = 128
+
+
+@pytest.fixture(scope="module")
+def wa():
+    import worldattention_b200 as pkg
+    return pkg
+
+
+def _draw(rng, shape, scale):
+    return O.bf16_round((rng.standard_normal(shape) * scale).astype(np.float32))
+
+
+def _proj(rank, seg, bs, rng):
+    e = np.zeros((rank, seg), np.float32)
+    for r in range(rank):
+        lo, hi = r * bs, min((r + 1) * bs, seg)
+        if hi > lo:
+            e[r, lo:hi] = 1.0 / (hi - lo)
+    return O.bf16_round(e + 0.002 * rng.standard_normal(e.shape).astype(np.float32))
+
+
+def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=True, coarse_len=None):
+    rng = np.random.default_rng(seed)
+    q = _draw(rng, (bsz, q_len, heads, D), scale)
+    k = _draw(rng, (bsz, kv_len, heads, D), scale)
+    v = _draw(rng, (bsz, kv_len, heads, D), 1.0)
+    ek = _proj(math.ceil(seg / 128), seg, 128, rng)
+    gw = (rng.standard_normal((D, D)) * 0.05).astype(np.float32)
+    gb = (rng.standard_normal((D,)) * 0.3).astype(np.float32)
+    kc = vc = None
+    if coarse_len:
+        kc = _draw(rng, (bsz, coarse_len, heads, D), scale)
+        vc = _draw(rng, (bsz, coarse_len, heads, D), 1.0)
+    lin = None
+    if gate:
+        lin = torch.nn.Linear(D, D).to(dev())
+        with torch.no_grad():
+            lin.weight.copy_(to_gpu(gw)); lin.bias.copy_(to_gpu(gb))
+    tk = None if topk is None else torch.tensor(topk, dtype=torch.int32)
+    kwargs = dict(k_proj_mat=to_gpu(ek, "bf16"), v_proj_mat=to_gpu(ek, "bf16"), gate_lin=lin, block_size=128,
+                  proj_segment_len=seg, topk_per_head=tk, return_routing=True)
+    if coarse_len:
+        kwargs.update(k_coarse=to_gpu(kc, "bf16"), v_coarse=to_gpu(vc, "bf16"))
+    args = [to_gpu(x, "bf16") for x in (q, k, v)]
+    out, (index, num, thr, used) = wa.hsa.hsa_attention(*args, check_status=True, **kwargs)
+    assert used, "the tcgen05 kernel did not run"
+    ref, (index_g, num_g, thr_g, used_g) = wa.hsa.hsa_attention(*args, force_generic=True, **kwargs)
+    assert not used_g
+    assert torch.equal(index, index_g) and torch.equal(num, num_g) and torch.equal(thr, thr_g)
+    # bf16 rounding of the gate weights is the only arithmetic the generic path does not share
+    gw_used = O.bf16_round(gw) if gate else None
+    want, parts = O.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=ek, v_proj_mat=ek,
+                                  gate_weight=gw_used, gate_bias=gb if gate else None, block_size=128,
+                                  proj_segment_len=seg, dtype="bf16", topk_per_head=topk, return_parts=True)
+    assert np.array_equal(to_np(num), parts["num"])
+    max_abs, mean_rel = attention_error(to_np(out), want)
+    assert max_abs < MAX_ABS and mean_rel < MEAN_REL, ("vs oracle", max_abs, mean_rel)
+    max_abs_g, mean_rel_g = attention_error(to_np(out), to_np(ref))
+    assert max_abs_g < MAX_ABS and mean_rel_g < MEAN_REL, ("vs generic", max_abs_g, mean_rel_g)
+    return to_np(out), parts
+
+
+def test_small_ragged_shapes_fixed_topk(wa):
+    _run_case(wa, seed=1, bsz=1, heads=2, q_len=300, kv_len=1170, seg=390, topk=[3, 10], scale=1.0 / math.sqrt(D))
+
+
+def test_cumulative_mass_routing_batch_two(wa):
+    _run_case(wa, seed=2, bsz=2, heads=3, q_len=520, kv_len=2000, seg=500, topk=None, scale=0.5)
+
+
+def test_supplied_compressed_cache_spanning_several_tiles(wa):
+    _run_case(wa, seed=3, bsz=1, heads=4, q_len=128, kv_len=900, seg=300, topk=[1, 8, 2, 5], scale=0.3, coarse_len=300)
+
+
+def test_empty_selection_gives_the_linear_term_only(wa):
+    out, parts = _run_case(wa, seed=4, bsz=1, heads=2, q_len=200, kv_len=700, seg=350, topk=[0, 4], scale=0.3)
+    assert np.count_nonzero(parts["sparse"][:, :, 0]) == 0
+    want = O.as_dtype(parts["linear"][:, :, 0] * parts["gate"][:, :, 0], "bf16")
+    assert np.max(np.abs(out[:, :, 0] - want)) < MAX_ABS
+
+
+def test_no_gate_module_uses_sigmoid_of_q(wa):
+    _run_case(wa, seed=5, bsz=1, heads=2, q_len=256, kv_len=512, seg=256, topk=[2, 4], scale=0.4, gate=False)
+
+
+def test_large_logits_exercise_the_running_max_rescale(wa):
+    _run_case(wa, seed=6, bsz=1, heads=2, q_len=256, kv_len=2048, seg=512, topk=[16, 9], scale=3.0)
+
+
+def test_config2_shape_head_adaptive_topk(wa):
+    """BASELINE config 2 at full size: the property checked is agreement with the SIMT path of this library."""
+    heads, q_len, kv_len, seg = 12, 4680, 32760, 1560
+    g = torch.Generator().manual_seed(1)
+    topk = torch.tensor([4, 8, 16, 32])[torch.randint(0, 4, (heads,), generator=g)].to(torch.int32)
+    torch.manual_seed(1)
+    q = (torch.randn(1, q_len, heads, D, device=dev()) / math.sqrt(D)).bfloat16()
+    k = (torch.randn(1, kv_len, heads, D, device=dev()) / math.sqrt(D)).bfloat16()
+    v = (torch.randn(1, kv_len, heads, D, device=dev()) / math.sqrt(D)).bfloat16()
+    hsa = wa.hsa.HSAAttention(heads, D, block_size=128, proj_segment_len=seg).to(dev())
+    wa.hsa_stage.init_hsa_parameters(hsa)
+    with torch.no_grad():
+        hsa.gate_lin.weight.normal_(0, 0.02)
+        kc, vc = hsa.compress_kv_cache(k, v)
+    kwargs = dict(k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
+                  block_size=128, proj_segment_len=seg, topk_per_head=topk, return_routing=True)
+    out, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, check_status=True, **kwargs)
+    ref, (index_g, num_g, _, _) = wa.hsa.hsa_attention(q, k, v, force_generic=True, **kwargs)
+    assert used and torch.equal(index, index_g) and torch.equal(num, num_g)
+    assert torch.equal(num[0, :, 0].cpu(), topk)
+    max_abs, mean_rel = attention_error(to_np(out), to_np(ref))
+    assert max_abs < MAX_ABS and mean_rel < MEAN_REL, (max_abs, mean_rel)
+    assert torch.isfinite(out).all()

@@ -66,6 +66,7 @@ SIGNATURES = {
     "wa_merge_partials": [_vp, _vp, _i, _i64, _i, _vp, _vp, _vp],
     "wa_hsa_workspace_bytes": [C.POINTER(HsaParams)],
     "wa_hsa_forward": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
+    "wa_hsa_status": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
     "wa_hkv_page_centroids": [_T4P, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "wa_hkv_score_topk": [_vp, _vp, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp],
     "wa_hkv_gather_pages": [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp],

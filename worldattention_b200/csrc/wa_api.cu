@@ -129,6 +129,20 @@ extern "C" size_t wa_hsa_workspace_bytes(const wa_hsa_params *p) {
     return plan(p).total;
 }
 
+extern "C" int wa_hsa_status(const wa_hsa_params *p, int *status, void *stream_) {
+    int rc = validate(p);
+    if (rc) return rc;
+    WA_REQUIRE(status && p->workspace, WA_ERR_ARG, "wa_hsa_status: null pointer");
+    const Workspace w = plan(p);
+    WA_REQUIRE(p->workspace_bytes >= w.total, WA_ERR_WORKSPACE, "wa_hsa_status: workspace too small");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    cudaError_t e = cudaMemcpyAsync(status, (char *)p->workspace + w.tuned + hsa_sm100_status_offset(p), sizeof(int),
+                                    cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail((int)e, "wa_hsa_status: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *stream_) {
     const char *what = "wa_hsa_forward";
     int rc = validate(p);

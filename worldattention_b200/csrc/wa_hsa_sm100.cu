@@ -1,10 +1,728 @@
-// Placeholder until the tcgen05 kernel lands: reports every shape as unsupported.
+// Fused HSA forward for sm_100a: block-sparse softmax branch, compressed ("linear") branch, gate
+// GEMM and combine in one persistent, warp-specialised kernel.
+//
+// Replaces the reference's Triton `_fwd_kernel` (wan/modules/hsa/block_sparse_triton.py:67-139)
+// plus `_linear_branch` and the gate/addcmul epilogue (wan/modules/hsa/attention.py:113-118,
+// 246-259) for bf16, head_dim 128, 128-token blocks.
+//
+// Work item = (batch, head, 128-row query block).  Per item the CTA runs a chain of 128x128 tiles:
+//   sparse:  for each selected key block   S = Q K^T -> online softmax -> O += P V
+//   linear:  for each 128 compressed slots  S = Q Kc^T -> online softmax -> O += P Vc
+//   gate:    S = Q Wg^T ; out = O_sparse/l_s + sigmoid(S + b) * O_linear/l_l
+// Data path: TMA (cp.async.bulk.tensor, 128-byte swizzle, one consumer CTA per copy) -> shared memory ->
+// tcgen05.mma with the S and O accumulators in tensor memory; P goes back to tensor memory as
+// bf16 and is the A operand of the PV product.  Warp 0 issues TMA, warp 1 issues MMA, warps 2-5
+// (one thread per query row) do softmax and the epilogue.  Two CTAs share an SM (256 tensor-memory
+// columns and ~97 KB shared memory each) so one CTA's softmax overlaps the other's MMAs.
+//
+// Every mbarrier wait is bounded (about two seconds); on expiry the kernel raises a flag in
+// global memory, all roles leave their loops, tensor memory is released and the kernel returns.
+#include <cuda.h>
+
 #include "wa_internal.cuh"
+
 namespace wa {
-size_t hsa_sm100_workspace_bytes(const wa_hsa_params *) { return 0; }
-bool hsa_sm100_supported(const wa_hsa_params *, int, const wa_tensor4 *, const wa_tensor4 *) { return false; }
-int hsa_sm100_launch(const wa_hsa_params *, int, const wa_tensor4 *, const wa_tensor4 *, const int32_t *,
-                     const int32_t *, int, int, void *, cudaStream_t) {
-    return fail(WA_ERR_UNSUPPORTED, "tcgen05 kernel not built");
+namespace sm100 {
+
+constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
+constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
+constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
+constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
+constexpr int TMEM_COLS = 256;       // S: columns [0,128), O: [128,256)
+constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long WAIT_CYCLES = 4000000000ll;
+
+struct Params {
+    int B, H, Lq, Lkv, Lc, Nq, Nkv;
+    int n_items;
+    const int32_t *index;   // [B,H,Nq,Nkv]
+    const int32_t *num;     // [B,H,Nq]
+    const int32_t *order;   // [n_items] work order (heaviest first)
+    int *work_counter;
+    int *error_flag;
+    __nv_bfloat16 *out;
+    long long osb, osl, osh;
+    const float *gate_bias;   // [128] or null
+    int has_gate;             // 0: gate = sigmoid(q)
+    const __nv_bfloat16 *q;   // for the no-gate path
+    long long qsb, qsl, qsh;
+    float scale_log2;         // D^-1/2 * log2(e)
+    // partial-output mode (KV-sharded multi-GPU): normalised per-branch outputs + natural-log LSE
+    float *part_sparse, *part_linear;   // [B, Lq, H, 128] float32 or null
+    float *lse_sparse, *lse_linear;     // [B, H, Lq]
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false after the abort flag is raised or the time budget is spent.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *error_flag,
+                                          int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicExch(error_flag, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+
+#define TMEM_LD32(taddr, r)                                                                                          \
+    asm volatile(                                                                                                    \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                    \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                    \
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                    \
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),            \
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),      \
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),    \
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])     \
+        : "r"(taddr) : "memory")
+
+#define TMEM_ST16(taddr, r)                                                                                          \
+    asm volatile(                                                                                                    \
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                              \
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                                   \
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),        \
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory")
+
+#define TMEM_ST32(taddr, r)                                                                                          \
+    asm volatile(                                                                                                    \
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                                              \
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "                                   \
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"                           \
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),        \
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),              \
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),            \
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory")
+
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle.  `lbo`, `sbo` in bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;   // 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: bf16 x bf16 -> f32, M = N = 128; `b_mn_major` for the V operand.
+__host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major) {
+    return (1u << 4)                 // D format f32
+           | (1u << 7)               // A format bf16
+           | (1u << 10)              // B format bf16
+           | ((b_mn_major ? 1u : 0u) << 16)
+           | ((uint32_t)(TILE >> 3) << 17)
+           | ((uint32_t)(TILE >> 4) << 24);
+}
+
+struct Barriers {
+    uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done, o_free;
+    uint32_t tmem_base;
+    int item;
+    int abort_flag;
+};
+
+// ---- the kernel ----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 2)
+hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
+                     const __grid_constant__ CUtensorMap tm_vc, const __grid_constant__ CUtensorMap tm_w,
+                     const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem, *k_s = smem + TILE_BYTES, *v_s = smem + 2 * TILE_BYTES;
+    Barriers *bar = reinterpret_cast<Barriers *>(smem + 3 * TILE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int *abort_flag = &bar->abort_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar->q_full, 1);
+        mbar_init(&bar->k_full, 1);
+        mbar_init(&bar->k_empty, 1);
+        mbar_init(&bar->v_full, 1);
+        mbar_init(&bar->v_empty, 1);
+        mbar_init(&bar->s_full, 1);
+        mbar_init(&bar->p_full, 128);
+        mbar_init(&bar->o_done, 1);
+        mbar_init(&bar->o_free, 128);
+        bar->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
+                     "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bar->tmem_base;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + TILE;
+
+    // phase parities, carried across work items
+    // ("empty" parities start at 1: a fresh barrier counts as already released)
+    uint32_t ph_q = 0, ph_kf = 0, ph_ke = 1, ph_vf = 0, ph_ve = 1, ph_s = 0, ph_p = 0, ph_od = 0, ph_of = 0;
+    const int lin_tiles = (p.Lc + TILE - 1) / TILE;
+
+    while (true) {
+        if (threadIdx.x == 0) bar->item = atomicAdd(p.work_counter, 1);
+        __syncthreads();
+        const int slot = bar->item;
+        if (slot >= p.n_items || *abort_flag) break;
+        const int item = p.order[slot];
+        const int qb = item % p.Nq;
+        const int h = (item / p.Nq) % p.H;
+        const int b = item / (p.Nq * p.H);
+        const long long meta = item;   // (b*H + h)*Nq + qb
+        const int n_sel = max(0, min(p.num[meta], p.Nkv));
+        const int32_t *ids = p.index + meta * (long long)p.Nkv;
+        const int n_tiles = n_sel + lin_tiles + 1;   // sparse, linear, gate
+
+        if (warp == 0) {
+            // ================= TMA producer =================
+            if (lane == 0) {
+                mbar_expect_tx(&bar->q_full, TILE_BYTES);
+                tma_load_4d(q_s, &tm_q, &bar->q_full, 0, h, qb * TILE, b);
+                tma_load_4d(q_s + HALF_BYTES, &tm_q, &bar->q_full, 64, h, qb * TILE, b);
+                bool ok = true;
+                for (int t = 0; t < n_tiles && ok; ++t) {
+                    // K-type operand of tile t: the buffer is free once the previous product that read it completed
+                    ok = mbar_wait(&bar->k_empty, ph_ke, abort_flag, p.error_flag, 1);
+                    if (!ok) break;
+                    ph_ke ^= 1u;
+                    mbar_expect_tx(&bar->k_full, TILE_BYTES);
+                    if (t < n_sel) {
+                        const int id = max(0, min(ids[t], p.Nkv - 1));
+                        tma_load_4d(k_s, &tm_k, &bar->k_full, 0, h, id * TILE, b);
+                        tma_load_4d(k_s + HALF_BYTES, &tm_k, &bar->k_full, 64, h, id * TILE, b);
+                    } else if (t < n_sel + lin_tiles) {
+                        const int c = (t - n_sel) * TILE;
+                        tma_load_4d(k_s, &tm_kc, &bar->k_full, 0, h, c, b);
+                        tma_load_4d(k_s + HALF_BYTES, &tm_kc, &bar->k_full, 64, h, c, b);
+                    } else {
+                        tma_load_2d(k_s, &tm_w, &bar->k_full, 0, 0);
+                        tma_load_2d(k_s + HALF_BYTES, &tm_w, &bar->k_full, 64, 0);
+                    }
+                    if (t < n_sel + lin_tiles) {
+                        ok = mbar_wait(&bar->v_empty, ph_ve, abort_flag, p.error_flag, 2);
+                        if (!ok) break;
+                        ph_ve ^= 1u;
+                        mbar_expect_tx(&bar->v_full, TILE_BYTES);
+                        if (t < n_sel) {
+                            const int id = max(0, min(ids[t], p.Nkv - 1));
+                            tma_load_4d(v_s, &tm_v, &bar->v_full, 0, h, id * TILE, b);
+                            tma_load_4d(v_s + HALF_BYTES, &tm_v, &bar->v_full, 64, h, id * TILE, b);
+                        } else {
+                            const int c = (t - n_sel) * TILE;
+                            tma_load_4d(v_s, &tm_vc, &bar->v_full, 0, h, c, b);
+                            tma_load_4d(v_s + HALF_BYTES, &tm_vc, &bar->v_full, 64, h, c, b);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ================= MMA issuer =================
+            if (lane == 0) {
+                constexpr uint32_t IDESC_QK = instr_desc(false), IDESC_PV = instr_desc(true);
+                bool ok = mbar_wait(&bar->q_full, ph_q, abort_flag, p.error_flag, 3);
+                const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+                for (int t = 0; t < n_tiles && ok; ++t) {
+                    ok = mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4);
+                    if (!ok) break;
+                    ph_kf ^= 1u;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                        mma_ss(tmem_s, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), IDESC_QK,
+                               kk > 0);
+                    }
+                    tc_commit(&bar->k_empty);
+                    tc_commit(&bar->s_full);
+                    if (t < n_sel + lin_tiles) {
+                        const bool first = (t == 0) || (t == n_sel);
+                        ok = mbar_wait(&bar->p_full, ph_p, abort_flag, p.error_flag, 5);
+                        if (!ok) break;
+                        ph_p ^= 1u;
+                        ok = mbar_wait(&bar->v_full, ph_vf, abort_flag, p.error_flag, 6);
+                        if (!ok) break;
+                        ph_vf ^= 1u;
+                        if (first && t > 0) {
+                            // the sparse accumulator must have been read out before the linear branch reuses it
+                            ok = mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7);
+                            if (!ok) break;
+                            ph_of ^= 1u;
+                        }
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk)
+                            mma_ts(tmem_o, tmem_s + kk * 8, smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), IDESC_PV,
+                                   !(first && kk == 0));
+                        tc_commit(&bar->v_empty);
+                        const bool last = (t == n_sel - 1) || (t == n_sel + lin_tiles - 1);
+                        if (last) tc_commit(&bar->o_done);
+                    }
+                }
+            }
+            ph_q ^= 1u;
+        } else {
+            // ================= softmax / epilogue: one thread per query row =================
+            const int row = (warp & 3) * 32 + lane;
+            const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
+            const int token = qb * TILE + row;
+            const bool row_ok = token < p.Lq;
+            __nv_bfloat16 *out_row = p.out + (long long)b * p.osb + (long long)token * p.osl + (long long)h * p.osh;
+            const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE;
+            const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
+            bool ok = true;
+            float inv_l_lin = 0.f;
+
+            for (int phase = 0; phase < 2 && ok; ++phase) {
+                const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_sel + lin_tiles;
+                float m_used = -INFINITY, l = 0.f;
+                for (int t = t0; t < t1 && ok; ++t) {
+                    int valid;
+                    if (phase == 0) {
+                        const int id = max(0, min(ids[t], p.Nkv - 1));
+                        valid = min(TILE, p.Lkv - id * TILE);
+                    } else {
+                        valid = min(TILE, p.Lc - (t - n_sel) * TILE);
+                    }
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full, ph_s, abort_flag, p.error_flag, 8));
+                    if (!ok) break;
+                    ph_s ^= 1u;
+                    tc_fence_after();
+                    uint32_t r[32];
+                    // pass 1: row maximum over the valid columns
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        TMEM_LD32(tmem_s + lane_addr + c * 32, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c * 32 + j < valid) mx = fmaxf(mx, __uint_as_float(r[j]));
+                    }
+                    mx *= p.scale_log2;
+                    // lazy rescale: only when the running maximum grows by more than 2^8
+                    float m_new = m_used;
+                    const bool grow = mx > m_used + 8.0f;
+                    if (grow) m_new = mx;
+                    if (__any_sync(0xffffffffu, grow && t > t0)) {
+                        const float f = (grow && t > t0) ? ex2(m_used - m_new) : 1.0f;
+                        l *= f;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            TMEM_LD32(tmem_o + lane_addr + c * 32, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+                            TMEM_ST32(tmem_o + lane_addr + c * 32, r);
+                        }
+                        tmem_wait_st();
+                    }
+                    m_used = m_new;
+                    // pass 2: p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
+                    float sum = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        TMEM_LD32(tmem_s + lane_addr + c * 32, r);
+                        tmem_wait_ld();
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            float p0 = (c * 32 + j < valid) ? ex2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_used)) : 0.f;
+                            float p1 = (c * 32 + j + 1 < valid) ? ex2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_used)) : 0.f;
+                            sum += p0 + p1;
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                            pk[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                        }
+                        TMEM_ST16(tmem_s + lane_addr + c * 16, pk);
+                    }
+                    l += sum;
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bar->p_full);
+                }
+                if (!ok) break;
+                // ---- end of a branch: read the accumulator ----
+                if (t1 > t0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
+                    if (!ok) break;
+                    ph_od ^= 1u;
+                    tc_fence_after();
+                }
+                const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+                const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                if (phase == 0) {
+                    // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park
+                    // it in the output row; the same thread reads it back in the final epilogue.
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        if (t1 > t0) {
+                            TMEM_LD32(tmem_o + lane_addr + c * 32, r);
+                            tmem_wait_ld();
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) r[j] = 0u;
+                        }
+                        if (row_ok) {
+                            if (p.part_sparse) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    float4 o4 = make_float4(__uint_as_float(r[j]) * inv_l, __uint_as_float(r[j + 1]) * inv_l,
+                                                            __uint_as_float(r[j + 2]) * inv_l, __uint_as_float(r[j + 3]) * inv_l);
+                                    *reinterpret_cast<float4 *>(p.part_sparse + part_off + c * 32 + j) = o4;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint4 o4;
+                                    uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv_l,
+                                                                                   __uint_as_float(r[j + 2 * e + 1]) * inv_l);
+                                        w[e] = *reinterpret_cast<uint32_t *>(&h2);
+                                    }
+                                    *reinterpret_cast<uint4 *>(out_row + c * 32 + j) = o4;
+                                }
+                            }
+                        }
+                    }
+                    if (p.lse_sparse && row_ok) p.lse_sparse[lse_off] = lse;
+                    if (t1 > t0) {
+                        tc_fence_before();
+                        mbar_arrive(&bar->o_free);
+                    }
+                } else {
+                    inv_l_lin = inv_l;
+                    if (p.lse_linear && row_ok) p.lse_linear[lse_off] = lse;
+                }
+            }
+            // ---- gate tile + combine ----
+            if (ok) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full, ph_s, abort_flag, p.error_flag, 10));
+                if (ok) {
+                    ph_s ^= 1u;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t g[32], o[32];
+                        TMEM_LD32(tmem_s + lane_addr + c * 32, g);
+                        TMEM_LD32(tmem_o + lane_addr + c * 32, o);
+                        tmem_wait_ld();
+                        if (!row_ok) continue;
+                        if (p.part_linear) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 o4 = make_float4(__uint_as_float(o[j]) * inv_l_lin, __uint_as_float(o[j + 1]) * inv_l_lin,
+                                                        __uint_as_float(o[j + 2]) * inv_l_lin, __uint_as_float(o[j + 3]) * inv_l_lin);
+                                *reinterpret_cast<float4 *>(p.part_linear + part_off + c * 32 + j) = o4;
+                            }
+                            continue;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 sp = *reinterpret_cast<const uint4 *>(out_row + c * 32 + j);
+                            const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp);
+                            uint4 qv = make_uint4(0, 0, 0, 0);
+                            if (!p.has_gate)
+                                qv = *reinterpret_cast<const uint4 *>(p.q + (long long)b * p.qsb + (long long)token * p.qsl +
+                                                                      (long long)h * p.qsh + c * 32 + j);
+                            const __nv_bfloat162 *q2 = reinterpret_cast<const __nv_bfloat162 *>(&qv);
+                            uint4 o4;
+                            uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int col = c * 32 + j + 2 * e;
+                                float z0, z1;
+                                if (p.has_gate) {
+                                    z0 = __uint_as_float(g[j + 2 * e]) + (p.gate_bias ? p.gate_bias[col] : 0.f);
+                                    z1 = __uint_as_float(g[j + 2 * e + 1]) + (p.gate_bias ? p.gate_bias[col + 1] : 0.f);
+                                } else {
+                                    const float2 qf = __bfloat1622float2(q2[e]);
+                                    z0 = qf.x;
+                                    z1 = qf.y;
+                                }
+                                const float g0 = 1.0f / (1.0f + ex2(-z0 * 1.4426950408889634f));
+                                const float g1 = 1.0f / (1.0f + ex2(-z1 * 1.4426950408889634f));
+                                const float2 s2 = __bfloat1622float2(sp2[e]);
+                                const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, g0, s2.x);
+                                const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, g1, s2.y);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(r0, r1);
+                                w[e] = *reinterpret_cast<uint32_t *>(&h2);
+                            }
+                            *reinterpret_cast<uint4 *>(out_row + c * 32 + j) = o4;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+        __syncthreads();   // every role is done with this item's shared and tensor memory
+        tc_fence_after();
+    }
+
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- work ordering: heaviest items first (counting sort on the selected-block count) ---------------
+constexpr int SCHED_BINS = 4096;
+__global__ void __launch_bounds__(1024)
+schedule_kernel(const int32_t *__restrict__ num, int n_items, int Nkv, int32_t *__restrict__ order, int *work_counter,
+                int *error_flag) {
+    __shared__ int hist[SCHED_BINS];
+    for (int i = threadIdx.x; i < SCHED_BINS; i += blockDim.x) hist[i] = 0;
+    if (threadIdx.x == 0) {
+        *work_counter = 0;
+        *error_flag = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+        const int key = max(0, min(min(num[i], Nkv), SCHED_BINS - 1));
+        atomicAdd(&hist[SCHED_BINS - 1 - key], 1);   // bin 0 = heaviest
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < SCHED_BINS; ++i) {
+            const int c = hist[i];
+            hist[i] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+        const int key = max(0, min(min(num[i], Nkv), SCHED_BINS - 1));
+        order[atomicAdd(&hist[SCHED_BINS - 1 - key], 1)] = i;
+    }
+}
+
+__global__ void convert_gate_kernel(const void *w, const void *bias, int dt, __nv_bfloat16 *w_out, float *b_out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < TILE * TILE) w_out[i] = __float2bfloat16_rn(load_elem(w, dt, i));
+    if (i < TILE) b_out[i] = bias ? load_elem(bias, dt, i) : 0.f;
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// `[B, L, H, 128]` bf16 view -> 4-D map (d, h, token, batch), box 64 x 1 x 128 x 1, 128-byte swizzle.
+static int make_map_4d(CUtensorMap *map, const wa_tensor4 *t, int B, int L, int H, const char *name) {
+    EncodeTiledFn fn = encode_fn();
+    WA_REQUIRE(fn, WA_ERR_DEVICE, "tcgen05 path: cuTensorMapEncodeTiled is unavailable");
+    cuuint64_t dims[4] = {(cuuint64_t)TILE, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)t->stride_h * 2, (cuuint64_t)t->stride_l * 2, (cuuint64_t)t->stride_b * 2};
+    if (B == 1) strides[2] = strides[1] * (cuuint64_t)L;   // unused extent: any legal stride
+    if (H == 1) strides[0] = 256;
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)TILE, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t->ptr, dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    WA_REQUIRE(r == CUDA_SUCCESS, WA_ERR_ALIGN, "tcgen05 path: tensor map for %s rejected (CUresult %d)", name, (int)r);
+    return 0;
+}
+
+static int make_map_w(CUtensorMap *map, const void *w) {
+    EncodeTiledFn fn = encode_fn();
+    WA_REQUIRE(fn, WA_ERR_DEVICE, "tcgen05 path: cuTensorMapEncodeTiled is unavailable");
+    cuuint64_t dims[2] = {(cuuint64_t)TILE, (cuuint64_t)TILE};
+    cuuint64_t strides[1] = {(cuuint64_t)TILE * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)TILE};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(w), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    WA_REQUIRE(r == CUDA_SUCCESS, WA_ERR_ALIGN, "tcgen05 path: tensor map for the gate weight rejected (CUresult %d)",
+               (int)r);
+    return 0;
+}
+
+static bool view_ok(const wa_tensor4 *t) {
+    return t->ptr && t->dtype == WA_BF16 && ((uintptr_t)t->ptr % 16 == 0) && t->stride_h % 8 == 0 &&
+           t->stride_l % 8 == 0 && t->stride_b % 8 == 0 && t->stride_h > 0 && t->stride_l > 0;
+}
+
+struct TunedWs {
+    size_t order, counter, w_bf16, bias, total;
+};
+static TunedWs tuned_plan(const wa_hsa_params *p) {
+    TunedWs w{};
+    size_t c = 0;
+    const size_t items = (size_t)p->B * p->H * ceil_div(p->Lq, TILE);
+    w.order = c; c = align_up(c + items * sizeof(int32_t), 256);
+    w.counter = c; c = align_up(c + 2 * sizeof(int), 256);
+    w.w_bf16 = c; c = align_up(c + (size_t)TILE * TILE * 2, 256);
+    w.bias = c; c = align_up(c + TILE * sizeof(float), 256);
+    w.total = c;
+    return w;
+}
+
+}  // namespace sm100
+
+size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p) { return sm100::tuned_plan(p).total; }
+size_t hsa_sm100_status_offset(const wa_hsa_params *p) { return sm100::tuned_plan(p).counter + sizeof(int); }
+
+static bool device_is_sm100() {
+    static int cached = -1;
+    if (cached < 0) {
+        int dev = 0, major = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+            return false;
+        cached = major == 10 ? 1 : 0;
+    }
+    return cached == 1;
+}
+
+bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc) {
+    using namespace sm100;
+    if (p->D != TILE || p->block_size != TILE || Lc <= 0) return false;
+    if (!view_ok(&p->q) || !view_ok(&p->k) || !view_ok(&p->v) || !view_ok(kc) || !view_ok(vc)) return false;
+    if (p->out.dtype != WA_BF16 || !p->out.ptr || (uintptr_t)p->out.ptr % 16 || p->out.stride_h % 8 || p->out.stride_l % 8 ||
+        p->out.stride_b % 8)
+        return false;
+    if ((long long)p->B * p->H * ceil_div(p->Lq, TILE) > (1 << 24)) return false;
+    return device_is_sm100() && encode_fn() != nullptr;
+}
+
+int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc, const int32_t *index,
+                     const int32_t *num, int Nq, int Nkv, void *workspace, cudaStream_t stream) {
+    using namespace sm100;
+    const TunedWs w = tuned_plan(p);
+    char *ws = (char *)workspace;
+    int32_t *order = (int32_t *)(ws + w.order);
+    int *counter = (int *)(ws + w.counter);
+    __nv_bfloat16 *w_bf16 = (__nv_bfloat16 *)(ws + w.w_bf16);
+    float *bias = (float *)(ws + w.bias);
+
+    CUtensorMap tq, tk, tv, tkc, tvc, tw;
+    int rc;
+    if ((rc = make_map_4d(&tq, &p->q, p->B, p->Lq, p->H, "q"))) return rc;
+    if ((rc = make_map_4d(&tk, &p->k, p->B, p->Lkv, p->H, "k"))) return rc;
+    if ((rc = make_map_4d(&tv, &p->v, p->B, p->Lkv, p->H, "v"))) return rc;
+    if ((rc = make_map_4d(&tkc, kc, p->B, Lc, p->H, "k_coarse"))) return rc;
+    if ((rc = make_map_4d(&tvc, vc, p->B, Lc, p->H, "v_coarse"))) return rc;
+    if (p->gate_w) {
+        convert_gate_kernel<<<(TILE * TILE + 255) / 256, 256, 0, stream>>>(p->gate_w, p->gate_b, p->gate_dtype, w_bf16, bias);
+        if ((rc = check_launch("wa_hsa_forward(gate convert)"))) return rc;
+    }
+    if ((rc = make_map_w(&tw, w_bf16))) return rc;
+
+    const int n_items = p->B * p->H * Nq;
+    schedule_kernel<<<1, 1024, 0, stream>>>(num, n_items, Nkv, order, counter, counter + 1);
+    if ((rc = check_launch("wa_hsa_forward(schedule)"))) return rc;
+
+    Params kp{};
+    kp.B = p->B; kp.H = p->H; kp.Lq = p->Lq; kp.Lkv = p->Lkv; kp.Lc = Lc; kp.Nq = Nq; kp.Nkv = Nkv;
+    kp.n_items = n_items;
+    kp.index = index; kp.num = num; kp.order = order; kp.work_counter = counter; kp.error_flag = counter + 1;
+    kp.out = (__nv_bfloat16 *)p->out.ptr; kp.osb = p->out.stride_b; kp.osl = p->out.stride_l; kp.osh = p->out.stride_h;
+    kp.gate_bias = bias; kp.has_gate = p->gate_w != nullptr;
+    kp.q = (const __nv_bfloat16 *)p->q.ptr; kp.qsb = p->q.stride_b; kp.qsl = p->q.stride_l; kp.qsh = p->q.stride_h;
+    kp.scale_log2 = (float)(pow((double)TILE, -0.5) * 1.4426950408889634);
+    kp.part_sparse = kp.part_linear = kp.lse_sparse = kp.lse_linear = nullptr;
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = n_items < 2 * sms ? n_items : 2 * sms;
+    hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, kp);
+    return check_launch("wa_hsa_forward(tcgen05)");
+}
+
 }  // namespace wa

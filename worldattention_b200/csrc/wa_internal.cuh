@@ -6,6 +6,7 @@ namespace wa {
 
 // tcgen05 fused HSA kernel (wa_hsa_sm100.cu)
 size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p);
+size_t hsa_sm100_status_offset(const wa_hsa_params *p);   // int32 flag inside the tuned workspace
 bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc);
 int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc,
                      const int32_t *index, const int32_t *num, int Nq, int Nkv, void *workspace,

@@ -160,12 +160,14 @@ def hsa_attention(
     topk_per_head: torch.Tensor | None = None,
     force_generic: bool = False,
     return_routing: bool = False,
+    check_status: bool = False,
 ):
     """Run HSA over `[B, L, H, D]` queries, keys and values (attention.py:153-259).
 
     Beyond the reference signature: `topk_per_head` (int32 `[H]`) selects a fixed number of blocks
     per head instead of the cumulative-mass count; `force_generic` skips the tcgen05 kernel;
-    `return_routing` also returns `(index, num, thresholds, used_tuned)`.
+    `return_routing` also returns `(index, num, thresholds, used_tuned)`; `check_status` waits for
+    the launch and raises if a bounded wait inside the tcgen05 kernel ran out.
     """
     if (k_coarse is None) != (v_coarse is None):
         raise ValueError("k_coarse and v_coarse must be provided together")
@@ -249,6 +251,11 @@ def hsa_attention(
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     used = ctypes.c_int(0)
     _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
+    if check_status and used.value:
+        status = ctypes.c_int(0)
+        _lib.check(lib.wa_hsa_status(ctypes.byref(p), ctypes.byref(status), _lib.stream_ptr(dev)))
+        if status.value:
+            raise RuntimeError(f"tcgen05 HSA kernel gave up at wait site {status.value}; its output is invalid")
 
     if distill.distill_enabled() and torch.is_grad_enabled():
         distill.record_against_dense(out, q, k, v)
