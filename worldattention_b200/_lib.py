@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libwa_b200.so")
+LIB_PATH = os.environ.get("WORLDATTENTION_B200_LIB") or os.path.join(_HERE, "libwa_b200.so")
 
 WA_F32, WA_BF16 = 0, 1
 WA_ERR_ARG, WA_ERR_UNSUPPORTED, WA_ERR_WORKSPACE, WA_ERR_ALIGN, WA_ERR_DEVICE = -1, -2, -3, -4, -5

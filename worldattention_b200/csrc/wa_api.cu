@@ -162,8 +162,9 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
     if (used_tuned) *used_tuned = 0;
 
     // ---- routing (routing.py:45-118) ---------------------------------------------------------
-    if ((rc = wa_pool_blocks(&p->q, p->B, p->Lq, p->H, p->D, p->block_size, q_pooled, stream))) return rc;
-    if ((rc = wa_pool_blocks(&p->k, p->B, p->Lkv, p->H, p->D, p->block_size, k_pooled, stream))) return rc;
+    WA_REQUIRE(p->H <= 65535 && p->B <= 65535, WA_ERR_UNSUPPORTED, "%s: B, H must be <= 65535", what);
+    if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream)))
+        return rc;
     if ((rc = wa_route_scores(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, block_attn, stream))) return rc;
     if ((rc = wa_route_select(block_attn, p->B, p->H, w.Nq, w.Nkv, p->tau_min, p->tau_max, p->topk_per_head, index,
                               num, nullptr, thresholds, gini, stream)))

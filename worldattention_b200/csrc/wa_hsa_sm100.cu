@@ -29,8 +29,56 @@ constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2..5 softm
 constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
 constexpr int TMEM_COLS = 256;       // S: columns [0,128), O: [128,256)
-constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 /*alignment slack*/ + 1024 /*barriers, bias*/;
 constexpr long long WAIT_CYCLES = 4000000000ll;
+
+// Optional event trace for kernel tuning (compile with -DWA_SM100_TRACE): CTA 0 appends
+// (event id, clock) pairs from one thread per role to a global buffer.
+#ifdef WA_SM100_TRACE
+constexpr int TRACE_SLOTS = 8192;            // (id, clock) pairs per traced role
+__device__ long long g_trace[3][2 * TRACE_SLOTS];
+__device__ int g_trace_n[3];
+__device__ long long g_cta_stats[1024][6];
+__device__ __forceinline__ unsigned long long wa_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned wa_smid() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(r));
+    return r;
+}
+#define WA_TRACE_DECL int trace_at = 0; long long st_items = 0, st_tiles = 0; const unsigned long long st_t0 = wa_globaltimer(); const long long st_c0 = clock64()
+#define WA_STATS_ITEM(n) do { st_items += 1; st_tiles += (n); } while (0)
+#define WA_TRACE(id)                                                                         \
+    do {                                                                                     \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) <= 2 &&         \
+            trace_at < TRACE_SLOTS) {                                                        \
+            g_trace[threadIdx.x >> 5][2 * trace_at] = (id);                                  \
+            g_trace[threadIdx.x >> 5][2 * trace_at + 1] = clock64();                         \
+            ++trace_at;                                                                      \
+        }                                                                                    \
+    } while (0)
+#define WA_TRACE_FLUSH                                                                       \
+    do {                                                                                     \
+        if (threadIdx.x == 0 && blockIdx.x < 1024) {                                         \
+            g_cta_stats[blockIdx.x][0] = wa_smid();                                          \
+            g_cta_stats[blockIdx.x][1] = (long long)st_t0;                                   \
+            g_cta_stats[blockIdx.x][2] = (long long)wa_globaltimer();                        \
+            g_cta_stats[blockIdx.x][3] = st_items;                                           \
+            g_cta_stats[blockIdx.x][4] = st_tiles;                                           \
+            g_cta_stats[blockIdx.x][5] = clock64() - st_c0;                                  \
+        }                                                                                    \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) <= 2)           \
+            g_trace_n[threadIdx.x >> 5] = trace_at;                                          \
+    } while (0)
+#else
+#define WA_TRACE_DECL
+#define WA_STATS_ITEM(n) do { } while (0)
+#define WA_TRACE(id) do { } while (0)
+#define WA_TRACE_FLUSH do { } while (0)
+#endif
 
 struct Params {
     int B, H, Lq, Lkv, Lc, Nq, Nkv;
@@ -50,6 +98,7 @@ struct Params {
     // partial-output mode (KV-sharded multi-GPU): normalised per-branch outputs + natural-log LSE
     float *part_sparse, *part_linear;   // [B, Lq, H, 128] float32 or null
     float *lse_sparse, *lse_linear;     // [B, H, Lq]
+    uint4 *stash;                       // per-CTA scratch for the parked sparse result: [grid][16][128] x 16 B
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -99,6 +148,11 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, const void *src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -180,11 +234,45 @@ __host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major) {
            | ((uint32_t)(TILE >> 4) << 24);
 }
 
+template <bool MASKED>
+__device__ __forceinline__ float row_max32(const uint32_t (&r)[32], int col0, int valid) {
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+        if (!MASKED || col0 + j < valid) m0 = fmaxf(m0, __uint_as_float(r[j]));
+        if (!MASKED || col0 + j + 1 < valid) m1 = fmaxf(m1, __uint_as_float(r[j + 1]));
+    }
+    return fmaxf(m0, m1);
+}
+
+// 32 scores -> 32 probabilities packed as 16 bf16 pairs; returns their float32 sum.
+template <bool MASKED>
+__device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale, float m, int col0,
+                                            int valid) {
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+        float p0 = ex2(fmaf(__uint_as_float(r[j]), scale, -m));
+        float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale, -m));
+        if (MASKED) {
+            if (col0 + j >= valid) p0 = 0.f;
+            if (col0 + j + 1 >= valid) p1 = 0.f;
+        }
+        s0 += p0;
+        s1 += p1;
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+        pk[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+    }
+    return s0 + s1;
+}
+
 struct Barriers {
     uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done, o_free;
     uint32_t tmem_base;
     int item;
     int abort_flag;
+    int valid[4];   // real token count of the K tile in flight, ring indexed by tile number
+    float bias[TILE];   // gate bias
 };
 
 // ---- the kernel ----------------------------------------------------------------------------------
@@ -192,7 +280,7 @@ __global__ void __launch_bounds__(THREADS, 2)
 hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
                      const __grid_constant__ CUtensorMap tm_vc, const __grid_constant__ CUtensorMap tm_w,
-                     const Params p) {
+                     const __grid_constant__ CUtensorMap tm_out, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *q_s = smem, *k_s = smem + TILE_BYTES, *v_s = smem + 2 * TILE_BYTES;
@@ -214,6 +302,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         bar->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x >= 64) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
                      "r"(TMEM_COLS) : "memory");
@@ -224,6 +313,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = bar->tmem_base;
     const uint32_t tmem_s = tmem, tmem_o = tmem + TILE;
+    WA_TRACE_DECL;
+    WA_TRACE(0);
 
     // phase parities, carried across work items
     // ("empty" parities start at 1: a fresh barrier counts as already released)
@@ -243,6 +334,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int n_sel = max(0, min(p.num[meta], p.Nkv));
         const int32_t *ids = p.index + meta * (long long)p.Nkv;
         const int n_tiles = n_sel + lin_tiles + 1;   // sparse, linear, gate
+        WA_STATS_ITEM(n_tiles);
 
         if (warp == 0) {
             // ================= TMA producer =================
@@ -256,9 +348,15 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     ok = mbar_wait(&bar->k_empty, ph_ke, abort_flag, p.error_flag, 1);
                     if (!ok) break;
                     ph_ke ^= 1u;
+                    int id = 0;
+                    if (t < n_sel) {
+                        id = max(0, min(ids[t], p.Nkv - 1));
+                        bar->valid[t & 3] = min(TILE, p.Lkv - id * TILE);
+                    } else {
+                        bar->valid[t & 3] = min(TILE, p.Lc - (t - n_sel) * TILE);
+                    }
                     mbar_expect_tx(&bar->k_full, TILE_BYTES);
                     if (t < n_sel) {
-                        const int id = max(0, min(ids[t], p.Nkv - 1));
                         tma_load_4d(k_s, &tm_k, &bar->k_full, 0, h, id * TILE, b);
                         tma_load_4d(k_s + HALF_BYTES, &tm_k, &bar->k_full, 64, h, id * TILE, b);
                     } else if (t < n_sel + lin_tiles) {
@@ -275,7 +373,6 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         ph_ve ^= 1u;
                         mbar_expect_tx(&bar->v_full, TILE_BYTES);
                         if (t < n_sel) {
-                            const int id = max(0, min(ids[t], p.Nkv - 1));
                             tma_load_4d(v_s, &tm_v, &bar->v_full, 0, h, id * TILE, b);
                             tma_load_4d(v_s + HALF_BYTES, &tm_v, &bar->v_full, 64, h, id * TILE, b);
                         } else {
@@ -296,6 +393,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     ok = mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4);
                     if (!ok) break;
                     ph_kf ^= 1u;
+                    WA_TRACE(1);
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
@@ -305,14 +403,17 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     }
                     tc_commit(&bar->k_empty);
                     tc_commit(&bar->s_full);
+                    WA_TRACE(4);
                     if (t < n_sel + lin_tiles) {
                         const bool first = (t == 0) || (t == n_sel);
                         ok = mbar_wait(&bar->p_full, ph_p, abort_flag, p.error_flag, 5);
                         if (!ok) break;
                         ph_p ^= 1u;
+                        WA_TRACE(5);
                         ok = mbar_wait(&bar->v_full, ph_vf, abort_flag, p.error_flag, 6);
                         if (!ok) break;
                         ph_vf ^= 1u;
+                        WA_TRACE(6);
                         if (first && t > 0) {
                             // the sparse accumulator must have been read out before the linear branch reuses it
                             ok = mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7);
@@ -325,6 +426,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             mma_ts(tmem_o, tmem_s + kk * 8, smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), IDESC_PV,
                                    !(first && kk == 0));
                         tc_commit(&bar->v_empty);
+                        WA_TRACE(7);
                         const bool last = (t == n_sel - 1) || (t == n_sel + lin_tiles - 1);
                         if (last) tc_commit(&bar->o_done);
                     }
@@ -337,9 +439,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
             const int token = qb * TILE + row;
             const bool row_ok = token < p.Lq;
-            __nv_bfloat16 *out_row = p.out + (long long)b * p.osb + (long long)token * p.osl + (long long)h * p.osh;
             const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE;
             const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
+            uint4 *stash = p.stash + (size_t)blockIdx.x * (16 * TILE);
             bool ok = true;
             float inv_l_lin = 0.f;
 
@@ -347,29 +449,28 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_sel + lin_tiles;
                 float m_used = -INFINITY, l = 0.f;
                 for (int t = t0; t < t1 && ok; ++t) {
-                    int valid;
-                    if (phase == 0) {
-                        const int id = max(0, min(ids[t], p.Nkv - 1));
-                        valid = min(TILE, p.Lkv - id * TILE);
-                    } else {
-                        valid = min(TILE, p.Lc - (t - n_sel) * TILE);
-                    }
                     ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full, ph_s, abort_flag, p.error_flag, 8));
                     if (!ok) break;
                     ph_s ^= 1u;
+                    WA_TRACE(2);
                     tc_fence_after();
-                    uint32_t r[32];
-                    // pass 1: row maximum over the valid columns
+                    const int valid = bar->valid[t & 3];   // written by the producer before it armed this tile
+                    uint32_t ra[32], rb[32];
+                    // pass 1: row maximum over the valid columns, two 32-column loads in flight
                     float mx = -INFINITY;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        TMEM_LD32(tmem_s + lane_addr + c * 32, r);
+                    for (int c = 0; c < 4; c += 2) {
+                        TMEM_LD32(tmem_s + lane_addr + c * 32, ra);
+                        TMEM_LD32(tmem_s + lane_addr + c * 32 + 32, rb);
                         tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (c * 32 + j < valid) mx = fmaxf(mx, __uint_as_float(r[j]));
+                        if (valid == TILE) {
+                            mx = fmaxf(mx, fmaxf(row_max32<false>(ra, 0, 0), row_max32<false>(rb, 0, 0)));
+                        } else {
+                            mx = fmaxf(mx, fmaxf(row_max32<true>(ra, c * 32, valid), row_max32<true>(rb, c * 32 + 32, valid)));
+                        }
                     }
                     mx *= p.scale_log2;
+                    WA_TRACE(8);
                     // lazy rescale: only when the running maximum grows by more than 2^8
                     float m_new = m_used;
                     const bool grow = mx > m_used + 8.0f;
@@ -379,11 +480,11 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         l *= f;
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            TMEM_LD32(tmem_o + lane_addr + c * 32, r);
+                            TMEM_LD32(tmem_o + lane_addr + c * 32, ra);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * f);
-                            TMEM_ST32(tmem_o + lane_addr + c * 32, r);
+                            for (int j = 0; j < 32; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) * f);
+                            TMEM_ST32(tmem_o + lane_addr + c * 32, ra);
                         }
                         tmem_wait_st();
                     }
@@ -391,24 +492,23 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     // pass 2: p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
                     float sum = 0.f;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        TMEM_LD32(tmem_s + lane_addr + c * 32, r);
+                    for (int c = 0; c < 4; c += 2) {
+                        TMEM_LD32(tmem_s + lane_addr + c * 32, ra);
+                        TMEM_LD32(tmem_s + lane_addr + c * 32 + 32, rb);
                         tmem_wait_ld();
                         uint32_t pk[16];
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            float p0 = (c * 32 + j < valid) ? ex2(fmaf(__uint_as_float(r[j]), p.scale_log2, -m_used)) : 0.f;
-                            float p1 = (c * 32 + j + 1 < valid) ? ex2(fmaf(__uint_as_float(r[j + 1]), p.scale_log2, -m_used)) : 0.f;
-                            sum += p0 + p1;
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                            pk[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
-                        }
+                        if (valid == TILE) sum += exp_pack32<false>(ra, pk, p.scale_log2, m_used, 0, 0);
+                        else sum += exp_pack32<true>(ra, pk, p.scale_log2, m_used, c * 32, valid);
                         TMEM_ST16(tmem_s + lane_addr + c * 16, pk);
+                        if (valid == TILE) sum += exp_pack32<false>(rb, pk, p.scale_log2, m_used, 0, 0);
+                        else sum += exp_pack32<true>(rb, pk, p.scale_log2, m_used, c * 32 + 32, valid);
+                        TMEM_ST16(tmem_s + lane_addr + c * 16 + 16, pk);
                     }
                     l += sum;
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(&bar->p_full);
+                    WA_TRACE(3);
                 }
                 if (!ok) break;
                 // ---- end of a branch: read the accumulator ----
@@ -417,12 +517,13 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (!ok) break;
                     ph_od ^= 1u;
                     tc_fence_after();
+                    WA_TRACE(12);
                 }
                 const float inv_l = l > 0.f ? 1.0f / l : 0.f;
                 const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
                 if (phase == 0) {
-                    // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park
-                    // it in the output row; the same thread reads it back in the final epilogue.
+                    // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park it
+                    // in this CTA's stash, laid out [16-byte chunk][thread] so that warps store and reload whole lines.
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t r[32];
@@ -433,27 +534,27 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
                             for (int j = 0; j < 32; ++j) r[j] = 0u;
                         }
-                        if (row_ok) {
-                            if (p.part_sparse) {
+                        if (p.part_sparse) {
+                            if (row_ok) {
 #pragma unroll
                                 for (int j = 0; j < 32; j += 4) {
                                     float4 o4 = make_float4(__uint_as_float(r[j]) * inv_l, __uint_as_float(r[j + 1]) * inv_l,
                                                             __uint_as_float(r[j + 2]) * inv_l, __uint_as_float(r[j + 3]) * inv_l);
                                     *reinterpret_cast<float4 *>(p.part_sparse + part_off + c * 32 + j) = o4;
                                 }
-                            } else {
+                            }
+                        } else {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 o4;
-                                    uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 o4;
+                                uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
 #pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv_l,
-                                                                                   __uint_as_float(r[j + 2 * e + 1]) * inv_l);
-                                        w[e] = *reinterpret_cast<uint32_t *>(&h2);
-                                    }
-                                    *reinterpret_cast<uint4 *>(out_row + c * 32 + j) = o4;
+                                for (int e = 0; e < 4; ++e) {
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv_l,
+                                                                               __uint_as_float(r[j + 2 * e + 1]) * inv_l);
+                                    w[e] = *reinterpret_cast<uint32_t *>(&h2);
                                 }
+                                stash[(c * 4 + (j >> 3)) * TILE + row] = o4;
                             }
                         }
                     }
@@ -469,34 +570,50 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             // ---- gate tile + combine ----
             if (ok) {
+                uint4 sp_next[4];
+                if (!p.part_linear) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sp_next[e] = stash[e * TILE + row];   // in flight during the waits below
+                }
                 ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full, ph_s, abort_flag, p.error_flag, 10));
                 if (ok) {
                     ph_s ^= 1u;
                     tc_fence_after();
+                    WA_TRACE(13);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t g[32], o[32];
                         TMEM_LD32(tmem_s + lane_addr + c * 32, g);
                         TMEM_LD32(tmem_o + lane_addr + c * 32, o);
-                        tmem_wait_ld();
-                        if (!row_ok) continue;
-                        if (p.part_linear) {
+                        uint4 sp_cur[4];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 o4 = make_float4(__uint_as_float(o[j]) * inv_l_lin, __uint_as_float(o[j + 1]) * inv_l_lin,
-                                                        __uint_as_float(o[j + 2]) * inv_l_lin, __uint_as_float(o[j + 3]) * inv_l_lin);
-                                *reinterpret_cast<float4 *>(p.part_linear + part_off + c * 32 + j) = o4;
+                        for (int e = 0; e < 4; ++e) sp_cur[e] = sp_next[e];
+                        if (!p.part_linear && c < 3) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) sp_next[e] = stash[((c + 1) * 4 + e) * TILE + row];
+                        }
+                        tmem_wait_ld();
+                        WA_TRACE(14);
+                        if (p.part_linear) {
+                            if (row_ok) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    float4 o4 = make_float4(__uint_as_float(o[j]) * inv_l_lin, __uint_as_float(o[j + 1]) * inv_l_lin,
+                                                            __uint_as_float(o[j + 2]) * inv_l_lin, __uint_as_float(o[j + 3]) * inv_l_lin);
+                                    *reinterpret_cast<float4 *>(p.part_linear + part_off + c * 32 + j) = o4;
+                                }
                             }
                             continue;
                         }
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
-                            uint4 sp = *reinterpret_cast<const uint4 *>(out_row + c * 32 + j);
-                            const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp);
+                            // 16-byte chunk `cc` of this row inside the swizzled 128 x 128 bf16 tile that held Q
+                            const int cc = c * 4 + (j >> 3);
+                            uint4 *slot = reinterpret_cast<uint4 *>(q_s + (cc >> 3) * HALF_BYTES + row * 128 +
+                                                                    (((cc & 7) ^ (row & 7)) << 4));
+                            const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp_cur[j >> 3]);
                             uint4 qv = make_uint4(0, 0, 0, 0);
-                            if (!p.has_gate)
-                                qv = *reinterpret_cast<const uint4 *>(p.q + (long long)b * p.qsb + (long long)token * p.qsl +
-                                                                      (long long)h * p.qsh + c * 32 + j);
+                            if (!p.has_gate) qv = *slot;   // the gate-less path needs q itself: read it before overwriting
                             const __nv_bfloat162 *q2 = reinterpret_cast<const __nv_bfloat162 *>(&qv);
                             uint4 o4;
                             uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
@@ -505,32 +622,48 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                 const int col = c * 32 + j + 2 * e;
                                 float z0, z1;
                                 if (p.has_gate) {
-                                    z0 = __uint_as_float(g[j + 2 * e]) + (p.gate_bias ? p.gate_bias[col] : 0.f);
-                                    z1 = __uint_as_float(g[j + 2 * e + 1]) + (p.gate_bias ? p.gate_bias[col + 1] : 0.f);
+                                    z0 = __uint_as_float(g[j + 2 * e]) + bar->bias[col];
+                                    z1 = __uint_as_float(g[j + 2 * e + 1]) + bar->bias[col + 1];
                                 } else {
                                     const float2 qf = __bfloat1622float2(q2[e]);
                                     z0 = qf.x;
                                     z1 = qf.y;
                                 }
-                                const float g0 = 1.0f / (1.0f + ex2(-z0 * 1.4426950408889634f));
-                                const float g1 = 1.0f / (1.0f + ex2(-z1 * 1.4426950408889634f));
+                                const float g0 = __fdividef(1.0f, 1.0f + ex2(-z0 * 1.4426950408889634f));
+                                const float g1 = __fdividef(1.0f, 1.0f + ex2(-z1 * 1.4426950408889634f));
                                 const float2 s2 = __bfloat1622float2(sp2[e]);
                                 const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, g0, s2.x);
                                 const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, g1, s2.y);
                                 __nv_bfloat162 h2 = __floats2bfloat162_rn(r0, r1);
                                 w[e] = *reinterpret_cast<uint32_t *>(&h2);
                             }
-                            *reinterpret_cast<uint4 *>(out_row + c * 32 + j) = o4;
+                            *slot = o4;
                         }
                     }
                 }
             }
+            if (!p.part_linear) {
+                // Hand the staged tile to the TMA store (rows beyond q_len are clipped by the tensor map).  Every
+                // softmax thread takes part in the barrier whether or not its waits succeeded.
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64 && ok) {
+                    tma_store_4d(&tm_out, q_s, 0, h, qb * TILE, b);
+                    tma_store_4d(&tm_out, q_s + HALF_BYTES, 64, h, qb * TILE, b);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // smem reusable afterwards
+                }
+            }
             tc_fence_before();
         }
+        WA_TRACE(10);
         __syncthreads();   // every role is done with this item's shared and tensor memory
+        WA_TRACE(11);
         tc_fence_after();
     }
 
+    WA_TRACE(9);
+    WA_TRACE_FLUSH;
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -541,7 +674,15 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 constexpr int SCHED_BINS = 4096;
 __global__ void __launch_bounds__(1024)
 schedule_kernel(const int32_t *__restrict__ num, int n_items, int Nkv, int32_t *__restrict__ order, int *work_counter,
-                int *error_flag) {
+                int *error_flag, const void *gate_w, const void *gate_b, int gate_dt, __nv_bfloat16 *w_out,
+                float *b_out) {
+    if (blockIdx.x > 0) {
+        // blocks 1..16: gate weight -> bf16, bias -> float32 (the weight is an MMA operand)
+        const int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
+        if (i < TILE * TILE) w_out[i] = __float2bfloat16_rn(load_elem(gate_w, gate_dt, i));
+        if (i < TILE) b_out[i] = gate_b ? load_elem(gate_b, gate_dt, i) : 0.f;
+        return;
+    }
     __shared__ int hist[SCHED_BINS];
     for (int i = threadIdx.x; i < SCHED_BINS; i += blockDim.x) hist[i] = 0;
     if (threadIdx.x == 0) {
@@ -554,25 +695,39 @@ schedule_kernel(const int32_t *__restrict__ num, int n_items, int Nkv, int32_t *
         atomicAdd(&hist[SCHED_BINS - 1 - key], 1);   // bin 0 = heaviest
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int i = 0; i < SCHED_BINS; ++i) {
-            const int c = hist[i];
-            hist[i] = run;
-            run += c;
-        }
+    // exclusive prefix over the bins: four bins per thread, then a block scan of the per-thread totals
+    __shared__ int warp_tot[32];
+    const int b0 = threadIdx.x * 4;
+    const int c0 = hist[b0], c1 = hist[b0 + 1], c2 = hist[b0 + 2], c3 = hist[b0 + 3];
+    int incl = c0 + c1 + c2 + c3;
+    const int mine = incl;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((threadIdx.x & 31) >= o) incl += v;
     }
+    if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = incl;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int w = warp_tot[threadIdx.x];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (threadIdx.x >= o) w += v;
+        }
+        warp_tot[threadIdx.x] = w;
+    }
+    __syncthreads();
+    int base = incl - mine + ((threadIdx.x >> 5) ? warp_tot[(threadIdx.x >> 5) - 1] : 0);
+    hist[b0] = base;
+    hist[b0 + 1] = base + c0;
+    hist[b0 + 2] = base + c0 + c1;
+    hist[b0 + 3] = base + c0 + c1 + c2;
     __syncthreads();
     for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
         const int key = max(0, min(min(num[i], Nkv), SCHED_BINS - 1));
         order[atomicAdd(&hist[SCHED_BINS - 1 - key], 1)] = i;
     }
-}
-
-__global__ void convert_gate_kernel(const void *w, const void *bias, int dt, __nv_bfloat16 *w_out, float *b_out) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < TILE * TILE) w_out[i] = __float2bfloat16_rn(load_elem(w, dt, i));
-    if (i < TILE) b_out[i] = bias ? load_elem(bias, dt, i) : 0.f;
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -631,8 +786,16 @@ static bool view_ok(const wa_tensor4 *t) {
            t->stride_l % 8 == 0 && t->stride_b % 8 == 0 && t->stride_h > 0 && t->stride_l > 0;
 }
 
+static int max_grid() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0)
+        sms = 160;
+    return 2 * sms;
+}
+
 struct TunedWs {
-    size_t order, counter, w_bf16, bias, total;
+    size_t order, counter, w_bf16, bias, stash, total;
 };
 static TunedWs tuned_plan(const wa_hsa_params *p) {
     TunedWs w{};
@@ -642,11 +805,34 @@ static TunedWs tuned_plan(const wa_hsa_params *p) {
     w.counter = c; c = align_up(c + 2 * sizeof(int), 256);
     w.w_bf16 = c; c = align_up(c + (size_t)TILE * TILE * 2, 256);
     w.bias = c; c = align_up(c + TILE * sizeof(float), 256);
+    w.stash = c; c = align_up(c + (size_t)max_grid() * 16 * TILE * sizeof(uint4), 256);
     w.total = c;
     return w;
 }
 
 }  // namespace sm100
+
+#ifdef WA_SM100_TRACE
+extern "C" int wa_stats_read(long long *dst, int n_ctas) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(dst, sm100::g_cta_stats, (size_t)n_ctas * 6 * sizeof(long long));
+    return 0;
+}
+extern "C" int wa_trace_read(long long *dst, int max_words) {
+    // concatenates the three roles' (id, clock) pairs; returns the number of 64-bit words written
+    int n[3] = {0, 0, 0}, out = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(n, sm100::g_trace_n, sizeof(n));
+    for (int r = 0; r < 3; ++r) {
+        const int words = 2 * n[r];
+        if (out + words > max_words) break;
+        cudaMemcpyFromSymbol(dst + out, sm100::g_trace, (size_t)words * sizeof(long long),
+                             (size_t)r * 2 * sm100::TRACE_SLOTS * sizeof(long long));
+        out += words;
+    }
+    return out;
+}
+#endif
 
 size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p) { return sm100::tuned_plan(p).total; }
 size_t hsa_sm100_status_offset(const wa_hsa_params *p) { return sm100::tuned_plan(p).counter + sizeof(int); }
@@ -684,21 +870,19 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     __nv_bfloat16 *w_bf16 = (__nv_bfloat16 *)(ws + w.w_bf16);
     float *bias = (float *)(ws + w.bias);
 
-    CUtensorMap tq, tk, tv, tkc, tvc, tw;
+    CUtensorMap tq, tk, tv, tkc, tvc, tw, tout;
     int rc;
     if ((rc = make_map_4d(&tq, &p->q, p->B, p->Lq, p->H, "q"))) return rc;
     if ((rc = make_map_4d(&tk, &p->k, p->B, p->Lkv, p->H, "k"))) return rc;
     if ((rc = make_map_4d(&tv, &p->v, p->B, p->Lkv, p->H, "v"))) return rc;
     if ((rc = make_map_4d(&tkc, kc, p->B, Lc, p->H, "k_coarse"))) return rc;
     if ((rc = make_map_4d(&tvc, vc, p->B, Lc, p->H, "v_coarse"))) return rc;
-    if (p->gate_w) {
-        convert_gate_kernel<<<(TILE * TILE + 255) / 256, 256, 0, stream>>>(p->gate_w, p->gate_b, p->gate_dtype, w_bf16, bias);
-        if ((rc = check_launch("wa_hsa_forward(gate convert)"))) return rc;
-    }
     if ((rc = make_map_w(&tw, w_bf16))) return rc;
+    if ((rc = make_map_4d(&tout, &p->out, p->B, p->Lq, p->H, "out"))) return rc;
 
     const int n_items = p->B * p->H * Nq;
-    schedule_kernel<<<1, 1024, 0, stream>>>(num, n_items, Nkv, order, counter, counter + 1);
+    schedule_kernel<<<p->gate_w ? 1 + TILE * TILE / 1024 : 1, 1024, 0, stream>>>(
+        num, n_items, Nkv, order, counter, counter + 1, p->gate_w, p->gate_b, p->gate_dtype, w_bf16, bias);
     if ((rc = check_launch("wa_hsa_forward(schedule)"))) return rc;
 
     Params kp{};
@@ -710,6 +894,7 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.q = (const __nv_bfloat16 *)p->q.ptr; kp.qsb = p->q.stride_b; kp.qsl = p->q.stride_l; kp.qsh = p->q.stride_h;
     kp.scale_log2 = (float)(pow((double)TILE, -0.5) * 1.4426950408889634);
     kp.part_sparse = kp.part_linear = kp.lse_sparse = kp.lse_linear = nullptr;
+    kp.stash = (uint4 *)(ws + w.stash);
 
     static bool attr_set = false;
     if (!attr_set) {
@@ -717,11 +902,8 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = n_items < 2 * sms ? n_items : 2 * sms;
-    hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, kp);
+    const int grid = n_items < max_grid() ? n_items : max_grid();
+    hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     return check_launch("wa_hsa_forward(tcgen05)");
 }
 

@@ -4,6 +4,10 @@
 
 namespace wa {
 
+// routing (wa_routing.cu): pools x and optionally y in one launch
+int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
+                int block_size, cudaStream_t stream);
+
 // tcgen05 fused HSA kernel (wa_hsa_sm100.cu)
 size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p);
 size_t hsa_sm100_status_offset(const wa_hsa_params *p);   // int32 flag inside the tuned workspace

@@ -16,8 +16,14 @@ constexpr int POOL_THREADS = 256;
 template <bool VEC_BF16>
 __global__ void __launch_bounds__(POOL_THREADS)
 pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, int aligned,
-                   float *__restrict__ pooled) {
-    const int nb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+                   float *__restrict__ pooled, View4 x2, int L2, int num_blocks2, int aligned2,
+                   float *__restrict__ pooled2) {
+    int nb = blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    if (nb >= num_blocks) {   // second tensor (keys) pooled by the same launch
+        nb -= num_blocks;
+        x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2;
+    }
     const int t0 = nb * block_size;
     const int n_real = min(block_size, L - t0);
     extern __shared__ double pool_smem[];  // [rows_in_flight][D]
@@ -108,12 +114,19 @@ route_scores_kernel(const float *__restrict__ qp, const float *__restrict__ kp, 
     __shared__ float bcast;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = SCORE_THREADS / 32;
-    for (int j = warp; j < Nkv; j += nwarps) {
-        const float *kj = k + (long long)j * D;
-        double acc = 0.0;
-        for (int d = lane; d < D; d += 32) acc = fma((double)q[d], (double)kj[d], acc);
-        acc = warp_sum_d(acc);
-        if (lane == 0) out[j] = __fmul_rn((float)acc, scale);
+    for (int j0 = warp * 4; j0 < Nkv; j0 += nwarps * 4) {   // four independent dot products in flight
+        double acc[4] = {0.0, 0.0, 0.0, 0.0};
+        for (int d = lane; d < D; d += 32) {
+            const double qd = (double)q[d];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j0 + u < Nkv) acc[u] = fma(qd, (double)k[(long long)(j0 + u) * D + d], acc[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const double t = warp_sum_d(acc[u]);
+            if (lane == 0 && j0 + u < Nkv) out[j0 + u] = __fmul_rn((float)t, scale);
+        }
     }
     __syncthreads();
 
@@ -308,6 +321,35 @@ __global__ void map_to_index_kernel(const uint8_t *__restrict__ mask, long long 
 
 using namespace wa;
 
+namespace wa {
+static bool pool_vec_ok(const wa_tensor4 *x, int D) {
+    return x->dtype == WA_BF16 && D % 8 == 0 && D / 8 <= POOL_THREADS && ((uintptr_t)x->ptr % 16 == 0) &&
+           x->stride_b % 8 == 0 && x->stride_l % 8 == 0 && x->stride_h % 8 == 0;
+}
+
+// Pools `x` (and, when given, `y`, e.g. queries and keys of one forward) in a single launch.
+int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
+                int block_size, cudaStream_t stream) {
+    const int nbx = ceil_div(Lx, block_size), nby = y ? ceil_div(Ly, block_size) : 0;
+    View4 vx = make_view(x), vy = y ? make_view(y) : vx;
+    dim3 grid(nbx + nby, H, B);
+    const bool vec = pool_vec_ok(x, D) && (!y || pool_vec_ok(y, D));
+    if (vec) {
+        const int rows = POOL_THREADS / (D / 8);
+        const size_t smem = (size_t)rows * D * sizeof(float);
+        WA_REQUIRE(smem <= 48 * 1024, WA_ERR_UNSUPPORTED, "wa_pool_blocks: D=%d too large", D);
+        pool_blocks_kernel<true><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
+                                                                       px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py);
+    } else {
+        const int rows = D >= POOL_THREADS ? 1 : POOL_THREADS / D;
+        const size_t smem = (size_t)rows * (D < POOL_THREADS ? D : POOL_THREADS) * sizeof(double);
+        pool_blocks_kernel<false><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
+                                                                        px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py);
+    }
+    return check_launch("wa_pool_blocks");
+}
+}  // namespace wa
+
 extern "C" int wa_pool_blocks(const wa_tensor4 *x, int B, int L, int H, int D, int block_size,
                               float *pooled, void *stream) {
     WA_REQUIRE(x && x->ptr && pooled, WA_ERR_ARG, "wa_pool_blocks: null pointer");
@@ -316,26 +358,7 @@ extern "C" int wa_pool_blocks(const wa_tensor4 *x, int B, int L, int H, int D, i
                "wa_pool_blocks: sizes must be positive (B=%d L=%d H=%d D=%d block=%d)", B, L, H, D,
                block_size);
     WA_REQUIRE(H <= 65535 && B <= 65535, WA_ERR_UNSUPPORTED, "wa_pool_blocks: B, H must be <= 65535");
-    const int nb = ceil_div(L, block_size);
-    const int aligned = (L % block_size) == 0;
-    View4 v = make_view(x);
-    dim3 grid(nb, H, B);
-    const bool vec = x->dtype == WA_BF16 && D % 8 == 0 && D / 8 <= POOL_THREADS &&
-                     ((uintptr_t)x->ptr % 16 == 0) && x->stride_b % 8 == 0 && x->stride_l % 8 == 0 &&
-                     x->stride_h % 8 == 0;
-    if (vec) {
-        const int rows = POOL_THREADS / (D / 8);
-        const size_t smem = (size_t)rows * D * sizeof(float);
-        WA_REQUIRE(smem <= 48 * 1024, WA_ERR_UNSUPPORTED, "wa_pool_blocks: D=%d too large", D);
-        pool_blocks_kernel<true><<<grid, POOL_THREADS, smem, (cudaStream_t)stream>>>(
-            v, L, H, D, block_size, nb, aligned, pooled);
-    } else {
-        const int rows = D >= POOL_THREADS ? 1 : POOL_THREADS / D;
-        const size_t smem = (size_t)rows * (D < POOL_THREADS ? D : POOL_THREADS) * sizeof(double);
-        pool_blocks_kernel<false><<<grid, POOL_THREADS, smem, (cudaStream_t)stream>>>(
-            v, L, H, D, block_size, nb, aligned, pooled);
-    }
-    return check_launch("wa_pool_blocks");
+    return pool_launch(x, L, pooled, nullptr, 0, nullptr, B, H, D, block_size, (cudaStream_t)stream);
 }
 
 extern "C" int wa_route_scores(const float *q_pooled, const float *k_pooled, int B, int H, int Nq,
