@@ -19,12 +19,15 @@
 // global memory, all roles leave their loops, tensor memory is released and the kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "wa_internal.cuh"
 
 namespace wa {
 namespace sm100 {
 
 constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
+constexpr int HALF = 64;             // key tokens per softmax / MMA pipeline step
 constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
 constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
@@ -207,6 +210,12 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -225,12 +234,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
 }
 
 // kind::f16 instruction descriptor: bf16 x bf16 -> f32, M = N = 128; `b_mn_major` for the V operand.
-__host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major) {
+__host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major, int n) {
     return (1u << 4)                 // D format f32
            | (1u << 7)               // A format bf16
            | (1u << 10)              // B format bf16
            | ((b_mn_major ? 1u : 0u) << 16)
-           | ((uint32_t)(TILE >> 3) << 17)
+           | ((uint32_t)(n >> 3) << 17)
            | ((uint32_t)(TILE >> 4) << 24);
 }
 
@@ -246,8 +255,8 @@ __device__ __forceinline__ float row_max32(const uint32_t (&r)[32], int col0, in
 }
 
 // 32 scores -> 32 probabilities packed as 16 bf16 pairs; returns their float32 sum.
-template <bool MASKED>
-__device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale, float m, int col0,
+template <bool MASKED, int OFF>
+__device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&pk)[32], float scale, float m, int col0,
                                             int valid) {
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -261,13 +270,13 @@ __device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&
         s0 += p0;
         s1 += p1;
         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-        pk[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+        pk[OFF + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
     }
     return s0 + s1;
 }
 
 struct Barriers {
-    uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done, o_free;
+    uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2], g_full, pv_done, o_done, o_free;
     uint32_t tmem_base;
     int item;
     int abort_flag;
@@ -295,8 +304,12 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_init(&bar->k_empty, 1);
         mbar_init(&bar->v_full, 1);
         mbar_init(&bar->v_empty, 1);
-        mbar_init(&bar->s_full, 1);
-        mbar_init(&bar->p_full, 128);
+        mbar_init(&bar->s_full[0], 1);
+        mbar_init(&bar->s_full[1], 1);
+        mbar_init(&bar->p_full[0], 128);
+        mbar_init(&bar->p_full[1], 128);
+        mbar_init(&bar->g_full, 1);
+        mbar_init(&bar->pv_done, 1);
         mbar_init(&bar->o_done, 1);
         mbar_init(&bar->o_free, 128);
         bar->abort_flag = 0;
@@ -318,7 +331,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     // phase parities, carried across work items
     // ("empty" parities start at 1: a fresh barrier counts as already released)
-    uint32_t ph_q = 0, ph_kf = 0, ph_ke = 1, ph_vf = 0, ph_ve = 1, ph_s = 0, ph_p = 0, ph_od = 0, ph_of = 0;
+    uint32_t ph_q = 0, ph_kf = 0, ph_ke = 1, ph_vf = 0, ph_ve = 1, ph_g = 0, ph_of = 0, ph_od = 0;
+    uint32_t ph_s = 0, ph_p = 0;   // one parity bit per S buffer
+    uint32_t pv_count = 0;   // PV products committed so far by this CTA (tracked identically by the MMA and softmax roles)
     const int lin_tiles = (p.Lc + TILE - 1) / TILE;
 
     while (true) {
@@ -385,50 +400,105 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
         } else if (warp == 1) {
             // ================= MMA issuer =================
-            if (lane == 0) {
-                constexpr uint32_t IDESC_QK = instr_desc(false), IDESC_PV = instr_desc(true);
-                bool ok = mbar_wait(&bar->q_full, ph_q, abort_flag, p.error_flag, 3);
-                const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
-                for (int t = 0; t < n_tiles && ok; ++t) {
-                    ok = mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4);
+            // A key tile is consumed as two 64-token halves with two S buffers in tensor memory, so the QK^T of
+            // half h+1 runs while the softmax warps work on half h; the PV of half h is issued right after.
+            {
+                // The whole warp runs this role so that operands stay warp-uniform; one elected lane issues.
+                const bool leader = elect_one();
+                constexpr uint32_t IDESC_QK = instr_desc(false, HALF), IDESC_PV = instr_desc(true, TILE),
+                                   IDESC_G = instr_desc(false, TILE);
+                bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full, ph_q, abort_flag, p.error_flag, 3));
+                // operand descriptors of the three fixed buffers; per-instruction steps are added to the address field
+                const uint64_t qd = smem_desc(smem_u32(q_s), 16, 1024), kd = smem_desc(smem_u32(k_s), 16, 1024),
+                               vd = smem_desc(smem_u32(v_s), HALF_BYTES, 1024);
+                int hcount = 0;
+                // the half whose PV is still to be issued
+                bool pend = false;
+                int pend_buf = 0, pend_hh = 0;
+                bool pend_first = false, pend_need_v = false, pend_last_of_tile = false, pend_wait_ofree = false,
+                     pend_last_of_phase = false;
+
+                auto issue_pv = [&]() -> bool {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[pend_buf], (ph_p >> pend_buf) & 1u, abort_flag, p.error_flag, 5)))
+                        return false;
+                    ph_p ^= 1u << pend_buf;
+                    WA_TRACE(5);
+                    if (pend_need_v) {
+                        if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full, ph_vf, abort_flag, p.error_flag, 6))) return false;
+                        ph_vf ^= 1u;
+                    }
+                    if (pend_wait_ofree) {
+                        // the sparse accumulator must have been read out before the linear branch reuses it
+                        if (!__all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7))) return false;
+                        ph_of ^= 1u;
+                    }
+                    tc_fence_after();
+                    if (leader) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            mma_ts(tmem_o, tmem_s + pend_buf * HALF + kk * 8,
+                                   vd + (uint64_t)((pend_hh * (HALF * 128) + kk * 2048) >> 4), IDESC_PV,
+                                   !(pend_first && kk == 0));
+                        tc_commit(&bar->pv_done);
+                        if (pend_last_of_tile) tc_commit(&bar->v_empty);
+                        if (pend_last_of_phase) tc_commit(&bar->o_done);
+                    }
+                    __syncwarp();
+                    WA_TRACE(7);
+                    pend = false;
+                    return true;
+                };
+
+                for (int t = 0; t < n_sel + lin_tiles && ok; ++t) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4));
                     if (!ok) break;
                     ph_kf ^= 1u;
                     WA_TRACE(1);
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                        mma_ss(tmem_s, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), IDESC_QK,
-                               kk > 0);
-                    }
-                    tc_commit(&bar->k_empty);
-                    tc_commit(&bar->s_full);
-                    WA_TRACE(4);
-                    if (t < n_sel + lin_tiles) {
-                        const bool first = (t == 0) || (t == n_sel);
-                        ok = mbar_wait(&bar->p_full, ph_p, abort_flag, p.error_flag, 5);
-                        if (!ok) break;
-                        ph_p ^= 1u;
-                        WA_TRACE(5);
-                        ok = mbar_wait(&bar->v_full, ph_vf, abort_flag, p.error_flag, 6);
-                        if (!ok) break;
-                        ph_vf ^= 1u;
-                        WA_TRACE(6);
-                        if (first && t > 0) {
-                            // the sparse accumulator must have been read out before the linear branch reuses it
-                            ok = mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7);
-                            if (!ok) break;
-                            ph_of ^= 1u;
-                        }
+                    const int nh = bar->valid[t & 3] > HALF ? 2 : 1;
+                    for (int hh = 0; hh < nh && ok; ++hh) {
+                        const int buf = hcount & 1;
                         tc_fence_after();
+                        if (leader) {
 #pragma unroll
-                        for (int kk = 0; kk < 8; ++kk)
-                            mma_ts(tmem_o, tmem_s + kk * 8, smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), IDESC_PV,
-                                   !(first && kk == 0));
-                        tc_commit(&bar->v_empty);
-                        WA_TRACE(7);
-                        const bool last = (t == n_sel - 1) || (t == n_sel + lin_tiles - 1);
-                        if (last) tc_commit(&bar->o_done);
+                            for (int kk = 0; kk < 8; ++kk) {
+                                const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                                mma_ss(tmem_s + buf * HALF, qd + (uint64_t)(off >> 4),
+                                       kd + (uint64_t)((hh * (HALF * 128) + off) >> 4), IDESC_QK, kk > 0);
+                            }
+                            tc_commit(&bar->s_full[buf]);
+                            if (hh == nh - 1) tc_commit(&bar->k_empty);
+                        }
+                        __syncwarp();
+                        WA_TRACE(4);
+                        if (pend) ok = issue_pv();
+                        pend = true;
+                        pend_buf = buf;
+                        pend_hh = hh;
+                        pend_first = (hh == 0) && (t == 0 || t == n_sel);
+                        pend_need_v = hh == 0;
+                        pend_last_of_tile = hh == nh - 1;
+                        pend_wait_ofree = pend_first && t == n_sel && n_sel > 0;
+                        pend_last_of_phase = (hh == nh - 1) && (t == n_sel - 1 || t == n_sel + lin_tiles - 1);
+                        ++hcount;
+                    }
+                }
+                if (ok && pend) ok = issue_pv();
+                if (ok) {
+                    // gate tile: S = Q Wg^T over all 128 columns (both S buffers are free once the last PV is queued)
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4));
+                    if (ok) {
+                        ph_kf ^= 1u;
+                        tc_fence_after();
+                        if (leader) {
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk) {
+                                const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                                mma_ss(tmem_s, qd + (uint64_t)(off >> 4), kd + (uint64_t)(off >> 4), IDESC_G, kk > 0);
+                            }
+                            tc_commit(&bar->k_empty);
+                            tc_commit(&bar->g_full);
+                        }
+                        __syncwarp();
                     }
                 }
             }
@@ -445,70 +515,78 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             bool ok = true;
             float inv_l_lin = 0.f;
 
+            int hcount = 0;
             for (int phase = 0; phase < 2 && ok; ++phase) {
                 const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_sel + lin_tiles;
                 float m_used = -INFINITY, l = 0.f;
+                bool first = true;
                 for (int t = t0; t < t1 && ok; ++t) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full, ph_s, abort_flag, p.error_flag, 8));
-                    if (!ok) break;
-                    ph_s ^= 1u;
-                    WA_TRACE(2);
-                    tc_fence_after();
-                    const int valid = bar->valid[t & 3];   // written by the producer before it armed this tile
-                    uint32_t ra[32], rb[32];
-                    // pass 1: row maximum over the valid columns, two 32-column loads in flight
-                    float mx = -INFINITY;
-#pragma unroll
-                    for (int c = 0; c < 4; c += 2) {
-                        TMEM_LD32(tmem_s + lane_addr + c * 32, ra);
-                        TMEM_LD32(tmem_s + lane_addr + c * 32 + 32, rb);
+                    int nh = 1;
+                    for (int hh = 0; hh < nh && ok; ++hh) {
+                        const int buf = hcount & 1;
+                        const uint32_t s_addr = tmem_s + lane_addr + buf * HALF;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], (ph_s >> buf) & 1u, abort_flag, p.error_flag, 8));
+                        if (!ok) break;
+                        ph_s ^= 1u << buf;
+                        WA_TRACE(2);
+                        tc_fence_after();
+                        const int valid_t = bar->valid[t & 3];   // written by the producer before it armed this tile
+                        nh = valid_t > HALF ? 2 : 1;
+                        const int valid = min(HALF, valid_t - hh * HALF);
+                        // one pass: the 64 scores of this row stay in registers
+                        uint32_t ra[32], rb[32];
+                        TMEM_LD32(s_addr, ra);
+                        TMEM_LD32(s_addr + 32, rb);
                         tmem_wait_ld();
-                        if (valid == TILE) {
-                            mx = fmaxf(mx, fmaxf(row_max32<false>(ra, 0, 0), row_max32<false>(rb, 0, 0)));
+                        float mx;
+                        if (valid == HALF) mx = fmaxf(row_max32<false>(ra, 0, 0), row_max32<false>(rb, 0, 0));
+                        else mx = fmaxf(row_max32<true>(ra, 0, valid), row_max32<true>(rb, 32, valid));
+                        mx *= p.scale_log2;
+                        WA_TRACE(8);
+                        // lazy rescale: only when the running maximum grows by more than 2^8
+                        float m_new = m_used;
+                        const bool grow = mx > m_used + 8.0f;
+                        if (grow) m_new = mx;
+                        if (__any_sync(0xffffffffu, grow && !first)) {
+                            // every PV issued so far must have landed before the accumulator is touched
+                            ok = __all_sync(0xffffffffu, mbar_wait(&bar->pv_done, (pv_count - 1u) & 1u, abort_flag,
+                                                                   p.error_flag, 9));
+                            if (!ok) break;
+                            tc_fence_after();
+                            const float f = (grow && !first) ? ex2(m_used - m_new) : 1.0f;
+                            l *= f;
+                            uint32_t ro[32];
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                TMEM_LD32(tmem_o + lane_addr + c * 32, ro);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) ro[j] = __float_as_uint(__uint_as_float(ro[j]) * f);
+                                TMEM_ST32(tmem_o + lane_addr + c * 32, ro);
+                            }
+                            tmem_wait_st();
+                        }
+                        m_used = m_new;
+                        // p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
+                        uint32_t pk[32];
+                        float sum;
+                        if (valid == HALF) {
+                            sum = exp_pack32<false, 0>(ra, pk, p.scale_log2, m_used, 0, 0);
+                            sum += exp_pack32<false, 16>(rb, pk, p.scale_log2, m_used, 0, 0);
                         } else {
-                            mx = fmaxf(mx, fmaxf(row_max32<true>(ra, c * 32, valid), row_max32<true>(rb, c * 32 + 32, valid)));
+                            sum = exp_pack32<true, 0>(ra, pk, p.scale_log2, m_used, 0, valid);
+                            sum += exp_pack32<true, 16>(rb, pk, p.scale_log2, m_used, 32, valid);
                         }
-                    }
-                    mx *= p.scale_log2;
-                    WA_TRACE(8);
-                    // lazy rescale: only when the running maximum grows by more than 2^8
-                    float m_new = m_used;
-                    const bool grow = mx > m_used + 8.0f;
-                    if (grow) m_new = mx;
-                    if (__any_sync(0xffffffffu, grow && t > t0)) {
-                        const float f = (grow && t > t0) ? ex2(m_used - m_new) : 1.0f;
-                        l *= f;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            TMEM_LD32(tmem_o + lane_addr + c * 32, ra);
-                            tmem_wait_ld();
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) * f);
-                            TMEM_ST32(tmem_o + lane_addr + c * 32, ra);
-                        }
+                        TMEM_ST32(s_addr, pk);
+                        l += sum;
                         tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(&bar->p_full[buf]);
+                        WA_TRACE(3);
+                        ++hcount;
+                        ++pv_count;
+                        first = false;
                     }
-                    m_used = m_new;
-                    // pass 2: p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
-                    float sum = 0.f;
-#pragma unroll
-                    for (int c = 0; c < 4; c += 2) {
-                        TMEM_LD32(tmem_s + lane_addr + c * 32, ra);
-                        TMEM_LD32(tmem_s + lane_addr + c * 32 + 32, rb);
-                        tmem_wait_ld();
-                        uint32_t pk[16];
-                        if (valid == TILE) sum += exp_pack32<false>(ra, pk, p.scale_log2, m_used, 0, 0);
-                        else sum += exp_pack32<true>(ra, pk, p.scale_log2, m_used, c * 32, valid);
-                        TMEM_ST16(tmem_s + lane_addr + c * 16, pk);
-                        if (valid == TILE) sum += exp_pack32<false>(rb, pk, p.scale_log2, m_used, 0, 0);
-                        else sum += exp_pack32<true>(rb, pk, p.scale_log2, m_used, c * 32 + 32, valid);
-                        TMEM_ST16(tmem_s + lane_addr + c * 16 + 16, pk);
-                    }
-                    l += sum;
-                    tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(&bar->p_full);
-                    WA_TRACE(3);
                 }
                 if (!ok) break;
                 // ---- end of a branch: read the accumulator ----
@@ -575,9 +653,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
                     for (int e = 0; e < 4; ++e) sp_next[e] = stash[e * TILE + row];   // in flight during the waits below
                 }
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full, ph_s, abort_flag, p.error_flag, 10));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->g_full, ph_g, abort_flag, p.error_flag, 10));
                 if (ok) {
-                    ph_s ^= 1u;
+                    ph_g ^= 1u;
                     tc_fence_after();
                     WA_TRACE(13);
 #pragma unroll
@@ -902,7 +980,10 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    const int grid = n_items < max_grid() ? n_items : max_grid();
+    int grid = n_items < max_grid() ? n_items : max_grid();
+#ifdef WA_SM100_TRACE
+    if (getenv("WA_SM100_ONE_CTA") && grid > max_grid() / 2) grid = max_grid() / 2;   // tuning aid: one CTA per SM
+#endif
     hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     return check_launch("wa_hsa_forward(tcgen05)");
 }
