@@ -28,11 +28,13 @@ namespace sm100 {
 
 constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
 constexpr int HALF = 64;             // key tokens per softmax / MMA pipeline step
-constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
+constexpr int THREADS = 320;         // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two threads per query row)
 constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
-constexpr int TMEM_COLS = 256;       // S: columns [0,128), O: [128,256)
-constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 /*alignment slack*/ + 1024 /*barriers, bias*/;
+constexpr int TMEM_COLS = 512;       // two S buffers: columns [0,128), [128,256); O: [256,384)
+constexpr int KV_STAGES = 3;         // shared-memory ring depth for K tiles
+constexpr int V_STAGES = 2;          // shared-memory ring depth for V tiles
+constexpr int SMEM_BYTES = (1 + KV_STAGES + V_STAGES) * TILE_BYTES + 1024 /*alignment slack*/ + 4096 /*barriers, bias, exchange*/;
 constexpr long long WAIT_CYCLES = 4000000000ll;
 
 // Optional event trace for kernel tuning (compile with -DWA_SM100_TRACE): CTA 0 appends
@@ -275,47 +277,54 @@ __device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&
     return s0 + s1;
 }
 
+static_assert(true, "");
 struct Barriers {
-    uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2], g_full, pv_done, o_done, o_free;
+    uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
+    uint64_t s_full[2], p_full[2], pv_done, o_done, o_free;
     uint32_t tmem_base;
     int item;
     int abort_flag;
-    int valid[4];   // real token count of the K tile in flight, ring indexed by tile number
+    int valid[8];       // real token count of the K tiles in flight, ring indexed by tile number
     float bias[TILE];   // gate bias
+    float xch[2][2][TILE];   // row-maximum exchange between the two threads of a row: [tile parity][half][row]
+    float lx[2][TILE];       // row-sum exchange at the end of a branch
 };
 
 // ---- the kernel ----------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
 hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
                      const __grid_constant__ CUtensorMap tm_vc, const __grid_constant__ CUtensorMap tm_w,
                      const __grid_constant__ CUtensorMap tm_out, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *q_s = smem, *k_s = smem + TILE_BYTES, *v_s = smem + 2 * TILE_BYTES;
-    Barriers *bar = reinterpret_cast<Barriers *>(smem + 3 * TILE_BYTES);
+    uint8_t *q_s = smem, *k_s = smem + TILE_BYTES, *v_s = smem + (1 + KV_STAGES) * TILE_BYTES;
+    Barriers *bar = reinterpret_cast<Barriers *>(smem + (1 + KV_STAGES + V_STAGES) * TILE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &bar->abort_flag;
 
     if (threadIdx.x == 0) {
         mbar_init(&bar->q_full, 1);
-        mbar_init(&bar->k_full, 1);
-        mbar_init(&bar->k_empty, 1);
-        mbar_init(&bar->v_full, 1);
-        mbar_init(&bar->v_empty, 1);
+        for (int i = 0; i < KV_STAGES; ++i) {
+            mbar_init(&bar->k_full[i], 1);
+            mbar_init(&bar->k_empty[i], 1);
+        }
+        for (int i = 0; i < V_STAGES; ++i) {
+            mbar_init(&bar->v_full[i], 1);
+            mbar_init(&bar->v_empty[i], 1);
+        }
         mbar_init(&bar->s_full[0], 1);
         mbar_init(&bar->s_full[1], 1);
-        mbar_init(&bar->p_full[0], 128);
-        mbar_init(&bar->p_full[1], 128);
-        mbar_init(&bar->g_full, 1);
+        mbar_init(&bar->p_full[0], 256);
+        mbar_init(&bar->p_full[1], 256);
         mbar_init(&bar->pv_done, 1);
         mbar_init(&bar->o_done, 1);
-        mbar_init(&bar->o_free, 128);
+        mbar_init(&bar->o_free, 256);
         bar->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x >= 64) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + TILE) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
                      "r"(TMEM_COLS) : "memory");
@@ -325,15 +334,15 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bar->tmem_base;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + TILE;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * TILE;   // S buffer b at tmem_s + b * TILE
     WA_TRACE_DECL;
     WA_TRACE(0);
 
-    // phase parities, carried across work items
-    // ("empty" parities start at 1: a fresh barrier counts as already released)
-    uint32_t ph_q = 0, ph_kf = 0, ph_ke = 1, ph_vf = 0, ph_ve = 1, ph_g = 0, ph_of = 0, ph_od = 0;
-    uint32_t ph_s = 0, ph_p = 0;   // one parity bit per S buffer
-    uint32_t pv_count = 0;   // PV products committed so far by this CTA (tracked identically by the MMA and softmax roles)
+    // State carried across work items.  Each role advances its own copy of the ring counters in the same way.
+    uint32_t kcount = 0, vcount = 0;   // K / V tiles produced (warp 0) or consumed (warp 1) so far
+    uint32_t ph_q = 0, ph_of = 0, ph_od = 0;
+    uint32_t ph_s = 0, ph_p = 0;       // one parity bit per S buffer
+    uint32_t pv_count = 0;             // PV products requested so far (softmax role)
     const int lin_tiles = (p.Lc + TILE - 1) / TILE;
 
     while (true) {
@@ -348,8 +357,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const long long meta = item;   // (b*H + h)*Nq + qb
         const int n_sel = max(0, min(p.num[meta], p.Nkv));
         const int32_t *ids = p.index + meta * (long long)p.Nkv;
-        const int n_tiles = n_sel + lin_tiles + 1;   // sparse, linear, gate
-        WA_STATS_ITEM(n_tiles);
+        const int n_kv = n_sel + lin_tiles;   // tiles with a softmax; tile n_kv is the gate product
+        WA_STATS_ITEM(n_kv + 1);
 
         if (warp == 0) {
             // ================= TMA producer =================
@@ -358,238 +367,207 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 tma_load_4d(q_s, &tm_q, &bar->q_full, 0, h, qb * TILE, b);
                 tma_load_4d(q_s + HALF_BYTES, &tm_q, &bar->q_full, 64, h, qb * TILE, b);
                 bool ok = true;
-                for (int t = 0; t < n_tiles && ok; ++t) {
-                    // K-type operand of tile t: the buffer is free once the previous product that read it completed
-                    ok = mbar_wait(&bar->k_empty, ph_ke, abort_flag, p.error_flag, 1);
+                for (int t = 0; t <= n_kv && ok; ++t) {
+                    const uint32_t ks = kcount % KV_STAGES, kpar = ((kcount / KV_STAGES) & 1u) ^ 1u;
+                    ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, p.error_flag, 1);
                     if (!ok) break;
-                    ph_ke ^= 1u;
+                    ++kcount;
+                    uint8_t *kdst = k_s + ks * TILE_BYTES;
                     int id = 0;
                     if (t < n_sel) {
                         id = max(0, min(ids[t], p.Nkv - 1));
-                        bar->valid[t & 3] = min(TILE, p.Lkv - id * TILE);
+                        bar->valid[t & 7] = min(TILE, p.Lkv - id * TILE);
                     } else {
-                        bar->valid[t & 3] = min(TILE, p.Lc - (t - n_sel) * TILE);
+                        bar->valid[t & 7] = min(TILE, p.Lc - (t - n_sel) * TILE);
                     }
-                    mbar_expect_tx(&bar->k_full, TILE_BYTES);
+                    mbar_expect_tx(&bar->k_full[ks], TILE_BYTES);
                     if (t < n_sel) {
-                        tma_load_4d(k_s, &tm_k, &bar->k_full, 0, h, id * TILE, b);
-                        tma_load_4d(k_s + HALF_BYTES, &tm_k, &bar->k_full, 64, h, id * TILE, b);
-                    } else if (t < n_sel + lin_tiles) {
+                        tma_load_4d(kdst, &tm_k, &bar->k_full[ks], 0, h, id * TILE, b);
+                        tma_load_4d(kdst + HALF_BYTES, &tm_k, &bar->k_full[ks], 64, h, id * TILE, b);
+                    } else if (t < n_kv) {
                         const int c = (t - n_sel) * TILE;
-                        tma_load_4d(k_s, &tm_kc, &bar->k_full, 0, h, c, b);
-                        tma_load_4d(k_s + HALF_BYTES, &tm_kc, &bar->k_full, 64, h, c, b);
+                        tma_load_4d(kdst, &tm_kc, &bar->k_full[ks], 0, h, c, b);
+                        tma_load_4d(kdst + HALF_BYTES, &tm_kc, &bar->k_full[ks], 64, h, c, b);
                     } else {
-                        tma_load_2d(k_s, &tm_w, &bar->k_full, 0, 0);
-                        tma_load_2d(k_s + HALF_BYTES, &tm_w, &bar->k_full, 64, 0);
+                        tma_load_2d(kdst, &tm_w, &bar->k_full[ks], 0, 0);
+                        tma_load_2d(kdst + HALF_BYTES, &tm_w, &bar->k_full[ks], 64, 0);
                     }
-                    if (t < n_sel + lin_tiles) {
-                        ok = mbar_wait(&bar->v_empty, ph_ve, abort_flag, p.error_flag, 2);
+                    if (t < n_kv) {
+                        const uint32_t vs = vcount % V_STAGES, vpar = ((vcount / V_STAGES) & 1u) ^ 1u;
+                        ok = mbar_wait(&bar->v_empty[vs], vpar, abort_flag, p.error_flag, 2);
                         if (!ok) break;
-                        ph_ve ^= 1u;
-                        mbar_expect_tx(&bar->v_full, TILE_BYTES);
+                        ++vcount;
+                        uint8_t *vdst = v_s + vs * TILE_BYTES;
+                        mbar_expect_tx(&bar->v_full[vs], TILE_BYTES);
                         if (t < n_sel) {
-                            tma_load_4d(v_s, &tm_v, &bar->v_full, 0, h, id * TILE, b);
-                            tma_load_4d(v_s + HALF_BYTES, &tm_v, &bar->v_full, 64, h, id * TILE, b);
+                            tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * TILE, b);
+                            tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * TILE, b);
                         } else {
                             const int c = (t - n_sel) * TILE;
-                            tma_load_4d(v_s, &tm_vc, &bar->v_full, 0, h, c, b);
-                            tma_load_4d(v_s + HALF_BYTES, &tm_vc, &bar->v_full, 64, h, c, b);
+                            tma_load_4d(vdst, &tm_vc, &bar->v_full[vs], 0, h, c, b);
+                            tma_load_4d(vdst + HALF_BYTES, &tm_vc, &bar->v_full[vs], 64, h, c, b);
                         }
                     }
                 }
             }
         } else if (warp == 1) {
             // ================= MMA issuer =================
-            // A key tile is consumed as two 64-token halves with two S buffers in tensor memory, so the QK^T of
-            // half h+1 runs while the softmax warps work on half h; the PV of half h is issued right after.
+            // Issue order QK(0), QK(1), PV(0), QK(2), PV(1), ...: the score product of tile t+1 lands in the
+            // other S buffer while the softmax warps work on tile t.  The whole warp runs this role so that
+            // operands stay warp-uniform; one elected lane issues.
             {
-                // The whole warp runs this role so that operands stay warp-uniform; one elected lane issues.
                 const bool leader = elect_one();
-                constexpr uint32_t IDESC_QK = instr_desc(false, HALF), IDESC_PV = instr_desc(true, TILE),
-                                   IDESC_G = instr_desc(false, TILE);
+                constexpr uint32_t IDESC_QK = instr_desc(false, TILE), IDESC_PV = instr_desc(true, TILE);
+                const uint64_t qd = smem_desc(smem_u32(q_s), 16, 1024);
                 bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full, ph_q, abort_flag, p.error_flag, 3));
-                // operand descriptors of the three fixed buffers; per-instruction steps are added to the address field
-                const uint64_t qd = smem_desc(smem_u32(q_s), 16, 1024), kd = smem_desc(smem_u32(k_s), 16, 1024),
-                               vd = smem_desc(smem_u32(v_s), HALF_BYTES, 1024);
-                int hcount = 0;
-                // the half whose PV is still to be issued
-                bool pend = false;
-                int pend_buf = 0, pend_hh = 0;
-                bool pend_first = false, pend_need_v = false, pend_last_of_tile = false, pend_wait_ofree = false,
-                     pend_last_of_phase = false;
 
-                auto issue_pv = [&]() -> bool {
-                    if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[pend_buf], (ph_p >> pend_buf) & 1u, abort_flag, p.error_flag, 5)))
-                        return false;
-                    ph_p ^= 1u << pend_buf;
-                    WA_TRACE(5);
-                    if (pend_need_v) {
-                        if (!__all_sync(0xffffffffu, mbar_wait(&bar->v_full, ph_vf, abort_flag, p.error_flag, 6))) return false;
-                        ph_vf ^= 1u;
+                auto issue_qk = [&](int t) -> bool {
+                    const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
+                    ++kcount;
+                    WA_TRACE(1);
+                    tc_fence_after();
+                    if (leader) {
+                        const uint64_t kd = smem_desc(smem_u32(k_s + ks * TILE_BYTES), 16, 1024);
+                        const uint32_t d = tmem_s + (t & 1) * TILE;
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) {
+                            const uint64_t off = (uint64_t)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
+                            mma_ss(d, qd + off, kd + off, IDESC_QK, kk > 0);
+                        }
+                        tc_commit(&bar->k_empty[ks]);
+                        tc_commit(&bar->s_full[t & 1]);
                     }
-                    if (pend_wait_ofree) {
+                    __syncwarp();
+                    WA_TRACE(4);
+                    return true;
+                };
+
+                if (ok) ok = issue_qk(0);
+                for (int t = 0; t < n_kv && ok; ++t) {
+                    ok = issue_qk(t + 1);
+                    if (!ok) break;
+                    const int buf = t & 1;
+                    const bool first = (t == 0) || (t == n_sel);
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (ph_p >> buf) & 1u, abort_flag, p.error_flag, 5));
+                    if (!ok) break;
+                    ph_p ^= 1u << buf;
+                    WA_TRACE(5);
+                    const uint32_t vs = vcount % V_STAGES, vpar = (vcount / V_STAGES) & 1u;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, p.error_flag, 6));
+                    if (!ok) break;
+                    ++vcount;
+                    if (first && t > 0) {
                         // the sparse accumulator must have been read out before the linear branch reuses it
-                        if (!__all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7))) return false;
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7));
+                        if (!ok) break;
                         ph_of ^= 1u;
                     }
                     tc_fence_after();
                     if (leader) {
+                        const uint64_t vd = smem_desc(smem_u32(v_s + vs * TILE_BYTES), HALF_BYTES, 1024);
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            mma_ts(tmem_o, tmem_s + pend_buf * HALF + kk * 8,
-                                   vd + (uint64_t)((pend_hh * (HALF * 128) + kk * 2048) >> 4), IDESC_PV,
-                                   !(pend_first && kk == 0));
+                        for (int kk = 0; kk < 8; ++kk)
+                            mma_ts(tmem_o, tmem_s + buf * TILE + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
+                                   !(first && kk == 0));
+                        tc_commit(&bar->v_empty[vs]);
                         tc_commit(&bar->pv_done);
-                        if (pend_last_of_tile) tc_commit(&bar->v_empty);
-                        if (pend_last_of_phase) tc_commit(&bar->o_done);
+                        if (t == n_sel - 1 || t == n_kv - 1) tc_commit(&bar->o_done);
                     }
                     __syncwarp();
                     WA_TRACE(7);
-                    pend = false;
-                    return true;
-                };
-
-                for (int t = 0; t < n_sel + lin_tiles && ok; ++t) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4));
-                    if (!ok) break;
-                    ph_kf ^= 1u;
-                    WA_TRACE(1);
-                    const int nh = bar->valid[t & 3] > HALF ? 2 : 1;
-                    for (int hh = 0; hh < nh && ok; ++hh) {
-                        const int buf = hcount & 1;
-                        tc_fence_after();
-                        if (leader) {
-#pragma unroll
-                            for (int kk = 0; kk < 8; ++kk) {
-                                const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                                mma_ss(tmem_s + buf * HALF, qd + (uint64_t)(off >> 4),
-                                       kd + (uint64_t)((hh * (HALF * 128) + off) >> 4), IDESC_QK, kk > 0);
-                            }
-                            tc_commit(&bar->s_full[buf]);
-                            if (hh == nh - 1) tc_commit(&bar->k_empty);
-                        }
-                        __syncwarp();
-                        WA_TRACE(4);
-                        if (pend) ok = issue_pv();
-                        pend = true;
-                        pend_buf = buf;
-                        pend_hh = hh;
-                        pend_first = (hh == 0) && (t == 0 || t == n_sel);
-                        pend_need_v = hh == 0;
-                        pend_last_of_tile = hh == nh - 1;
-                        pend_wait_ofree = pend_first && t == n_sel && n_sel > 0;
-                        pend_last_of_phase = (hh == nh - 1) && (t == n_sel - 1 || t == n_sel + lin_tiles - 1);
-                        ++hcount;
-                    }
-                }
-                if (ok && pend) ok = issue_pv();
-                if (ok) {
-                    // gate tile: S = Q Wg^T over all 128 columns (both S buffers are free once the last PV is queued)
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->k_full, ph_kf, abort_flag, p.error_flag, 4));
-                    if (ok) {
-                        ph_kf ^= 1u;
-                        tc_fence_after();
-                        if (leader) {
-#pragma unroll
-                            for (int kk = 0; kk < 8; ++kk) {
-                                const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                                mma_ss(tmem_s, qd + (uint64_t)(off >> 4), kd + (uint64_t)(off >> 4), IDESC_G, kk > 0);
-                            }
-                            tc_commit(&bar->k_empty);
-                            tc_commit(&bar->g_full);
-                        }
-                        __syncwarp();
-                    }
                 }
             }
             ph_q ^= 1u;
         } else {
-            // ================= softmax / epilogue: one thread per query row =================
+            // ================= softmax / epilogue: two threads per query row (64 score columns each) ==========
+            // Warps 2..5 own columns [0,64), warps 6..9 columns [64,128) of the same rows (a warp may only touch
+            // the 32 tensor-memory lanes selected by warp % 4).  The two threads of a row meet at a 64-thread
+            // named barrier once per tile to agree on the row maximum.
+            const int half = (warp - 2) >> 2;
             const int row = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
+            const int pair_bar = 2 + (warp & 3);
             const int token = qb * TILE + row;
             const bool row_ok = token < p.Lq;
-            const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE;
+            const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE + half * HALF;
             const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
-            uint4 *stash = p.stash + (size_t)blockIdx.x * (16 * TILE);
+            uint4 *stash = p.stash + (size_t)blockIdx.x * (16 * TILE) + (size_t)half * (8 * TILE);
+            const int gbuf = n_kv & 1;
             bool ok = true;
             float inv_l_lin = 0.f;
 
-            int hcount = 0;
             for (int phase = 0; phase < 2 && ok; ++phase) {
-                const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_sel + lin_tiles;
+                const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_kv;
                 float m_used = -INFINITY, l = 0.f;
-                bool first = true;
                 for (int t = t0; t < t1 && ok; ++t) {
-                    int nh = 1;
-                    for (int hh = 0; hh < nh && ok; ++hh) {
-                        const int buf = hcount & 1;
-                        const uint32_t s_addr = tmem_s + lane_addr + buf * HALF;
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], (ph_s >> buf) & 1u, abort_flag, p.error_flag, 8));
+                    const int buf = t & 1;
+                    const uint32_t s_addr = tmem_s + buf * TILE + lane_addr;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], (ph_s >> buf) & 1u, abort_flag, p.error_flag, 8));
+                    if (!ok) break;
+                    ph_s ^= 1u << buf;
+                    WA_TRACE(2);
+                    tc_fence_after();
+                    // columns of this thread that hold real tokens (the producer wrote the tile's count)
+                    const int valid = max(0, min(HALF, bar->valid[t & 7] - half * HALF));
+                    uint32_t r0[32], r1[32];
+                    TMEM_LD32(s_addr + half * HALF, r0);
+                    TMEM_LD32(s_addr + half * HALF + 32, r1);
+                    tmem_wait_ld();
+                    float mx;
+                    if (valid == HALF) mx = fmaxf(row_max32<false>(r0, 0, 0), row_max32<false>(r1, 0, 0));
+                    else mx = fmaxf(row_max32<true>(r0, 0, valid), row_max32<true>(r1, 32, valid));
+                    bar->xch[t & 1][half][row] = mx;
+                    asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                    mx = fmaxf(mx, bar->xch[t & 1][half ^ 1][row]) * p.scale_log2;
+                    WA_TRACE(8);
+                    // lazy rescale: only when the running maximum grows by more than 2^8
+                    float m_new = m_used;
+                    const bool grow = mx > m_used + 8.0f;
+                    if (grow) m_new = mx;
+                    if (__any_sync(0xffffffffu, grow && t > t0)) {
+                        // every PV requested so far must have landed before the accumulator is touched
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->pv_done, (pv_count - 1u) & 1u, abort_flag, p.error_flag, 9));
                         if (!ok) break;
-                        ph_s ^= 1u << buf;
-                        WA_TRACE(2);
                         tc_fence_after();
-                        const int valid_t = bar->valid[t & 3];   // written by the producer before it armed this tile
-                        nh = valid_t > HALF ? 2 : 1;
-                        const int valid = min(HALF, valid_t - hh * HALF);
-                        // one pass: the 64 scores of this row stay in registers
-                        uint32_t ra[32], rb[32];
-                        TMEM_LD32(s_addr, ra);
-                        TMEM_LD32(s_addr + 32, rb);
-                        tmem_wait_ld();
-                        float mx;
-                        if (valid == HALF) mx = fmaxf(row_max32<false>(ra, 0, 0), row_max32<false>(rb, 0, 0));
-                        else mx = fmaxf(row_max32<true>(ra, 0, valid), row_max32<true>(rb, 32, valid));
-                        mx *= p.scale_log2;
-                        WA_TRACE(8);
-                        // lazy rescale: only when the running maximum grows by more than 2^8
-                        float m_new = m_used;
-                        const bool grow = mx > m_used + 8.0f;
-                        if (grow) m_new = mx;
-                        if (__any_sync(0xffffffffu, grow && !first)) {
-                            // every PV issued so far must have landed before the accumulator is touched
-                            ok = __all_sync(0xffffffffu, mbar_wait(&bar->pv_done, (pv_count - 1u) & 1u, abort_flag,
-                                                                   p.error_flag, 9));
-                            if (!ok) break;
-                            tc_fence_after();
-                            const float f = (grow && !first) ? ex2(m_used - m_new) : 1.0f;
-                            l *= f;
-                            uint32_t ro[32];
+                        const float f = (grow && t > t0) ? ex2(m_used - m_new) : 1.0f;
+                        l *= f;
+                        uint32_t ro[32];
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                TMEM_LD32(tmem_o + lane_addr + c * 32, ro);
-                                tmem_wait_ld();
+                        for (int c = 0; c < 2; ++c) {
+                            TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, ro);
+                            tmem_wait_ld();
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) ro[j] = __float_as_uint(__uint_as_float(ro[j]) * f);
-                                TMEM_ST32(tmem_o + lane_addr + c * 32, ro);
-                            }
-                            tmem_wait_st();
+                            for (int j = 0; j < 32; ++j) ro[j] = __float_as_uint(__uint_as_float(ro[j]) * f);
+                            TMEM_ST32(tmem_o + lane_addr + half * HALF + c * 32, ro);
                         }
-                        m_used = m_new;
-                        // p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
-                        uint32_t pk[32];
-                        float sum;
-                        if (valid == HALF) {
-                            sum = exp_pack32<false, 0>(ra, pk, p.scale_log2, m_used, 0, 0);
-                            sum += exp_pack32<false, 16>(rb, pk, p.scale_log2, m_used, 0, 0);
-                        } else {
-                            sum = exp_pack32<true, 0>(ra, pk, p.scale_log2, m_used, 0, valid);
-                            sum += exp_pack32<true, 16>(rb, pk, p.scale_log2, m_used, 32, valid);
-                        }
-                        TMEM_ST32(s_addr, pk);
-                        l += sum;
                         tmem_wait_st();
-                        tc_fence_before();
-                        mbar_arrive(&bar->p_full[buf]);
-                        WA_TRACE(3);
-                        ++hcount;
-                        ++pv_count;
-                        first = false;
                     }
+                    m_used = m_new;
+                    // p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
+                    uint32_t pk[32];
+                    float sum;
+                    if (valid == HALF) {
+                        sum = exp_pack32<false, 0>(r0, pk, p.scale_log2, m_used, 0, 0);
+                        sum += exp_pack32<false, 16>(r1, pk, p.scale_log2, m_used, 0, 0);
+                    } else {
+                        sum = exp_pack32<true, 0>(r0, pk, p.scale_log2, m_used, 0, valid);
+                        sum += exp_pack32<true, 16>(r1, pk, p.scale_log2, m_used, 32, valid);
+                    }
+                    TMEM_ST32(s_addr + half * 32, pk);
+                    l += sum;
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bar->p_full[buf]);
+                    WA_TRACE(3);
+                    ++pv_count;
                 }
                 if (!ok) break;
-                // ---- end of a branch: read the accumulator ----
+                // ---- end of a branch: total row sum, then read the accumulator ----
+                bar->lx[half][row] = l;
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                l += bar->lx[half ^ 1][row];
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // lx is reused by the next branch
                 if (t1 > t0) {
                     ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
                     if (!ok) break;
@@ -601,12 +579,12 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
                 if (phase == 0) {
                     // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park it
-                    // in this CTA's stash, laid out [16-byte chunk][thread] so that warps store and reload whole lines.
+                    // in this CTA's stash, laid out [16-byte chunk][row] so that warps store and reload whole lines.
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
                         if (t1 > t0) {
-                            TMEM_LD32(tmem_o + lane_addr + c * 32, r);
+                            TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, r);
                             tmem_wait_ld();
                         } else {
 #pragma unroll
@@ -636,14 +614,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             }
                         }
                     }
-                    if (p.lse_sparse && row_ok) p.lse_sparse[lse_off] = lse;
+                    if (p.lse_sparse && row_ok && half == 0) p.lse_sparse[lse_off] = lse;
                     if (t1 > t0) {
                         tc_fence_before();
                         mbar_arrive(&bar->o_free);
                     }
                 } else {
                     inv_l_lin = inv_l;
-                    if (p.lse_linear && row_ok) p.lse_linear[lse_off] = lse;
+                    if (p.lse_linear && row_ok && half == 0) p.lse_linear[lse_off] = lse;
                 }
             }
             // ---- gate tile + combine ----
@@ -651,22 +629,22 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 uint4 sp_next[4];
                 if (!p.part_linear) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) sp_next[e] = stash[e * TILE + row];   // in flight during the waits below
+                    for (int e = 0; e < 4; ++e) sp_next[e] = stash[e * TILE + row];   // in flight during the wait below
                 }
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->g_full, ph_g, abort_flag, p.error_flag, 10));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], (ph_s >> gbuf) & 1u, abort_flag, p.error_flag, 10));
                 if (ok) {
-                    ph_g ^= 1u;
+                    ph_s ^= 1u << gbuf;
                     tc_fence_after();
                     WA_TRACE(13);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t g[32], o[32];
-                        TMEM_LD32(tmem_s + lane_addr + c * 32, g);
-                        TMEM_LD32(tmem_o + lane_addr + c * 32, o);
+                        TMEM_LD32(tmem_s + gbuf * TILE + lane_addr + half * HALF + c * 32, g);
+                        TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, o);
                         uint4 sp_cur[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) sp_cur[e] = sp_next[e];
-                        if (!p.part_linear && c < 3) {
+                        if (!p.part_linear && c < 1) {
 #pragma unroll
                             for (int e = 0; e < 4; ++e) sp_next[e] = stash[((c + 1) * 4 + e) * TILE + row];
                         }
@@ -686,7 +664,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             // 16-byte chunk `cc` of this row inside the swizzled 128 x 128 bf16 tile that held Q
-                            const int cc = c * 4 + (j >> 3);
+                            const int cc = half * 8 + c * 4 + (j >> 3);
                             uint4 *slot = reinterpret_cast<uint4 *>(q_s + (cc >> 3) * HALF_BYTES + row * 128 +
                                                                     (((cc & 7) ^ (row & 7)) << 4));
                             const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp_cur[j >> 3]);
@@ -697,7 +675,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const int col = c * 32 + j + 2 * e;
+                                const int col = half * HALF + c * 32 + j + 2 * e;
                                 float z0, z1;
                                 if (p.has_gate) {
                                     z0 = __uint_as_float(g[j + 2 * e]) + bar->bias[col];
@@ -724,7 +702,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 // Hand the staged tile to the TMA store (rows beyond q_len are clipped by the tensor map).  Every
                 // softmax thread takes part in the barrier whether or not its waits succeeded.
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 if (threadIdx.x == 64 && ok) {
                     tma_store_4d(&tm_out, q_s, 0, h, qb * TILE, b);
                     tma_store_4d(&tm_out, q_s + HALF_BYTES, 64, h, qb * TILE, b);
@@ -869,7 +847,7 @@ static int max_grid() {
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         sms <= 0)
         sms = 160;
-    return 2 * sms;
+    return sms;
 }
 
 struct TunedWs {
