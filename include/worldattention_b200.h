@@ -85,6 +85,21 @@ int wa_route_select(const float *block_attn, int B, int H, int Nq, int Nkv, doub
                     int32_t *num, uint8_t *mask, float *thresholds, float *gini_scratch,
                     void *stream);
 
+/* The same selection as wa_route_select for callers that cannot allocate device memory where
+ * routing runs (a server that partitions HBM once at start-up, a plugin whose host owns the
+ * allocator, code that must avoid the device-wide synchronisation cudaMalloc implies).  It has no
+ * counterpart in the reference.  The Gini scratch lives in a device array inside the library:
+ * at most WA_ROUTE_SELECT_STATIC_MAX_ROWS rows (B*H*Nq); larger problems are rejected with
+ * WA_ERR_UNSUPPORTED.  The library calls no allocation routine here.  The first call on each
+ * device looks up the array's device address (one cudaGetSymbolAddress); make that first call
+ * before any stream capture.  All calls on a device share the one array and it keeps the last
+ * call's contents, so two calls that can overlap on the GPU (different streams) race: serialise
+ * them.  Nothing in the array needs clearing between calls. */
+#define WA_ROUTE_SELECT_STATIC_MAX_ROWS 65536
+int wa_route_select_static(const float *block_attn, int B, int H, int Nq, int Nkv, double tau_min,
+                           double tau_max, const int32_t *fixed_num_per_head, int32_t *index,
+                           int32_t *num, uint8_t *mask, float *thresholds, void *stream);
+
 /* map_to_index (block_sparse_triton.py:20-57).  Byte mask -> ascending ids (-1 filled) + count. */
 int wa_map_to_index(const uint8_t *mask, int B, int H, int Nq, int Nkv, int32_t *index,
                     int32_t *num, void *stream);

@@ -427,3 +427,57 @@ extern "C" int wa_map_to_index(const uint8_t *mask, int B, int H, int Nq, int Nk
                           (cudaStream_t)stream>>>(mask, rows, Nkv, index, num);
     return check_launch("wa_map_to_index");
 }
+
+// ------------------------------------------------------------------------------------------------
+// wa_route_select_static: the same selection with its per-row scratch inside the library.
+//
+// For callers that are not allowed to allocate device memory at the point where routing runs: a
+// serving process that hands out its whole HBM budget at start-up and forbids later allocation, a
+// plugin whose host owns the allocator, or a loop that must not call anything that can synchronise
+// the device (cudaMalloc / cudaFree do).  Such a caller has nowhere to get the B*H*Nq floats of
+// Gini scratch from, so this entry point keeps them in a file-scope device array of fixed size.
+// Every GPU that loads the library carries that array (256 KiB) until the process exits.
+// ------------------------------------------------------------------------------------------------
+namespace wa {
+constexpr int STATIC_SELECT_MAX_ROWS = WA_ROUTE_SELECT_STATIC_MAX_ROWS;
+static __device__ __align__(256) float g_select_scratch[STATIC_SELECT_MAX_ROWS];
+
+// The array's name is only a host-side handle; the device address comes from the runtime, once
+// per device, with that device current.
+static float *select_scratch_address() {
+    constexpr int MAX_DEVICES = 64;
+    static float *cached[MAX_DEVICES] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        fail(WA_ERR_DEVICE, "wa_route_select_static: no usable current device");
+        return nullptr;
+    }
+    if (!cached[dev]) {
+        float *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_select_scratch);
+        if (e != cudaSuccess || !ptr) {
+            fail((int)e, "wa_route_select_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+}  // namespace wa
+
+extern "C" int wa_route_select_static(const float *block_attn, int B, int H, int Nq, int Nkv, double tau_min,
+                                      double tau_max, const int32_t *fixed_num_per_head, int32_t *index,
+                                      int32_t *num, uint8_t *mask, float *thresholds, void *stream) {
+    WA_REQUIRE(block_attn && index && num && thresholds, WA_ERR_ARG, "wa_route_select_static: null pointer");
+    WA_REQUIRE(B > 0 && H > 0 && Nq > 0 && Nkv > 0, WA_ERR_ARG, "wa_route_select_static: sizes must be positive");
+    const long long rows = (long long)B * H * Nq;
+    WA_REQUIRE(rows <= STATIC_SELECT_MAX_ROWS, WA_ERR_UNSUPPORTED,
+               "wa_route_select_static: %lld rows (B*H*Nq) exceed the built-in scratch of %d rows; "
+               "use wa_route_select with caller-provided scratch",
+               rows, STATIC_SELECT_MAX_ROWS);
+    float *scratch = select_scratch_address();
+    if (!scratch) return WA_ERR_DEVICE;
+    // Nothing in the scratch has to start at zero: pass A writes every row's Gini term before pass B reads it.
+    return route_select_launch(block_attn, B, H, Nq, Nkv, tau_min, tau_max, fixed_num_per_head, index, num, mask,
+                               thresholds, scratch, (cudaStream_t)stream);
+}
