@@ -225,6 +225,77 @@ def workload_config(name, n_gpus):
 
 
 # ------------------------------------------------------------------------------------------------
+# HKV retrieval (BASELINE config 3): per-head page scoring, top-16, gather from the HBM-hot pool
+# ------------------------------------------------------------------------------------------------
+def bench_hkv(dev, steps=5, layers=30, pages_total=480, pages_hot=64, topk=16):
+    """Score 480 page centroids per (layer, head), take the top-16 per head, gather those pages.
+
+    The hot pool holds `pages_hot` pages per layer in HBM (`[layers, pages, 1560, H, D]` bf16, K and V);
+    a selected page id maps to hot slot `id % pages_hot` (a synthetic residency map: the timing is that of
+    a retrieval whose pages are all resident).  Keys are re-rotated in flight, values copied verbatim.
+    Returns GB/s of the gather kernel against the algorithmic bytes (read + write of every selected page).
+    """
+    import worldattention_b200 as wa
+    from worldattention_b200.hkv.install import gather_pages, per_head_records
+    from worldattention_b200.hkv.retrieval import score_and_topk
+    g = torch.Generator(device="cpu").manual_seed(3)
+    page_tokens, row = FRAME_TOKENS, HEADS * HEAD_DIM
+    pool = torch.empty((2, layers, pages_hot, page_tokens, HEADS, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    for i in range(2):
+        for l in range(layers):                      # seeded on the device side in slices to bound host time
+            pool[i, l].normal_(0, 1)
+    offsets = torch.randn((layers, pages_total, row), generator=g) * 0.5
+    centroids = offsets.to(dev)                      # page index: per-page mean key = per-page offset
+    query = torch.randn((row,), generator=g).to(dev)
+    cache = torch.zeros((2, layers, topk * page_tokens, HEADS, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    nt = wa.hkv.temporal_complex_dims(HEAD_DIM)
+    rot = torch.randn((topk, nt, 2), generator=g)
+    rot = (rot / rot.norm(dim=-1, keepdim=True)).to(dev).contiguous()
+    esz = 2
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gather_ms, total_ms = [], []
+    for it in range(steps + 2):
+        torch.cuda.synchronize()
+        ev0.record()
+        ids = torch.empty((layers, HEADS, topk), dtype=torch.int32, device=dev)
+        for l in range(layers):
+            _, top, _ = score_and_topk(query, centroids[l], topk, groups=HEADS)
+            ids[l] = top
+        ids_h = ids.cpu().numpy()
+        chron = np.sort(ids_h, axis=-1)              # install in chronological (page id) order
+        slots = chron % pages_hot
+        rot_ids = np.broadcast_to(np.arange(topk, dtype=np.int32), slots.shape)
+        common = dict(src_page_stride=page_tokens * row * esz, src_layer_stride=pages_hot * page_tokens * row * esz,
+                      dst_layer_stride=topk * page_tokens * row * esz, page_tokens=page_tokens, heads=HEADS,
+                      head_dim=HEAD_DIM, elem_size=esz)
+        rec = np.concatenate([
+            per_head_records(slots, src_base=pool[0].data_ptr(), dst_base=cache[0].data_ptr(), rot=rot_ids, **common),
+            per_head_records(slots, src_base=pool[1].data_ptr(), dst_base=cache[1].data_ptr(), rot=None, **common)])
+        rec_dev = torch.from_numpy(rec.view(np.uint8).reshape(-1)).to(dev)
+        ev2.record()
+        gather_pages(rec, max_tokens=page_tokens, row_elems=HEAD_DIM, head_dim=HEAD_DIM, dtype=torch.bfloat16,
+                     device=dev, rotations=rot, n_temporal=nt, records_dev=rec_dev)
+        ev3.record()
+        ev1.record()
+        ev1.synchronize()
+        if it >= 2:
+            gather_ms.append(ev2.elapsed_time(ev3))
+            total_ms.append(ev0.elapsed_time(ev1))
+    moved = 2.0 * 2 * layers * HEADS * topk * page_tokens * HEAD_DIM * esz     # K and V, read + write
+    # spot check: first selected page of layer 0 / head 0, values are copied verbatim
+    src0 = pool[1, 0, int(slots[0, 0, 0]), :, 0]
+    ok = bool(torch.equal(cache[1, 0, :page_tokens, 0], src0))
+    _, peak_gbs, _ = measured_peaks()
+    gbs = moved / (float(np.mean(gather_ms)) * 1e-3) / 1e9
+    return {"workload": f"c3: {layers} layers x {HEADS} heads, {pages_total} page centroids scored per head, top-{topk} pages "
+                        f"of {page_tokens} tokens gathered from a {pages_hot}-page HBM-hot pool, keys re-rotated",
+            "gather_ms": float(np.mean(gather_ms)), "gather_gbs": gbs, "hbm_peak_gbs": peak_gbs,
+            "gather_frac_of_hbm": gbs / peak_gbs, "bytes_moved": moved, "retrieval_ms_end_to_end": float(np.mean(total_ms)),
+            "records": int(rec.shape[0]), "verbatim_value_check": ok}
+
+
+# ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
 def main():
@@ -236,6 +307,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
+    ap.add_argument("--no-hkv", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -445,6 +517,10 @@ def main():
         value, ms, what = run_cpu(spec, steps=2, warmup=1, n_heads_sample=2 if args.workload == "c2" else 1)
         line["cpu_baseline"] = {"value": value, "unit": "chunks/s", "cores": cores, "kind": "port", "sample": what,
                                 "ms_per_chunk": ms}
+    if world == 1 and not args.no_hkv:
+        del q, k, v, flush
+        torch.cuda.empty_cache()
+        line["hkv"] = bench_hkv(dev)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -62,6 +62,91 @@ compress_kernel(View4 k, View4 v, void *ok, void *ov, int out_dtype, long long o
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Fast path: bf16, heads contiguous (stride_h == D), rank <= 32.  One CTA per (128 columns, segment,
+// K|V, batch); the eight warps take every eighth token, a lane owns four adjacent columns (8-byte
+// loads), the projection tile is staged in shared memory as float32 [token][rank] so that four
+// ranks come from one 16-byte broadcast load.  Partial sums of the warps are added in warp order.
+// ------------------------------------------------------------------------------------------------
+constexpr int CF_WARPS = 8;
+constexpr int CF_TT = 128;      // tokens per staged projection tile
+constexpr int CF_R = 32;        // padded rank
+
+__global__ void __launch_bounds__(CF_WARPS * 32)
+compress_fast_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v, long long xsb, long long xsl,
+                     __nv_bfloat16 *__restrict__ ok, __nv_bfloat16 *__restrict__ ov, long long osb, long long osl, int L,
+                     int segment_len, int block_size, const void *pk, const void *pv, int pdt, int proj_rank,
+                     int proj_cols, int rank_full) {
+    __shared__ __align__(16) float es[CF_TT][CF_R];
+    __shared__ float red[CF_R][128];
+    const int col0 = blockIdx.x * 128;
+    const int seg = blockIdx.y;
+    const int b = blockIdx.z >> 1, which = blockIdx.z & 1;
+    const __nv_bfloat16 *x = (which ? v : k) + (long long)b * xsb + col0;
+    const void *proj = which ? pv : pk;
+    __nv_bfloat16 *out = (which ? ov : ok) + (long long)b * osb + col0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int t0 = seg * segment_len;
+    const int n_tok = min(segment_len, L - t0);
+    const int rank = min(proj_rank, (n_tok + block_size - 1) / block_size);
+
+    float acc[CF_R][4];
+#pragma unroll
+    for (int r = 0; r < CF_R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+
+    for (int tt0 = 0; tt0 < n_tok; tt0 += CF_TT) {
+        const int nt = min(CF_TT, n_tok - tt0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < CF_TT * CF_R; e += CF_WARPS * 32) {
+            const int r = e / CF_TT, t = e % CF_TT;     // consecutive threads read consecutive tokens of one row
+            es[t][r] = (r < rank && t < nt) ? load_elem(proj, pdt, (long long)r * proj_cols + tt0 + t) : 0.f;
+        }
+        __syncthreads();
+        for (int t = warp; t < nt; t += CF_WARPS) {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(x + (long long)(t0 + tt0 + t) * xsl + lane * 4);
+            const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+            const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+#pragma unroll
+            for (int r4 = 0; r4 < CF_R; r4 += 4) {
+                if (r4 < rank) {
+                    const float4 e4 = *reinterpret_cast<const float4 *>(&es[t][r4]);
+                    const float ev[4] = {e4.x, e4.y, e4.z, e4.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        acc[r4 + u][0] = fmaf(ev[u], x01.x, acc[r4 + u][0]);
+                        acc[r4 + u][1] = fmaf(ev[u], x01.y, acc[r4 + u][1]);
+                        acc[r4 + u][2] = fmaf(ev[u], x23.x, acc[r4 + u][2]);
+                        acc[r4 + u][3] = fmaf(ev[u], x23.y, acc[r4 + u][3]);
+                    }
+                }
+            }
+        }
+    }
+    // ordered reduction over the warps
+    for (int w = 0; w < CF_WARPS; ++w) {
+        __syncthreads();
+        if (warp == w) {
+#pragma unroll
+            for (int r = 0; r < CF_R; ++r) {
+                if (r < rank) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (w == 0) red[r][lane * 4 + u] = acc[r][u];
+                        else red[r][lane * 4 + u] += acc[r][u];
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < rank * 128; e += CF_WARPS * 32) {
+        const int r = e / 128, c = e % 128;
+        out[(long long)(seg * rank_full + r) * osl + c] = __float2bfloat16_rn(red[r][c]);
+    }
+}
+
 }  // namespace wa
 
 using namespace wa;
@@ -88,6 +173,18 @@ extern "C" int wa_compress_kv(const wa_tensor4 *k, const wa_tensor4 *v, const wa
                longest, proj_cols);
     const int rank_full = proj_rank < ceil_div(longest, block_size) ? proj_rank : ceil_div(longest, block_size);
     WA_REQUIRE(n_seg <= 65535 && 2 * B <= 65535, WA_ERR_UNSUPPORTED, "%s: too many segments", what);
+    const bool fast = k->dtype == WA_BF16 && out_k->dtype == WA_BF16 && k->stride_h == D && v->stride_h == D &&
+                      out_k->stride_h == D && (H * D) % 128 == 0 && rank_full <= CF_R && k->stride_b == v->stride_b &&
+                      k->stride_l == v->stride_l && k->stride_l % 4 == 0 && k->stride_b % 4 == 0 &&
+                      ((uintptr_t)k->ptr % 8 == 0) && ((uintptr_t)v->ptr % 8 == 0);
+    if (fast) {
+        dim3 fgrid(H * D / 128, n_seg, 2 * B);
+        compress_fast_kernel<<<fgrid, CF_WARPS * 32, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16 *)k->ptr, (const __nv_bfloat16 *)v->ptr, k->stride_b, k->stride_l,
+            (__nv_bfloat16 *)out_k->ptr, (__nv_bfloat16 *)out_v->ptr, out_k->stride_b, out_k->stride_l, L, segment_len,
+            block_size, k_proj, v_proj, proj_dtype, proj_rank, proj_cols, rank_full);
+        return check_launch(what);
+    }
     dim3 grid(ceil_div(H * D, CK_THREADS), n_seg, 2 * B);
     compress_kernel<<<grid, CK_THREADS, 0, (cudaStream_t)stream>>>(
         make_view(k), make_view(v), out_k->ptr, out_v->ptr, out_k->dtype, out_k->stride_b, out_k->stride_l,
