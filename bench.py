@@ -308,6 +308,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
     ap.add_argument("--no-hkv", action="store_true")
+    ap.add_argument("--shard", default="auto", choices=["auto", "heads", "kv"], help="sharding for --gpus > 1")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -348,6 +349,8 @@ def main():
     mode = "single"
     if world > 1:
         mode = "heads" if (HEADS % world == 0 and world <= 4) else "kv"
+        if args.shard != "auto":
+            mode = args.shard
     if mode == "heads":
         plan = sharded.plan_head_split(HEADS, world, topk_all.tolist())
         mine = plan[rank]

@@ -70,16 +70,17 @@ compress_kernel(View4 k, View4 v, void *ok, void *ov, int out_dtype, long long o
 // ranks come from one 16-byte broadcast load.  Partial sums of the warps are added in warp order.
 // ------------------------------------------------------------------------------------------------
 constexpr int CF_WARPS = 8;
-constexpr int CF_TT = 128;      // tokens per staged projection tile
-constexpr int CF_R = 32;        // padded rank
+constexpr int CF_TT = 128;      // tokens per staged projection tile (16 per warp)
+constexpr int CF_PF = 8;        // token rows a warp keeps in flight
 
+template <int R>                // padded rank: 16 or 32
 __global__ void __launch_bounds__(CF_WARPS * 32)
 compress_fast_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v, long long xsb, long long xsl,
                      __nv_bfloat16 *__restrict__ ok, __nv_bfloat16 *__restrict__ ov, long long osb, long long osl, int L,
                      int segment_len, int block_size, const void *pk, const void *pv, int pdt, int proj_rank,
                      int proj_cols, int rank_full) {
-    __shared__ __align__(16) float es[CF_TT][CF_R];
-    __shared__ float red[CF_R][128];
+    __shared__ __align__(16) float es[CF_TT][R];
+    __shared__ float red[R][128];
     const int col0 = blockIdx.x * 128;
     const int seg = blockIdx.y;
     const int b = blockIdx.z >> 1, which = blockIdx.z & 1;
@@ -92,25 +93,35 @@ compress_fast_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *_
     const int n_tok = min(segment_len, L - t0);
     const int rank = min(proj_rank, (n_tok + block_size - 1) / block_size);
 
-    float acc[CF_R][4];
+    float acc[R][4];
 #pragma unroll
-    for (int r = 0; r < CF_R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+    for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 
     for (int tt0 = 0; tt0 < n_tok; tt0 += CF_TT) {
         const int nt = min(CF_TT, n_tok - tt0);
         __syncthreads();
-        for (int e = threadIdx.x; e < CF_TT * CF_R; e += CF_WARPS * 32) {
+        for (int e = threadIdx.x; e < CF_TT * R; e += CF_WARPS * 32) {
             const int r = e / CF_TT, t = e % CF_TT;     // consecutive threads read consecutive tokens of one row
             es[t][r] = (r < rank && t < nt) ? load_elem(proj, pdt, (long long)r * proj_cols + tt0 + t) : 0.f;
         }
         __syncthreads();
-        for (int t = warp; t < nt; t += CF_WARPS) {
-            const uint2 raw = *reinterpret_cast<const uint2 *>(x + (long long)(t0 + tt0 + t) * xsl + lane * 4);
-            const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
-            const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+        // this warp's tokens of the tile: warp, warp + 8, ...; CF_PF rows are loaded before any is used
+        for (int g0 = 0; g0 < CF_TT / CF_WARPS; g0 += CF_PF) {
+            uint2 raw[CF_PF];
 #pragma unroll
-            for (int r4 = 0; r4 < CF_R; r4 += 4) {
-                if (r4 < rank) {
+            for (int i = 0; i < CF_PF; ++i) {
+                const int t = warp + (g0 + i) * CF_WARPS;
+                raw[i] = t < nt ? *reinterpret_cast<const uint2 *>(x + (long long)(t0 + tt0 + t) * xsl + lane * 4)
+                                : make_uint2(0u, 0u);
+            }
+#pragma unroll
+            for (int i = 0; i < CF_PF; ++i) {
+                const int t = warp + (g0 + i) * CF_WARPS;
+                if (t >= nt) break;
+                const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[i].x));
+                const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[i].y));
+#pragma unroll
+                for (int r4 = 0; r4 < R; r4 += 4) {
                     const float4 e4 = *reinterpret_cast<const float4 *>(&es[t][r4]);
                     const float ev[4] = {e4.x, e4.y, e4.z, e4.w};
 #pragma unroll
@@ -129,13 +140,11 @@ compress_fast_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *_
         __syncthreads();
         if (warp == w) {
 #pragma unroll
-            for (int r = 0; r < CF_R; ++r) {
-                if (r < rank) {
+            for (int r = 0; r < R; ++r) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (w == 0) red[r][lane * 4 + u] = acc[r][u];
-                        else red[r][lane * 4 + u] += acc[r][u];
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    if (w == 0) red[r][lane * 4 + u] = acc[r][u];
+                    else red[r][lane * 4 + u] += acc[r][u];
                 }
             }
         }
@@ -174,15 +183,21 @@ extern "C" int wa_compress_kv(const wa_tensor4 *k, const wa_tensor4 *v, const wa
     const int rank_full = proj_rank < ceil_div(longest, block_size) ? proj_rank : ceil_div(longest, block_size);
     WA_REQUIRE(n_seg <= 65535 && 2 * B <= 65535, WA_ERR_UNSUPPORTED, "%s: too many segments", what);
     const bool fast = k->dtype == WA_BF16 && out_k->dtype == WA_BF16 && k->stride_h == D && v->stride_h == D &&
-                      out_k->stride_h == D && (H * D) % 128 == 0 && rank_full <= CF_R && k->stride_b == v->stride_b &&
+                      out_k->stride_h == D && (H * D) % 128 == 0 && rank_full <= 32 && k->stride_b == v->stride_b &&
                       k->stride_l == v->stride_l && k->stride_l % 4 == 0 && k->stride_b % 4 == 0 &&
                       ((uintptr_t)k->ptr % 8 == 0) && ((uintptr_t)v->ptr % 8 == 0);
     if (fast) {
         dim3 fgrid(H * D / 128, n_seg, 2 * B);
-        compress_fast_kernel<<<fgrid, CF_WARPS * 32, 0, (cudaStream_t)stream>>>(
-            (const __nv_bfloat16 *)k->ptr, (const __nv_bfloat16 *)v->ptr, k->stride_b, k->stride_l,
-            (__nv_bfloat16 *)out_k->ptr, (__nv_bfloat16 *)out_v->ptr, out_k->stride_b, out_k->stride_l, L, segment_len,
-            block_size, k_proj, v_proj, proj_dtype, proj_rank, proj_cols, rank_full);
+        if (rank_full <= 16)
+            compress_fast_kernel<16><<<fgrid, CF_WARPS * 32, 0, (cudaStream_t)stream>>>(
+                (const __nv_bfloat16 *)k->ptr, (const __nv_bfloat16 *)v->ptr, k->stride_b, k->stride_l,
+                (__nv_bfloat16 *)out_k->ptr, (__nv_bfloat16 *)out_v->ptr, out_k->stride_b, out_k->stride_l, L,
+                segment_len, block_size, k_proj, v_proj, proj_dtype, proj_rank, proj_cols, rank_full);
+        else
+            compress_fast_kernel<32><<<fgrid, CF_WARPS * 32, 0, (cudaStream_t)stream>>>(
+                (const __nv_bfloat16 *)k->ptr, (const __nv_bfloat16 *)v->ptr, k->stride_b, k->stride_l,
+                (__nv_bfloat16 *)out_k->ptr, (__nv_bfloat16 *)out_v->ptr, out_k->stride_b, out_k->stride_l, L,
+                segment_len, block_size, k_proj, v_proj, proj_dtype, proj_rank, proj_cols, rank_full);
         return check_launch(what);
     }
     dim3 grid(ceil_div(H * D, CK_THREADS), n_seg, 2 * B);
