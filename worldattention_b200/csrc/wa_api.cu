@@ -190,9 +190,7 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
     // ---- tuned tcgen05 path -------------------------------------------------------------------
     const bool want_tuned = !(p->flags & WA_HSA_FORCE_GENERIC);
     if (want_tuned && hsa_sm100_supported(p, Lc, &kc, &vc)) {
-        profile_mark(true, stream);
         rc = hsa_sm100_launch(p, Lc, &kc, &vc, index, num, w.Nq, w.Nkv, ws + w.tuned, stream);
-        profile_mark(false, stream);
         if (rc) return rc;
         if (used_tuned) *used_tuned = 1;
         return 0;

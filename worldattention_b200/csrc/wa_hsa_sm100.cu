@@ -28,13 +28,14 @@ namespace sm100 {
 
 constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
 constexpr int HALF = 64;             // key tokens per softmax / MMA pipeline step
-constexpr int THREADS = 320;         // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two threads per query row)
+constexpr int THREADS = 352;         // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two threads per query row), warp 10 output store
 constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
-constexpr int TMEM_COLS = 512;       // two S buffers: columns [0,128), [128,256); O: [256,384)
-constexpr int KV_STAGES = 3;         // shared-memory ring depth for K tiles
+constexpr int TMEM_COLS = 512;       // two S buffers: columns [0,128), [128,256); O: [256,384); parked sparse result: [384,448)
+constexpr int Q_STAGES = 2;          // the staged output of item j leaves from one Q buffer while item j+1 loads the other
+constexpr int KV_STAGES = 2;         // shared-memory ring depth for K tiles
 constexpr int V_STAGES = 2;          // shared-memory ring depth for V tiles
-constexpr int SMEM_BYTES = (1 + KV_STAGES + V_STAGES) * TILE_BYTES + 1024 /*alignment slack*/ + 4096 /*barriers, bias, exchange*/;
+constexpr int SMEM_BYTES = (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES + 1024 /*alignment slack*/ + 4096 /*barriers, bias, exchange*/;
 constexpr long long WAIT_CYCLES = 4000000000ll;
 
 // Optional event trace for kernel tuning (compile with -DWA_SM100_TRACE): CTA 0 appends
@@ -103,7 +104,6 @@ struct Params {
     // partial-output mode (KV-sharded multi-GPU): normalised per-branch outputs + natural-log LSE
     float *part_sparse, *part_linear;   // [B, Lq, H, 128] float32 or null
     float *lse_sparse, *lse_linear;     // [B, H, Lq]
-    uint4 *stash;                       // per-CTA scratch for the parked sparse result: [grid][16][128] x 16 B
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -192,6 +192,14 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])     \
         : "r"(taddr) : "memory")
 
+#define TMEM_LD16(taddr, r)                                                                                          \
+    asm volatile(                                                                                                    \
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "                                                                    \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                             \
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),            \
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])       \
+        : "r"(taddr) : "memory")
+
 #define TMEM_ST16(taddr, r)                                                                                          \
     asm volatile(                                                                                                    \
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                              \
@@ -211,6 +219,12 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
@@ -257,14 +271,29 @@ __device__ __forceinline__ float row_max32(const uint32_t (&r)[32], int col0, in
 }
 
 // 32 scores -> 32 probabilities packed as 16 bf16 pairs; returns their float32 sum.
+// 2^x on the FMA pipe: split x into round(x) + f, f in [-0.5, 0.5], evaluate a cubic for 2^f and add round(x)
+// to the exponent field.  Relative error < 2^-10, below the bf16 rounding of P.  The special-function unit
+// (16 results per clock per SM) is the narrowest pipe of the softmax, so every third element takes this path.
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;            // 1.5 * 2^23: the integer part of x lands in the low mantissa bits
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.0555041f, 0.2402265f);
+    p = fmaf(p, f, 0.6931472f);
+    p = fmaf(p, f, 1.0f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+constexpr int POLY_EVERY = 3;
+
 template <bool MASKED, int OFF>
 __device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&pk)[32], float scale, float m, int col0,
                                             int valid) {
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int j = 0; j < 32; j += 2) {
-        float p0 = ex2(fmaf(__uint_as_float(r[j]), scale, -m));
-        float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale, -m));
+        const float x0 = fmaf(__uint_as_float(r[j]), scale, -m), x1 = fmaf(__uint_as_float(r[j + 1]), scale, -m);
+        float p0 = (j % POLY_EVERY == 0) ? ex2_poly(x0) : ex2(x0);
+        float p1 = ((j + 1) % POLY_EVERY == 0) ? ex2_poly(x1) : ex2(x1);
         if (MASKED) {
             if (col0 + j >= valid) p0 = 0.f;
             if (col0 + j + 1 >= valid) p1 = 0.f;
@@ -277,20 +306,29 @@ __device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&
     return s0 + s1;
 }
 
-static_assert(true, "");
+struct ItemDesc {
+    int item;    // (b*H + h)*Nq + qb, or -1: no more work
+    int n_sel;   // selected key blocks of this item
+};
+
 struct Barriers {
-    uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
+    uint64_t item_full[2], item_empty[2];
+    uint64_t q_full[Q_STAGES], q_empty[Q_STAGES], out_ready[Q_STAGES];
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
     uint64_t s_full[2], p_full[2], pv_done, o_done, o_free;
     uint32_t tmem_base;
-    int item;
     int abort_flag;
-    int valid[8];       // real token count of the K tiles in flight, ring indexed by tile number
-    float bias[TILE];   // gate bias
+    ItemDesc items[2];
+    int valid[8];            // real token count of the K-type tiles in flight, ring indexed by global tile number
+    float bias[TILE];        // gate bias
     float xch[2][2][TILE];   // row-maximum exchange between the two threads of a row: [tile parity][half][row]
     float lx[2][TILE];       // row-sum exchange at the end of a branch
 };
 
 // ---- the kernel ----------------------------------------------------------------------------------
+// The three roles run their own loops over work items and meet only at mbarriers, so the producer
+// prefetches the next item's Q/K/V and the MMA warp starts its first products while the softmax
+// warps are still in the previous item's epilogue.
 __global__ void __launch_bounds__(THREADS, 1)
 hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
@@ -298,14 +336,24 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                      const __grid_constant__ CUtensorMap tm_out, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *q_s = smem, *k_s = smem + TILE_BYTES, *v_s = smem + (1 + KV_STAGES) * TILE_BYTES;
-    Barriers *bar = reinterpret_cast<Barriers *>(smem + (1 + KV_STAGES + V_STAGES) * TILE_BYTES);
+    uint8_t *q_s = smem, *k_s = smem + Q_STAGES * TILE_BYTES, *v_s = smem + (Q_STAGES + KV_STAGES) * TILE_BYTES;
+    Barriers *bar = reinterpret_cast<Barriers *>(smem + (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &bar->abort_flag;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bar->q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar->item_full[i], 1);
+            mbar_init(&bar->item_empty[i], 1 + 256 + 1);   // MMA leader + every softmax thread + store warp
+            mbar_init(&bar->s_full[i], 1);
+            mbar_init(&bar->p_full[i], 256);
+        }
+        for (int i = 0; i < Q_STAGES; ++i) {
+            mbar_init(&bar->q_full[i], 1);
+            mbar_init(&bar->q_empty[i], 1);
+            mbar_init(&bar->out_ready[i], 256);
+        }
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(&bar->k_full[i], 1);
             mbar_init(&bar->k_empty[i], 1);
@@ -314,10 +362,6 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_init(&bar->v_full[i], 1);
             mbar_init(&bar->v_empty[i], 1);
         }
-        mbar_init(&bar->s_full[0], 1);
-        mbar_init(&bar->s_full[1], 1);
-        mbar_init(&bar->p_full[0], 256);
-        mbar_init(&bar->p_full[1], 256);
         mbar_init(&bar->pv_done, 1);
         mbar_init(&bar->o_done, 1);
         mbar_init(&bar->o_free, 256);
@@ -337,49 +381,53 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * TILE;   // S buffer b at tmem_s + b * TILE
     WA_TRACE_DECL;
     WA_TRACE(0);
-
-    // State carried across work items.  Each role advances its own copy of the ring counters in the same way.
-    uint32_t kcount = 0, vcount = 0;   // K / V tiles produced (warp 0) or consumed (warp 1) so far
-    uint32_t ph_q = 0, ph_of = 0, ph_od = 0;
-    uint32_t ph_s = 0, ph_p = 0;       // one parity bit per S buffer
-    uint32_t pv_count = 0;             // PV products requested so far (softmax role)
     const int lin_tiles = (p.Lc + TILE - 1) / TILE;
 
-    while (true) {
-        if (threadIdx.x == 0) bar->item = atomicAdd(p.work_counter, 1);
-        __syncthreads();
-        const int slot = bar->item;
-        if (slot >= p.n_items || *abort_flag) break;
-        const int item = p.order[slot];
-        const int qb = item % p.Nq;
-        const int h = (item / p.Nq) % p.H;
-        const int b = item / (p.Nq * p.H);
-        const long long meta = item;   // (b*H + h)*Nq + qb
-        const int n_sel = max(0, min(p.num[meta], p.Nkv));
-        const int32_t *ids = p.index + meta * (long long)p.Nkv;
-        const int n_kv = n_sel + lin_tiles;   // tiles with a softmax; tile n_kv is the gate product
-        WA_STATS_ITEM(n_kv + 1);
+    if (warp == 0) {
+        // ================= producer: work queue + TMA =================
+        if (lane == 0) {
+            uint32_t jcount = 0, kcount = 0, vcount = 0;
+            bool ok = true;
+            while (ok) {
+                const uint32_t slot = jcount & 1u;
+                ok = mbar_wait(&bar->item_empty[slot], ((jcount >> 1) & 1u) ^ 1u, abort_flag, p.error_flag, 11);
+                if (!ok) break;
+                const int at = atomicAdd(p.work_counter, 1);
+                int item = -1, n_sel = 0;
+                if (at < p.n_items) {
+                    item = p.order[at];
+                    n_sel = max(0, min(p.num[item], p.Nkv));
+                }
+                bar->items[slot].item = item;
+                bar->items[slot].n_sel = n_sel;
+                mbar_arrive(&bar->item_full[slot]);
+                if (item < 0) break;
+                const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
+                const int32_t *ids = p.index + (long long)item * p.Nkv;
+                const int n_kv = n_sel + lin_tiles;
+                WA_STATS_ITEM(n_kv + 1);
 
-        if (warp == 0) {
-            // ================= TMA producer =================
-            if (lane == 0) {
-                mbar_expect_tx(&bar->q_full, TILE_BYTES);
-                tma_load_4d(q_s, &tm_q, &bar->q_full, 0, h, qb * TILE, b);
-                tma_load_4d(q_s + HALF_BYTES, &tm_q, &bar->q_full, 64, h, qb * TILE, b);
-                bool ok = true;
+                const uint32_t qs = jcount % Q_STAGES;
+                ok = mbar_wait(&bar->q_empty[qs], ((jcount / Q_STAGES) & 1u) ^ 1u, abort_flag, p.error_flag, 12);
+                if (!ok) break;
+                uint8_t *qdst = q_s + qs * TILE_BYTES;
+                mbar_expect_tx(&bar->q_full[qs], TILE_BYTES);
+                tma_load_4d(qdst, &tm_q, &bar->q_full[qs], 0, h, qb * TILE, b);
+                tma_load_4d(qdst + HALF_BYTES, &tm_q, &bar->q_full[qs], 64, h, qb * TILE, b);
+
                 for (int t = 0; t <= n_kv && ok; ++t) {
                     const uint32_t ks = kcount % KV_STAGES, kpar = ((kcount / KV_STAGES) & 1u) ^ 1u;
                     ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, p.error_flag, 1);
                     if (!ok) break;
-                    ++kcount;
                     uint8_t *kdst = k_s + ks * TILE_BYTES;
                     int id = 0;
                     if (t < n_sel) {
                         id = max(0, min(ids[t], p.Nkv - 1));
-                        bar->valid[t & 7] = min(TILE, p.Lkv - id * TILE);
+                        bar->valid[kcount & 7] = min(TILE, p.Lkv - id * TILE);
                     } else {
-                        bar->valid[t & 7] = min(TILE, p.Lc - (t - n_sel) * TILE);
+                        bar->valid[kcount & 7] = min(TILE, p.Lc - (t - n_sel) * TILE);
                     }
+                    ++kcount;
                     mbar_expect_tx(&bar->k_full[ks], TILE_BYTES);
                     if (t < n_sel) {
                         tma_load_4d(kdst, &tm_k, &bar->k_full[ks], 0, h, id * TILE, b);
@@ -409,99 +457,166 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         }
                     }
                 }
+                ++jcount;
             }
-        } else if (warp == 1) {
-            // ================= MMA issuer =================
-            // Issue order QK(0), QK(1), PV(0), QK(2), PV(1), ...: the score product of tile t+1 lands in the
-            // other S buffer while the softmax warps work on tile t.  The whole warp runs this role so that
-            // operands stay warp-uniform; one elected lane issues.
-            {
-                const bool leader = elect_one();
-                constexpr uint32_t IDESC_QK = instr_desc(false, TILE), IDESC_PV = instr_desc(true, TILE);
-                const uint64_t qd = smem_desc(smem_u32(q_s), 16, 1024);
-                bool ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full, ph_q, abort_flag, p.error_flag, 3));
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        // Issue order QK(0), QK(1), PV(0), QK(2), PV(1), ...: the score product of the next tile lands in the
+        // other S buffer while the softmax warps work on the current one; the sequence continues across
+        // work items.  The whole warp runs this role so that operands stay warp-uniform; one elected lane issues.
+        const bool leader = elect_one();
+        constexpr uint32_t IDESC_QK = instr_desc(false, TILE), IDESC_PV = instr_desc(true, TILE);
+        uint32_t jcount = 0, kcount = 0, vcount = 0, ph_p = 0, ph_of = 1;   // ph_of = 1: the first wait passes
+        uint32_t gate_in_buf = 0;   // bit b: S buffer b holds gate scores the softmax warps have not read yet
+        bool ok = true;
 
-                auto issue_qk = [&](int t) -> bool {
-                    const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
-                    if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
-                    ++kcount;
-                    WA_TRACE(1);
-                    tc_fence_after();
-                    if (leader) {
-                        const uint64_t kd = smem_desc(smem_u32(k_s + ks * TILE_BYTES), 16, 1024);
-                        const uint32_t d = tmem_s + (t & 1) * TILE;
+        auto issue_qk = [&](uint64_t qd, bool is_gate) -> bool {
+            const uint32_t buf = kcount & 1u;
+            if (gate_in_buf & (1u << buf)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (ph_p >> buf) & 1u, abort_flag, p.error_flag, 13)))
+                    return false;
+                ph_p ^= 1u << buf;
+                gate_in_buf &= ~(1u << buf);
+            }
+            const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
+            ++kcount;
+            WA_TRACE(1);
+            tc_fence_after();
+            if (leader) {
+                const uint64_t kd = smem_desc(smem_u32(k_s + ks * TILE_BYTES), 16, 1024);
+                const uint32_t d = tmem_s + buf * TILE;
 #pragma unroll
-                        for (int kk = 0; kk < 8; ++kk) {
-                            const uint64_t off = (uint64_t)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
-                            mma_ss(d, qd + off, kd + off, IDESC_QK, kk > 0);
-                        }
-                        tc_commit(&bar->k_empty[ks]);
-                        tc_commit(&bar->s_full[t & 1]);
-                    }
-                    __syncwarp();
-                    WA_TRACE(4);
-                    return true;
-                };
-
-                if (ok) ok = issue_qk(0);
-                for (int t = 0; t < n_kv && ok; ++t) {
-                    ok = issue_qk(t + 1);
-                    if (!ok) break;
-                    const int buf = t & 1;
-                    const bool first = (t == 0) || (t == n_sel);
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (ph_p >> buf) & 1u, abort_flag, p.error_flag, 5));
-                    if (!ok) break;
-                    ph_p ^= 1u << buf;
-                    WA_TRACE(5);
-                    const uint32_t vs = vcount % V_STAGES, vpar = (vcount / V_STAGES) & 1u;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, p.error_flag, 6));
-                    if (!ok) break;
-                    ++vcount;
-                    if (first && t > 0) {
-                        // the sparse accumulator must have been read out before the linear branch reuses it
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7));
-                        if (!ok) break;
-                        ph_of ^= 1u;
-                    }
-                    tc_fence_after();
-                    if (leader) {
-                        const uint64_t vd = smem_desc(smem_u32(v_s + vs * TILE_BYTES), HALF_BYTES, 1024);
-#pragma unroll
-                        for (int kk = 0; kk < 8; ++kk)
-                            mma_ts(tmem_o, tmem_s + buf * TILE + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
-                                   !(first && kk == 0));
-                        tc_commit(&bar->v_empty[vs]);
-                        tc_commit(&bar->pv_done);
-                        if (t == n_sel - 1 || t == n_kv - 1) tc_commit(&bar->o_done);
-                    }
-                    __syncwarp();
-                    WA_TRACE(7);
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t off = (uint64_t)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
+                    mma_ss(d, qd + off, kd + off, IDESC_QK, kk > 0);
                 }
+                tc_commit(&bar->k_empty[ks]);
+                tc_commit(&bar->s_full[buf]);
             }
-            ph_q ^= 1u;
-        } else {
-            // ================= softmax / epilogue: two threads per query row (64 score columns each) ==========
-            // Warps 2..5 own columns [0,64), warps 6..9 columns [64,128) of the same rows (a warp may only touch
-            // the 32 tensor-memory lanes selected by warp % 4).  The two threads of a row meet at a 64-thread
-            // named barrier once per tile to agree on the row maximum.
-            const int half = (warp - 2) >> 2;
-            const int row = (warp & 3) * 32 + lane;
-            const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
-            const int pair_bar = 2 + (warp & 3);
+            __syncwarp();
+            if (is_gate) gate_in_buf |= 1u << buf;
+            WA_TRACE(4);
+            return true;
+        };
+
+        while (ok) {
+            const uint32_t slot = jcount & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 14));
+            if (!ok) break;
+            const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
+            __syncwarp();
+            if (leader) mbar_arrive(&bar->item_empty[slot]);
+            if (item < 0) break;
+            const int n_kv = n_sel + lin_tiles;
+            const uint32_t qs = jcount % Q_STAGES;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full[qs], (jcount / Q_STAGES) & 1u, abort_flag, p.error_flag, 3));
+            if (!ok) break;
+            const uint64_t qd = smem_desc(smem_u32(q_s + qs * TILE_BYTES), 16, 1024);
+            const uint32_t g0 = kcount;   // global number of this item's first tile
+            ok = issue_qk(qd, false);
+            for (int t = 0; t < n_kv && ok; ++t) {
+                ok = issue_qk(qd, t + 1 == n_kv);
+                if (!ok) break;
+                const uint32_t buf = (g0 + t) & 1u;
+                const bool first = (t == 0) || (t == n_sel);
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (ph_p >> buf) & 1u, abort_flag, p.error_flag, 5));
+                if (!ok) break;
+                ph_p ^= 1u << buf;
+                WA_TRACE(5);
+                const uint32_t vs = vcount % V_STAGES, vpar = (vcount / V_STAGES) & 1u;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, p.error_flag, 6));
+                if (!ok) break;
+                ++vcount;
+                if (first) {
+                    // the accumulator of the previous branch (or item) must have been read out
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7));
+                    if (!ok) break;
+                    ph_of ^= 1u;
+                }
+                tc_fence_after();
+                if (leader) {
+                    const uint64_t vd = smem_desc(smem_u32(v_s + vs * TILE_BYTES), HALF_BYTES, 1024);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        mma_ts(tmem_o, tmem_s + buf * TILE + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
+                               !(first && kk == 0));
+                    tc_commit(&bar->v_empty[vs]);
+                    tc_commit(&bar->pv_done);
+                    if (t == n_sel - 1 || t == n_kv - 1) tc_commit(&bar->o_done);
+                }
+                __syncwarp();
+                WA_TRACE(7);
+            }
+            ++jcount;
+        }
+    } else if (warp == 10) {
+        // ================= store warp: TMA store of the staged output tile, then release of the Q stage =========
+        if (lane == 0) {
+            uint32_t jcount = 0;
+            bool ok = true;
+            while (ok) {
+                const uint32_t slot = jcount & 1u;
+                ok = mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 16);
+                if (!ok) break;
+                const int item = bar->items[slot].item;
+                mbar_arrive(&bar->item_empty[slot]);
+                if (item < 0) break;
+                const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
+                const uint32_t qs = jcount % Q_STAGES;
+                ok = mbar_wait(&bar->out_ready[qs], (jcount / Q_STAGES) & 1u, abort_flag, p.error_flag, 17);
+                if (!ok) break;
+                if (!p.part_linear) {
+                    // rows beyond q_len are clipped by the tensor map
+                    tma_store_4d(&tm_out, q_s + qs * TILE_BYTES, 0, h, qb * TILE, b);
+                    tma_store_4d(&tm_out, q_s + qs * TILE_BYTES + HALF_BYTES, 64, h, qb * TILE, b);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the Q stage is reusable afterwards
+                }
+                mbar_arrive(&bar->q_empty[qs]);
+                ++jcount;
+            }
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores have landed before the CTA exits
+        }
+    } else {
+        // ================= softmax / epilogue: two threads per query row (64 score columns each) ==========
+        // Warps 2..5 own columns [0,64), warps 6..9 columns [64,128) of the same rows (a warp may only touch
+        // the 32 tensor-memory lanes selected by warp % 4).  The two threads of a row meet at a 64-thread
+        // named barrier once per tile to agree on the row maximum.
+        const int half = (warp - 2) >> 2;
+        const int row = (warp & 3) * 32 + lane;
+        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
+        const int pair_bar = 2 + (warp & 3);
+        const uint32_t tmem_park = tmem + 3 * TILE + lane_addr + half * 32;   // parked sparse result (bf16 pairs)
+        uint32_t jcount = 0, sg = 0;       // items and K-type tiles seen so far
+        uint32_t ph_s = 0, ph_od = 0;
+        uint32_t pv_count = 0;             // PV products requested so far
+        bool ok = true;
+
+        while (ok) {
+            const uint32_t slot = jcount & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 15));
+            if (!ok) break;
+            const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
+            mbar_arrive(&bar->item_empty[slot]);
+            if (item < 0) break;
+            const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
+            const int n_kv = n_sel + lin_tiles;
+            const uint32_t qs = jcount % Q_STAGES;
+            uint8_t *q_stage = q_s + qs * TILE_BYTES;
             const int token = qb * TILE + row;
             const bool row_ok = token < p.Lq;
             const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE + half * HALF;
             const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
-            uint4 *stash = p.stash + (size_t)blockIdx.x * (16 * TILE) + (size_t)half * (8 * TILE);
-            const int gbuf = n_kv & 1;
-            bool ok = true;
+            const int gbuf = (sg + n_kv) & 1;
             float inv_l_lin = 0.f;
 
             for (int phase = 0; phase < 2 && ok; ++phase) {
                 const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_kv;
                 float m_used = -INFINITY, l = 0.f;
                 for (int t = t0; t < t1 && ok; ++t) {
-                    const int buf = t & 1;
+                    const int buf = (sg + t) & 1;
                     const uint32_t s_addr = tmem_s + buf * TILE + lane_addr;
                     ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], (ph_s >> buf) & 1u, abort_flag, p.error_flag, 8));
                     if (!ok) break;
@@ -509,7 +624,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     WA_TRACE(2);
                     tc_fence_after();
                     // columns of this thread that hold real tokens (the producer wrote the tile's count)
-                    const int valid = max(0, min(HALF, bar->valid[t & 7] - half * HALF));
+                    const int valid = max(0, min(HALF, bar->valid[(sg + t) & 7] - half * HALF));
                     uint32_t r0[32], r1[32];
                     TMEM_LD32(s_addr + half * HALF, r0);
                     TMEM_LD32(s_addr + half * HALF + 32, r1);
@@ -579,7 +694,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
                 if (phase == 0) {
                     // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park it
-                    // in this CTA's stash, laid out [16-byte chunk][row] so that warps store and reload whole lines.
+                    // in 64 spare tensor-memory columns (two bf16 per column) until the final combine.
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
@@ -600,20 +715,17 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                 }
                             }
                         } else {
+                            uint32_t pk16[16];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 o4;
-                                uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv_l,
-                                                                               __uint_as_float(r[j + 2 * e + 1]) * inv_l);
-                                    w[e] = *reinterpret_cast<uint32_t *>(&h2);
-                                }
-                                stash[(c * 4 + (j >> 3)) * TILE + row] = o4;
+                            for (int j = 0; j < 32; j += 2) {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j]) * inv_l,
+                                                                           __uint_as_float(r[j + 1]) * inv_l);
+                                pk16[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                             }
+                            TMEM_ST16(tmem_park + c * 16, pk16);
                         }
                     }
+                    if (!p.part_sparse) tmem_wait_st();
                     if (p.lse_sparse && row_ok && half == 0) p.lse_sparse[lse_off] = lse;
                     if (t1 > t0) {
                         tc_fence_before();
@@ -626,11 +738,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             // ---- gate tile + combine ----
             if (ok) {
-                uint4 sp_next[4];
-                if (!p.part_linear) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sp_next[e] = stash[e * TILE + row];   // in flight during the wait below
-                }
+                WA_TRACE(18);
                 ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], (ph_s >> gbuf) & 1u, abort_flag, p.error_flag, 10));
                 if (ok) {
                     ph_s ^= 1u << gbuf;
@@ -641,15 +749,16 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         uint32_t g[32], o[32];
                         TMEM_LD32(tmem_s + gbuf * TILE + lane_addr + half * HALF + c * 32, g);
                         TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, o);
-                        uint4 sp_cur[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) sp_cur[e] = sp_next[e];
-                        if (!p.part_linear && c < 1) {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) sp_next[e] = stash[((c + 1) * 4 + e) * TILE + row];
-                        }
+                        uint32_t sp_cur[16];   // parked sparse result of these 32 columns, two bf16 per word
+                        TMEM_LD16(tmem_park + c * 16, sp_cur);
                         tmem_wait_ld();
                         WA_TRACE(14);
+                        if (c == 1) {
+                            // gate scores and the linear accumulator are in registers: release both to the MMA warp
+                            tc_fence_before();
+                            mbar_arrive(&bar->p_full[gbuf]);
+                            mbar_arrive(&bar->o_free);
+                        }
                         if (p.part_linear) {
                             if (row_ok) {
 #pragma unroll
@@ -665,9 +774,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         for (int j = 0; j < 32; j += 8) {
                             // 16-byte chunk `cc` of this row inside the swizzled 128 x 128 bf16 tile that held Q
                             const int cc = half * 8 + c * 4 + (j >> 3);
-                            uint4 *slot = reinterpret_cast<uint4 *>(q_s + (cc >> 3) * HALF_BYTES + row * 128 +
+                            uint4 *slot = reinterpret_cast<uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 +
                                                                     (((cc & 7) ^ (row & 7)) << 4));
-                            const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp_cur[j >> 3]);
+                            const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp_cur[j >> 1]);
                             uint4 qv = make_uint4(0, 0, 0, 0);
                             if (!p.has_gate) qv = *slot;   // the gate-less path needs q itself: read it before overwriting
                             const __nv_bfloat162 *q2 = reinterpret_cast<const __nv_bfloat162 *>(&qv);
@@ -685,8 +794,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                     z0 = qf.x;
                                     z1 = qf.y;
                                 }
-                                const float g0 = __fdividef(1.0f, 1.0f + ex2(-z0 * 1.4426950408889634f));
-                                const float g1 = __fdividef(1.0f, 1.0f + ex2(-z1 * 1.4426950408889634f));
+                                const float g0 = fmaf(tanh_approx(0.5f * z0), 0.5f, 0.5f);   // sigmoid, one special-function op
+                                const float g1 = fmaf(tanh_approx(0.5f * z1), 0.5f, 0.5f);
                                 const float2 s2 = __bfloat1622float2(sp2[e]);
                                 const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, g0, s2.x);
                                 const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, g1, s2.y);
@@ -695,32 +804,25 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             }
                             *slot = o4;
                         }
+                        WA_TRACE(15);
                     }
                 }
             }
-            if (!p.part_linear) {
-                // Hand the staged tile to the TMA store (rows beyond q_len are clipped by the tensor map).  Every
-                // softmax thread takes part in the barrier whether or not its waits succeeded.
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (threadIdx.x == 64 && ok) {
-                    tma_store_4d(&tm_out, q_s, 0, h, qb * TILE, b);
-                    tma_store_4d(&tm_out, q_s + HALF_BYTES, 64, h, qb * TILE, b);
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // smem reusable afterwards
-                }
-            }
-            tc_fence_before();
+            // Hand the staged tile to the store warp (in partial-output mode nothing was staged, but the Q stage
+            // is released the same way).
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&bar->out_ready[qs]);
+            WA_TRACE(10);
+            sg += n_kv + 1;
+            ++jcount;
         }
-        WA_TRACE(10);
-        __syncthreads();   // every role is done with this item's shared and tensor memory
-        WA_TRACE(11);
-        tc_fence_after();
+        tc_fence_before();
     }
 
     WA_TRACE(9);
     WA_TRACE_FLUSH;
     __syncthreads();
+    tc_fence_after();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -851,7 +953,7 @@ static int max_grid() {
 }
 
 struct TunedWs {
-    size_t order, counter, w_bf16, bias, stash, total;
+    size_t order, counter, w_bf16, bias, total;
 };
 static TunedWs tuned_plan(const wa_hsa_params *p) {
     TunedWs w{};
@@ -861,7 +963,6 @@ static TunedWs tuned_plan(const wa_hsa_params *p) {
     w.counter = c; c = align_up(c + 2 * sizeof(int), 256);
     w.w_bf16 = c; c = align_up(c + (size_t)TILE * TILE * 2, 256);
     w.bias = c; c = align_up(c + TILE * sizeof(float), 256);
-    w.stash = c; c = align_up(c + (size_t)max_grid() * 16 * TILE * sizeof(uint4), 256);
     w.total = c;
     return w;
 }
@@ -950,7 +1051,7 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.q = (const __nv_bfloat16 *)p->q.ptr; kp.qsb = p->q.stride_b; kp.qsl = p->q.stride_l; kp.qsh = p->q.stride_h;
     kp.scale_log2 = (float)(pow((double)TILE, -0.5) * 1.4426950408889634);
     kp.part_sparse = kp.part_linear = kp.lse_sparse = kp.lse_linear = nullptr;
-    kp.stash = (uint4 *)(ws + w.stash);
+
 
     static bool attr_set = false;
     if (!attr_set) {
@@ -962,7 +1063,9 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
 #ifdef WA_SM100_TRACE
     if (getenv("WA_SM100_ONE_CTA") && grid > max_grid() / 2) grid = max_grid() / 2;   // tuning aid: one CTA per SM
 #endif
+    profile_mark(true, stream);
     hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
+    profile_mark(false, stream);
     return check_launch("wa_hsa_forward(tcgen05)");
 }
 

@@ -8,6 +8,9 @@ namespace wa {
 int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
                 int block_size, cudaStream_t stream);
 
+// optional CUDA-event bracket around the attention kernel (wa_api.cu)
+void profile_mark(bool begin, cudaStream_t stream);
+
 // tcgen05 fused HSA kernel (wa_hsa_sm100.cu)
 size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p);
 size_t hsa_sm100_status_offset(const wa_hsa_params *p);   // int32 flag inside the tuned workspace
