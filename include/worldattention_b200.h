@@ -167,6 +167,14 @@ typedef struct wa_hsa_params {
     float *thresholds_out;               /* optional `[H]`                                      */
     void *workspace;
     size_t workspace_bytes;
+    /* Sharded execution (no reference counterpart; the reference is single-device).
+     * index_in / num_in: routing decided elsewhere (e.g. globally across key shards) and already
+     * restricted to this call's key range; when set, pooling and selection are skipped.
+     * part_*: when part_sparse is set the call stops before the gate: it writes the normalised
+     * float32 output of each branch `[B, Lq, H, D]` (contiguous) and its natural-log row
+     * normaliser `[B, H, Lq]` (-inf where the branch saw no key), for wa_merge_partials. */
+    const int32_t *index_in, *num_in;
+    float *part_sparse, *part_linear, *lse_sparse, *lse_linear;
 } wa_hsa_params;
 
 /* Bytes of workspace wa_hsa_forward needs for these sizes (pointers in `p` are ignored). */

@@ -128,3 +128,42 @@ def test_config2_shape_head_adaptive_topk(wa):
     max_abs, mean_rel = attention_error(to_np(out), to_np(ref))
     assert max_abs < MAX_ABS and mean_rel < MEAN_REL, (max_abs, mean_rel)
     assert torch.isfinite(out).all()
+
+
+def test_partial_output_mode_merges_to_the_full_result(wa):
+    """Two key shards through the partial-output mode (tcgen05 kernel) merge to the single-pass result."""
+    from worldattention_b200 import sharded
+    from worldattention_b200.hsa import branches
+    heads, q_len, kv_len, seg = 4, 300, 3120, 1560
+    rng = np.random.default_rng(9)
+    q, k, v = (to_gpu(_draw(rng, (1, n, heads, D), s), "bf16") for n, s in ((q_len, 0.3), (kv_len, 0.3), (kv_len, 1.0)))
+    hsa = wa.hsa.HSAAttention(heads, D, block_size=128, proj_segment_len=seg).to(dev())
+    wa.hsa_stage.init_hsa_parameters(hsa)
+    with torch.no_grad():
+        hsa.gate_lin.weight.normal_(0, 0.05)
+    hsa.topk_per_head = torch.tensor([3, 9, 1, 25], dtype=torch.int32)
+    kc, vc = hsa.compress_kv_cache(k, v)
+    want, (index, num, _, used) = wa.hsa.hsa_attention(
+        q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
+        block_size=128, proj_segment_len=seg, topk_per_head=hsa.topk_per_head, return_routing=True)
+    assert used
+    shards = sharded.plan_kv_shards(kv_len, 128, 2, seg)
+    outs_s, lses_s, outs_l, lses_l = [], [], [], []
+    r, blk = hsa.proj_rank, 0
+    for i, (lo, hi) in enumerate(shards):
+        nb = -(-(hi - lo) // 128)
+        idx_l, num_l = sharded.local_selection(index, num, blk, blk + nb)
+        blk += nb
+        s_lo, s_hi = -(-lo // seg), (-(-hi // seg) if i == 0 else kv_len // seg)   # segments partitioned by start token
+        o_s, l_s, o_l, l_l, tuned = branches.hsa_partials(q, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(),
+                                                          kc[:, s_lo * r:s_hi * r].contiguous(),
+                                                          vc[:, s_lo * r:s_hi * r].contiguous(), idx_l, num_l, 128)
+        assert tuned
+        rows = lambda o: o.permute(0, 2, 1, 3).reshape(-1, D)
+        outs_s.append(rows(o_s)); lses_s.append(l_s.reshape(-1)); outs_l.append(rows(o_l)); lses_l.append(l_l.reshape(-1))
+    sp, _ = branches.merge_partials(torch.stack(outs_s), torch.stack(lses_s))
+    li, _ = branches.merge_partials(torch.stack(outs_l), torch.stack(lses_l))
+    back = lambda x: x.view(1, heads, q_len, D).permute(0, 2, 1, 3).contiguous()
+    got = branches.gate_combine(q, back(sp).to(torch.bfloat16), back(li), hsa.gate_lin, round_bf16=True)
+    max_abs, mean_rel = attention_error(to_np(got), to_np(want))
+    assert max_abs < MAX_ABS and mean_rel < MEAN_REL, (max_abs, mean_rel)

@@ -36,6 +36,8 @@ class HsaParams(C.Structure):
         ("k_proj", C.c_void_p), ("v_proj", C.c_void_p), ("gate_w", C.c_void_p), ("gate_b", C.c_void_p),
         ("topk_per_head", C.c_void_p), ("index_out", C.c_void_p), ("num_out", C.c_void_p),
         ("thresholds_out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("index_in", C.c_void_p), ("num_in", C.c_void_p), ("part_sparse", C.c_void_p), ("part_linear", C.c_void_p),
+        ("lse_sparse", C.c_void_p), ("lse_linear", C.c_void_p),
     ]
 
 

@@ -108,7 +108,7 @@ int validate(const wa_hsa_params *p) {
     WA_REQUIRE(p->block_size > 0, WA_ERR_ARG, "%s: block_size must be positive", what);
     WA_REQUIRE(p->Lc >= 0, WA_ERR_ARG, "%s: negative compressed length", what);
     WA_REQUIRE(valid_dtype(p->q.dtype) && valid_dtype(p->k.dtype) && p->k.dtype == p->v.dtype &&
-                   valid_dtype(p->out.dtype),
+                   (p->part_sparse || valid_dtype(p->out.dtype)),
                WA_ERR_ARG, "%s: bad or mismatched q/k/v/out dtypes", what);
     if (p->Lc > 0) {
         WA_REQUIRE(p->k_coarse.ptr && p->v_coarse.ptr, WA_ERR_ARG, "%s: compressed cache pointers are null", what);
@@ -163,12 +163,21 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
 
     // ---- routing (routing.py:45-118) ---------------------------------------------------------
     WA_REQUIRE(p->H <= 65535 && p->B <= 65535, WA_ERR_UNSUPPORTED, "%s: B, H must be <= 65535", what);
-    if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream)))
-        return rc;
-    if ((rc = wa_route_scores(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, block_attn, stream))) return rc;
-    if ((rc = wa_route_select(block_attn, p->B, p->H, w.Nq, w.Nkv, p->tau_min, p->tau_max, p->topk_per_head, index,
-                              num, nullptr, thresholds, gini, stream)))
-        return rc;
+    WA_REQUIRE((p->index_in == nullptr) == (p->num_in == nullptr), WA_ERR_ARG, "%s: index_in and num_in go together", what);
+    const bool partial = p->part_sparse != nullptr;
+    WA_REQUIRE(!partial || (p->part_linear && p->lse_sparse && p->lse_linear), WA_ERR_ARG,
+               "%s: partial-output mode needs all four of part_sparse, part_linear, lse_sparse, lse_linear", what);
+    if (p->index_in) {
+        index = const_cast<int32_t *>(p->index_in);
+        num = const_cast<int32_t *>(p->num_in);
+    } else {
+        if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream)))
+            return rc;
+        if ((rc = wa_route_scores(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, block_attn, stream))) return rc;
+        if ((rc = wa_route_select(block_attn, p->B, p->H, w.Nq, w.Nkv, p->tau_min, p->tau_max, p->topk_per_head, index,
+                                  num, nullptr, thresholds, gini, stream)))
+            return rc;
+    }
 
     // ---- compressed cache (attention.py:186-200) ----------------------------------------------
     wa_tensor4 kc = p->k_coarse, vc = p->v_coarse;
@@ -199,6 +208,18 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
                "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 128)", what);
 
     // ---- generic SIMT path --------------------------------------------------------------------
+    if (partial) {
+        wa_tensor4 ps{}, pl{};
+        ps.ptr = p->part_sparse; pl.ptr = p->part_linear;
+        ps.dtype = pl.dtype = WA_F32;
+        ps.stride_h = pl.stride_h = p->D;
+        ps.stride_l = pl.stride_l = (int64_t)p->H * p->D;
+        ps.stride_b = pl.stride_b = (int64_t)p->Lq * p->H * p->D;
+        if ((rc = wa_block_sparse_forward(&p->q, &p->k, &p->v, &ps, p->B, p->H, p->Lq, p->Lkv, p->D, p->block_size, index,
+                                          num, w.Nkv, nullptr, 1, 0, p->lse_sparse, stream)))
+            return rc;
+        return wa_linear_branch(&p->q, &kc, &vc, &pl, p->B, p->H, p->Lq, Lc, p->D, 0, p->lse_linear, stream);
+    }
     wa_tensor4 sparse{}, linear{};
     sparse.ptr = ws + w.sparse; sparse.dtype = WA_BF16;
     linear.ptr = ws + w.linear; linear.dtype = lin_dtype;

@@ -33,9 +33,9 @@ constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
 constexpr int TMEM_COLS = 512;       // two S buffers: columns [0,128), [128,256); O: [256,384); parked sparse result: [384,448)
 constexpr int Q_STAGES = 2;          // the staged output of item j leaves from one Q buffer while item j+1 loads the other
-constexpr int KV_STAGES = 2;         // shared-memory ring depth for K tiles
+constexpr int KV_STAGES = 3;         // shared-memory ring depth for K tiles
 constexpr int V_STAGES = 2;          // shared-memory ring depth for V tiles
-constexpr int SMEM_BYTES = (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES + 1024 /*alignment slack*/ + 4096 /*barriers, bias, exchange*/;
+constexpr int SMEM_BYTES = (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES + 3072 /*barriers, bias, exchange*/;
 constexpr long long WAIT_CYCLES = 4000000000ll;
 
 // Optional event trace for kernel tuning (compile with -DWA_SM100_TRACE): CTA 0 appends
@@ -322,8 +322,10 @@ struct Barriers {
     int valid[8];            // real token count of the K-type tiles in flight, ring indexed by global tile number
     float bias[TILE];        // gate bias
     float xch[2][2][TILE];   // row-maximum exchange between the two threads of a row: [tile parity][half][row]
-    float lx[2][TILE];       // row-sum exchange at the end of a branch
 };
+
+static_assert(sizeof(Barriers) <= 3072, "barrier block exceeds its shared-memory budget");
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
 
 // ---- the kernel ----------------------------------------------------------------------------------
 // The three roles run their own loops over work items and meet only at mbarriers, so the producer
@@ -334,8 +336,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
                      const __grid_constant__ CUtensorMap tm_vc, const __grid_constant__ CUtensorMap tm_w,
                      const __grid_constant__ CUtensorMap tm_out, const Params p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];   // swizzled TMA tiles need 1024-byte alignment (checked below)
     uint8_t *q_s = smem, *k_s = smem + Q_STAGES * TILE_BYTES, *v_s = smem + (Q_STAGES + KV_STAGES) * TILE_BYTES;
     Barriers *bar = reinterpret_cast<Barriers *>(smem + (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES);
 
@@ -343,6 +344,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     volatile int *abort_flag = &bar->abort_flag;
 
     if (threadIdx.x == 0) {
+        bar->abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;   // misaligned shared memory: give up before any TMA
+        if (bar->abort_flag) atomicExch(p.error_flag, 99);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar->item_full[i], 1);
             mbar_init(&bar->item_empty[i], 1 + 256 + 1);   // MMA leader + every softmax thread + store warp
@@ -365,7 +368,6 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_init(&bar->pv_done, 1);
         mbar_init(&bar->o_done, 1);
         mbar_init(&bar->o_free, 256);
-        bar->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (threadIdx.x >= 64 && threadIdx.x < 64 + TILE) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
@@ -679,10 +681,11 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
                 if (!ok) break;
                 // ---- end of a branch: total row sum, then read the accumulator ----
-                bar->lx[half][row] = l;
+                // (the exchange buffer of parity t1 was last read two tiles ago, so it is free here)
+                bar->xch[t1 & 1][half][row] = l;
                 asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-                l += bar->lx[half ^ 1][row];
-                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // lx is reused by the next branch
+                l += bar->xch[t1 & 1][half ^ 1][row];
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // the next branch's first tile reuses this buffer
                 if (t1 > t0) {
                     ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
                     if (!ok) break;
@@ -1010,9 +1013,10 @@ bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, c
     using namespace sm100;
     if (p->D != TILE || p->block_size != TILE || Lc <= 0) return false;
     if (!view_ok(&p->q) || !view_ok(&p->k) || !view_ok(&p->v) || !view_ok(kc) || !view_ok(vc)) return false;
-    if (p->out.dtype != WA_BF16 || !p->out.ptr || (uintptr_t)p->out.ptr % 16 || p->out.stride_h % 8 || p->out.stride_l % 8 ||
-        p->out.stride_b % 8)
+    if (!p->part_sparse && (p->out.dtype != WA_BF16 || !p->out.ptr || (uintptr_t)p->out.ptr % 16 || p->out.stride_h % 8 ||
+                            p->out.stride_l % 8 || p->out.stride_b % 8))
         return false;
+    if (p->part_sparse && (((uintptr_t)p->part_sparse | (uintptr_t)p->part_linear) % 16)) return false;
     if ((long long)p->B * p->H * ceil_div(p->Lq, TILE) > (1 << 24)) return false;
     return device_is_sm100() && encode_fn() != nullptr;
 }
@@ -1035,7 +1039,7 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     if ((rc = make_map_4d(&tkc, kc, p->B, Lc, p->H, "k_coarse"))) return rc;
     if ((rc = make_map_4d(&tvc, vc, p->B, Lc, p->H, "v_coarse"))) return rc;
     if ((rc = make_map_w(&tw, w_bf16))) return rc;
-    if ((rc = make_map_4d(&tout, &p->out, p->B, p->Lq, p->H, "out"))) return rc;
+    if ((rc = make_map_4d(&tout, p->part_sparse ? &p->q : &p->out, p->B, p->Lq, p->H, "out"))) return rc;   // unused in partial mode
 
     const int n_items = p->B * p->H * Nq;
     schedule_kernel<<<p->gate_w ? 1 + TILE * TILE / 1024 : 1, 1024, 0, stream>>>(
@@ -1050,7 +1054,8 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.gate_bias = bias; kp.has_gate = p->gate_w != nullptr;
     kp.q = (const __nv_bfloat16 *)p->q.ptr; kp.qsb = p->q.stride_b; kp.qsl = p->q.stride_l; kp.qsh = p->q.stride_h;
     kp.scale_log2 = (float)(pow((double)TILE, -0.5) * 1.4426950408889634);
-    kp.part_sparse = kp.part_linear = kp.lse_sparse = kp.lse_linear = nullptr;
+    kp.part_sparse = p->part_sparse; kp.part_linear = p->part_linear;
+    kp.lse_sparse = p->lse_sparse; kp.lse_linear = p->lse_linear;
 
 
     static bool attr_set = false;

@@ -9,7 +9,7 @@ import torch
 
 from .. import _lib
 
-__all__ = ["sparse_branch", "linear_branch", "gate_combine", "merge_partials"]
+__all__ = ["sparse_branch", "linear_branch", "gate_combine", "merge_partials", "hsa_partials"]
 
 
 def sparse_branch(q, k, v, index, num, block_size: int, *, kv_len: int | None = None, lse: bool = True,
@@ -72,3 +72,42 @@ def merge_partials(outs: torch.Tensor, lses: torch.Tensor):
     _lib.check(_lib.lib().wa_merge_partials(outs.data_ptr(), lses.data_ptr(), g, rows, d, out.data_ptr(),
                                             lse.data_ptr(), _lib.stream_ptr(dev)))
     return out, lse
+
+
+def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, force_generic: bool = False):
+    """Both branches over one key shard, in one `wa_hsa_forward` call with the routing supplied.
+
+    `index` / `num` are the routing restricted to this shard (`sharded.local_selection`).  Returns
+    `(sparse, lse_sparse, linear, lse_linear, used_tuned)`: float32 `[B, Lq, H, D]` normalised branch
+    outputs and `[B, H, Lq]` natural-log normalisers, ready for `merge_partials`.  The tcgen05 kernel
+    runs when the shape qualifies (bf16, head_dim 128, 128-token blocks), the SIMT kernels otherwise.
+    """
+    import ctypes
+    from .attention import _unit_last, _workspace
+    dev = _lib.require_cuda(q, k, v, k_coarse, v_coarse, index, num)
+    bsz, q_len, heads, head_dim = q.shape
+    p = _lib.HsaParams()
+    p.B, p.H, p.D, p.Lq, p.Lkv, p.Lc = bsz, heads, head_dim, q_len, k.shape[1], k_coarse.shape[1]
+    p.block_size = int(block_size)
+    p.flags = _lib.WA_HSA_FORCE_GENERIC if force_generic else 0
+    q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
+    k_coarse, v_coarse = _unit_last(k_coarse.to(v_coarse.dtype)), _unit_last(v_coarse)
+    p.q, p.k, p.v = _lib.t4_blhd(q), _lib.t4_blhd(k), _lib.t4_blhd(v)
+    p.k_coarse, p.v_coarse = _lib.t4_blhd(k_coarse), _lib.t4_blhd(v_coarse)
+    index = index.to(torch.int32).contiguous()
+    num = num.to(torch.int32).contiguous()
+    if index.shape[-1] != -(-k.shape[1] // block_size):
+        raise ValueError("index rows must span exactly this shard's key blocks")
+    p.index_in, p.num_in = index.data_ptr(), num.data_ptr()
+    sparse = torch.empty((bsz, q_len, heads, head_dim), device=dev, dtype=torch.float32)
+    linear = torch.empty_like(sparse)
+    lse_s = torch.empty((bsz, heads, q_len), device=dev, dtype=torch.float32)
+    lse_l = torch.empty_like(lse_s)
+    p.part_sparse, p.part_linear = sparse.data_ptr(), linear.data_ptr()
+    p.lse_sparse, p.lse_linear = lse_s.data_ptr(), lse_l.data_ptr()
+    lib = _lib.lib()
+    ws = _workspace(dev, lib.wa_hsa_workspace_bytes(ctypes.byref(p)))
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    used = ctypes.c_int(0)
+    _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
+    return sparse, lse_s, linear, lse_l, bool(used.value)

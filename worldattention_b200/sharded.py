@@ -171,17 +171,22 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     block_lo = sum(blocks_per_rank[:rank])
     index_l, num_l = local_selection(routing.index, routing.num, block_lo, block_lo + blocks_per_rank[rank])
 
-    # partials over what this rank owns
-    if n_local > 0:
-        o_s, l_s = branches.sparse_branch(q, k_local, v_local, index_l, num_l, bs, kv_len=n_local)
+    # partials over what this rank owns: one fused call when the shard has keys and compressed slots
+    has_kv = n_local > 0
+    has_coarse = kc_local is not None and kc_local.shape[1] > 0
+    if has_kv and has_coarse:
+        o_s, l_s, o_l, l_l, _ = branches.hsa_partials(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
     else:
-        o_s = q.new_zeros((bsz, q_len, heads, head_dim), dtype=torch.float32)
-        l_s = q.new_full((bsz, heads, q_len), float("-inf"), dtype=torch.float32)
-    if kc_local is not None and kc_local.shape[1] > 0:
-        o_l, l_l = branches.linear_branch(q, kc_local, vc_local)
-    else:
-        o_l = torch.zeros_like(o_s)
-        l_l = torch.full_like(l_s, float("-inf"))
+        if has_kv:
+            o_s, l_s = branches.sparse_branch(q, k_local, v_local, index_l, num_l, bs, kv_len=n_local)
+        else:
+            o_s = q.new_zeros((bsz, q_len, heads, head_dim), dtype=torch.float32)
+            l_s = q.new_full((bsz, heads, q_len), float("-inf"), dtype=torch.float32)
+        if has_coarse:
+            o_l, l_l = branches.linear_branch(q, kc_local, vc_local)
+        else:
+            o_l = torch.zeros_like(o_s)
+            l_l = torch.full_like(l_s, float("-inf"))
 
     # exchange + merge (rows ordered [B, H, Lq] to match the normalisers)
     def rows(o):
