@@ -38,6 +38,9 @@ WORKLOADS = {
     "c5": dict(q_frames=3, kv_frames=480, block=64, topk=32, seed=4, scale=1.0),
 }
 L2_FLUSH_BYTES = 256 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum of one hsa_fwd_sm100_kernel launch on workload c2
+# (ncu capture summarised in profiles/hsa_fwd_sm100_config2.md)
+NCU_TRAFFIC_BYTES = 170.8e6
 
 
 # ------------------------------------------------------------------------------------------------
@@ -99,44 +102,45 @@ def algorithmic_flops(num: np.ndarray, index: np.ndarray, q_len, kv_len, block, 
 # clocks sampler
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU during the timed region (NVML reads only)."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, gpu_index: int):
-        self.samples, self.proc, self.thread = [], None, None
-        self.gpu_index = gpu_index
+    def __init__(self, gpu_index: int, period_s: float = 0.002):
+        self.gpu_index, self.period_s = gpu_index, period_s
+        self.sm, self.mask, self.max_mhz = [], 0, None
+        self.thread, self.stop_flag, self.error = None, threading.Event(), None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.gpu_index]) if visible and visible.split(",")[self.gpu_index].isdigit() else self.gpu_index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception as err:  # noqa: BLE001
+            self.error = f"NVML unavailable: {err}"
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+
+        def loop():
+            while not self.stop_flag.is_set():
+                try:
+                    self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                    self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                except Exception:  # noqa: BLE001
+                    pass
+                time.sleep(self.period_s)
+        self.thread = threading.Thread(target=loop, daemon=True)
         self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 6:
-                self.samples.append(parts)
-
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error or "not sampled"]}
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        reasons = [name for name, bit in self.REASONS.items() if self.mask & bit]
+        return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.sm)}
 
 
 def measured_peaks():
@@ -214,7 +218,8 @@ def reference_arm(args):
 
 def workload_config(name, n_gpus):
     spec = WORKLOADS[name]
-    sharding = "none" if n_gpus == 1 else ("head-split" if HEADS % n_gpus == 0 and n_gpus <= 4 else "kv-shard+lse-merge")
+    sharding = "none" if n_gpus == 1 else ("head-split, no data-path collective (outputs stay head-sharded)"
+                                           if HEADS % n_gpus == 0 and n_gpus <= 4 else "kv-shard + LSE merge over NCCL")
     return {
         "workload": f"{name}: HSA layer forward, B=1 H={HEADS} D={HEAD_DIM}, q={spec['q_frames'] * FRAME_TOKENS} "
                     f"kv={spec['kv_frames'] * FRAME_TOKENS} tokens, block {spec['block']}, top-k {spec['topk']}, seed {spec['seed']}",
@@ -301,17 +306,26 @@ def bench_hkv(dev, steps=5, layers=30, pages_total=480, pages_hot=64, topk=16):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
     ap.add_argument("--no-hkv", action="store_true")
+    ap.add_argument("--hkv-only", action="store_true", help="run only the HKV retrieval measurement (one GPU)")
+    ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the HKV measurement (30 = BASELINE config 3)")
     ap.add_argument("--shard", default="auto", choices=["auto", "heads", "kv"], help="sharding for --gpus > 1")
+    ap.add_argument("--gather-heads", action="store_true",
+                    help="head split: also all-gather the outputs (off: they stay head-sharded for a head-parallel consumer)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.hkv_only:
+        torch.cuda.set_device(0)
+        print(json.dumps({"metric": "hkv_gather_gbs", "hkv": bench_hkv(torch.device("cuda", 0), layers=args.hkv_layers)}),
+              flush=True)
         return
     args.warmup = max(args.warmup, 3)
 
@@ -385,7 +399,8 @@ def main():
                                             force_generic=args.force_generic)
             if mode == "heads":
                 return sharded.hsa_attention_head_split(hsa, q, k, v, k_coarse=kc, v_coarse=vc,
-                                                        topk_local=hsa.topk_per_head, head_plan=plan)
+                                                        topk_local=hsa.topk_per_head, head_plan=plan,
+                                                        gather=args.gather_heads)
             return sharded.hsa_attention_kv_sharded(hsa, q, k_loc, v_loc, kc, vc, kv_len=kv_len, shards=shards,
                                                     topk_per_head=hsa.topk_per_head)
 
@@ -502,7 +517,9 @@ def main():
         "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, world),
         "roofline": {
             "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": (achieved / peak_tf) if achieved else None, "traffic": None, "peak_source": peak_src,
+            "frac": (achieved / peak_tf) if achieved else None,
+            "traffic": NCU_TRAFFIC_BYTES if (used_tuned and world == 1 and args.workload == "c2") else None,
+            "peak_source": peak_src,
             "kernel": "hsa_fwd_sm100 (tcgen05: sparse + linear + gate)" if used_tuned else "generic_attention_kernel (SIMT sparse branch)",
             "kernel_ms": kernel_ms,
             "flops": {"sparse": sparse_f, "linear": linear_f, "gate": gate_f, "counted": flops},
@@ -523,7 +540,7 @@ def main():
     if world == 1 and not args.no_hkv:
         del q, k, v, flush
         torch.cuda.empty_cache()
-        line["hkv"] = bench_hkv(dev)
+        line["hkv"] = bench_hkv(dev, layers=args.hkv_layers)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -223,6 +223,47 @@ gate_combine_kernel(View4 q, View4 sp, View4 li, void *out, int out_dtype, long 
     }
 }
 
+// Same operation with the gate weight staged in shared memory (head_dim <= 128): a persistent grid, each
+// warp walks over (batch, token, head) vectors, a lane produces outputs lane, lane + 32, ...
+constexpr int GS_WARPS = 8;
+
+__global__ void __launch_bounds__(GS_WARPS * 32)
+gate_combine_smem_kernel(View4 q, View4 sp, View4 li, void *out, int out_dtype, long long osb, long long osl,
+                         long long osh, long long n_vec, int L, int H, int D, const void *gw, const void *gb, int gdt,
+                         int round_gate) {
+    extern __shared__ float gs_smem[];
+    const int ldw = D + 1;
+    float *ws = gs_smem;                       // [D][D + 1]
+    float *bs = ws + D * ldw;                  // [D]
+    float *qv = bs + D + (threadIdx.x >> 5) * D;   // [GS_WARPS][D]
+    for (int e = threadIdx.x; e < D * D; e += GS_WARPS * 32) ws[(e / D) * ldw + (e % D)] = load_elem(gw, gdt, e);
+    for (int e = threadIdx.x; e < D; e += GS_WARPS * 32) bs[e] = gb ? load_elem(gb, gdt, e) : 0.f;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const long long stride = (long long)gridDim.x * GS_WARPS;
+    for (long long vec = (long long)blockIdx.x * GS_WARPS + (threadIdx.x >> 5); vec < n_vec; vec += stride) {
+        const int h = (int)(vec % H);
+        const int l = (int)((vec / H) % L);
+        const int b = (int)(vec / ((long long)H * L));
+        const long long qoff = (long long)b * q.sb + (long long)l * q.sl + (long long)h * q.sh;
+        __syncwarp();
+        for (int d = lane; d < D; d += 32) qv[d] = load_elem(q.ptr, q.dtype, qoff + d);
+        __syncwarp();
+        const long long soff = (long long)b * sp.sb + (long long)l * sp.sl + (long long)h * sp.sh;
+        const long long loff = (long long)b * li.sb + (long long)l * li.sl + (long long)h * li.sh;
+        const long long ooff = (long long)b * osb + (long long)l * osl + (long long)h * osh;
+        for (int e = lane; e < D; e += 32) {
+            float z = bs[e];
+            const float *w = ws + e * ldw;
+            for (int d = 0; d < D; ++d) z = fmaf(qv[d], w[d], z);
+            float g = 1.0f / (1.0f + expf(-z));
+            if (round_gate) g = bf16_round_f(g);
+            store_elem(out, out_dtype, ooff + e,
+                       fmaf(load_elem(li.ptr, li.dtype, loff + e), g, load_elem(sp.ptr, sp.dtype, soff + e)));
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Merge shard partials of one softmax branch.
 // ------------------------------------------------------------------------------------------------
@@ -317,6 +358,25 @@ extern "C" int wa_gate_combine(const wa_tensor4 *q, const wa_tensor4 *sparse, co
     const long long n_vec = (long long)B * L * H;
     const long long blocks = (n_vec + GC_WARPS - 1) / GC_WARPS;
     WA_REQUIRE(blocks < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: too many tokens", what);
+    if (gate_w && D <= 128) {
+        const size_t smem2 = ((size_t)D * (D + 1) + D + (size_t)GS_WARPS * D) * sizeof(float);
+        static bool attr_set = false;
+        if (smem2 > 48 * 1024 && !attr_set) {
+            cudaError_t e = cudaFuncSetAttribute(gate_combine_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)(((size_t)128 * 129 + 128 + GS_WARPS * 128) * sizeof(float)));
+            if (e != cudaSuccess) return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
+            attr_set = true;
+        }
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long want = (n_vec + GS_WARPS - 1) / GS_WARPS;
+        const unsigned grid = (unsigned)(want < 2ll * sms ? want : 2ll * sms);
+        gate_combine_smem_kernel<<<grid, GS_WARPS * 32, smem2, (cudaStream_t)stream>>>(
+            make_view(q), make_view(sparse), make_view(linear), out->ptr, out->dtype, out->stride_b, out->stride_l,
+            out->stride_h, n_vec, L, H, D, gate_w, gate_b, gate_dtype, round_gate_bf16);
+        return check_launch(what);
+    }
     const size_t smem = (size_t)GC_WARPS * D * sizeof(float);
     WA_REQUIRE(smem <= 48 * 1024, WA_ERR_UNSUPPORTED, "%s: head_dim %d too large", what, D);
     gate_combine_kernel<<<(unsigned)blocks, GC_WARPS * 32, smem, (cudaStream_t)stream>>>(
