@@ -54,7 +54,7 @@ extern "C" const char *wa_last_error(void) { return last_error_buffer(); }
 namespace {
 
 struct Workspace {
-    size_t q_pooled, k_pooled, block_attn, index, num, gini, thresholds, kc, vc, sparse, linear, tuned, total;
+    size_t q_pooled, k_pooled, block_attn, index, num, gini, thresholds, counters, kc, vc, sparse, linear, tuned, total;
     int Nq, Nkv, Lc_inline;
 };
 
@@ -89,6 +89,7 @@ Workspace plan(const wa_hsa_params *p) {
     w.num = take(c, bh * w.Nq * sizeof(int32_t));
     w.gini = take(c, bh * w.Nq * sizeof(float));
     w.thresholds = take(c, (size_t)p->H * sizeof(float));
+    w.counters = take(c, ((size_t)p->H + 1) * sizeof(int));
     const size_t kvsz = dtype_size(p->k.dtype);
     w.kc = take(c, (size_t)p->B * w.Lc_inline * p->H * p->D * kvsz);
     w.vc = take(c, (size_t)p->B * w.Lc_inline * p->H * p->D * kvsz);
@@ -167,45 +168,55 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
     const bool partial = p->part_sparse != nullptr;
     WA_REQUIRE(!partial || (p->part_linear && p->lse_sparse && p->lse_linear), WA_ERR_ARG,
                "%s: partial-output mode needs all four of part_sparse, part_linear, lse_sparse, lse_linear", what);
-    if (p->index_in) {
-        index = const_cast<int32_t *>(p->index_in);
-        num = const_cast<int32_t *>(p->num_in);
-    } else {
-        if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream)))
-            return rc;
-        if ((rc = wa_route_scores(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, block_attn, stream))) return rc;
-        if ((rc = wa_route_select(block_attn, p->B, p->H, w.Nq, w.Nkv, p->tau_min, p->tau_max, p->topk_per_head, index,
-                                  num, nullptr, thresholds, gini, stream)))
-            return rc;
-    }
-
-    // ---- compressed cache (attention.py:186-200) ----------------------------------------------
+    // ---- compressed cache views (attention.py:186-200); the kernel runs after routing ----------
     wa_tensor4 kc = p->k_coarse, vc = p->v_coarse;
     int Lc = p->Lc;
-    if (Lc == 0) {
+    const bool compress_inline = Lc == 0;
+    if (compress_inline) {
         Lc = w.Lc_inline;
         kc.ptr = ws + w.kc; vc.ptr = ws + w.vc;
         kc.dtype = vc.dtype = p->k.dtype;
         kc.stride_h = vc.stride_h = p->D;
         kc.stride_l = vc.stride_l = (int64_t)p->H * p->D;
         kc.stride_b = vc.stride_b = (int64_t)Lc * p->H * p->D;
+    }
+    const int lin_dtype = vc.dtype;
+    const bool tuned = !(p->flags & WA_HSA_FORCE_GENERIC) && hsa_sm100_supported(p, Lc, &kc, &vc);
+    WA_REQUIRE(tuned || !(p->flags & WA_HSA_REQUIRE_TUNED), WA_ERR_UNSUPPORTED,
+               "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 128)", what);
+
+    bool prepared = false;
+    if (p->index_in) {
+        index = const_cast<int32_t *>(p->index_in);
+        num = const_cast<int32_t *>(p->num_in);
+    } else {
+        // pooling, then scores + sort + thresholds + counts (+ the tcgen05 kernel's work order) in one launch
+        int *counters = (int *)(ws + w.counters);
+        if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream,
+                              counters, p->H + 1)))
+            return rc;
+        SchedJob job{};
+        if (tuned) job = hsa_sm100_sched_job(p, ws + w.tuned);
+        if ((rc = route_fused_launch(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, p->tau_min, p->tau_max,
+                                     p->topk_per_head, block_attn, index, num, thresholds, gini, counters, job, stream)))
+            return rc;
+        prepared = tuned;
+    }
+
+    if (compress_inline) {
         if ((rc = wa_compress_kv(&p->k, &p->v, &kc, &vc, p->B, p->Lkv, p->H, p->D, p->proj_segment_len,
                                  p->block_size, p->k_proj, p->v_proj, p->proj_dtype, p->proj_rank, p->proj_cols,
                                  stream)))
             return rc;
     }
-    const int lin_dtype = vc.dtype;
 
     // ---- tuned tcgen05 path -------------------------------------------------------------------
-    const bool want_tuned = !(p->flags & WA_HSA_FORCE_GENERIC);
-    if (want_tuned && hsa_sm100_supported(p, Lc, &kc, &vc)) {
-        rc = hsa_sm100_launch(p, Lc, &kc, &vc, index, num, w.Nq, w.Nkv, ws + w.tuned, stream);
+    if (tuned) {
+        rc = hsa_sm100_launch(p, Lc, &kc, &vc, index, num, w.Nq, w.Nkv, ws + w.tuned, prepared, stream);
         if (rc) return rc;
         if (used_tuned) *used_tuned = 1;
         return 0;
     }
-    WA_REQUIRE(!(p->flags & WA_HSA_REQUIRE_TUNED), WA_ERR_UNSUPPORTED,
-               "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 128)", what);
 
     // ---- generic SIMT path --------------------------------------------------------------------
     if (partial) {

@@ -831,64 +831,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
 }
 
-// ---- work ordering: heaviest items first (counting sort on the selected-block count) ---------------
-constexpr int SCHED_BINS = 4096;
+// ---- launch preparation as a kernel of its own (used when the routing kernel has not done it) --------
 __global__ void __launch_bounds__(1024)
-schedule_kernel(const int32_t *__restrict__ num, int n_items, int Nkv, int32_t *__restrict__ order, int *work_counter,
-                int *error_flag, const void *gate_w, const void *gate_b, int gate_dt, __nv_bfloat16 *w_out,
-                float *b_out) {
+schedule_kernel(const int32_t *__restrict__ num, int n_items, int Nkv, SchedJob job) {
     if (blockIdx.x > 0) {
-        // blocks 1..16: gate weight -> bf16, bias -> float32 (the weight is an MMA operand)
-        const int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
-        if (i < TILE * TILE) w_out[i] = __float2bfloat16_rn(load_elem(gate_w, gate_dt, i));
-        if (i < TILE) b_out[i] = gate_b ? load_elem(gate_b, gate_dt, i) : 0.f;
+        if (job.gate_w) convert_gate_slice(job, (blockIdx.x - 1) * 1024, 1024);
         return;
     }
-    __shared__ int hist[SCHED_BINS];
-    for (int i = threadIdx.x; i < SCHED_BINS; i += blockDim.x) hist[i] = 0;
-    if (threadIdx.x == 0) {
-        *work_counter = 0;
-        *error_flag = 0;
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
-        const int key = max(0, min(min(num[i], Nkv), SCHED_BINS - 1));
-        atomicAdd(&hist[SCHED_BINS - 1 - key], 1);   // bin 0 = heaviest
-    }
-    __syncthreads();
-    // exclusive prefix over the bins: four bins per thread, then a block scan of the per-thread totals
-    __shared__ int warp_tot[32];
-    const int b0 = threadIdx.x * 4;
-    const int c0 = hist[b0], c1 = hist[b0 + 1], c2 = hist[b0 + 2], c3 = hist[b0 + 3];
-    int incl = c0 + c1 + c2 + c3;
-    const int mine = incl;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if ((threadIdx.x & 31) >= o) incl += v;
-    }
-    if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = incl;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        int w = warp_tot[threadIdx.x];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, w, o);
-            if (threadIdx.x >= o) w += v;
-        }
-        warp_tot[threadIdx.x] = w;
-    }
-    __syncthreads();
-    int base = incl - mine + ((threadIdx.x >> 5) ? warp_tot[(threadIdx.x >> 5) - 1] : 0);
-    hist[b0] = base;
-    hist[b0 + 1] = base + c0;
-    hist[b0 + 2] = base + c0 + c1;
-    hist[b0 + 3] = base + c0 + c1 + c2;
-    __syncthreads();
-    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
-        const int key = max(0, min(min(num[i], Nkv), SCHED_BINS - 1));
-        order[atomicAdd(&hist[SCHED_BINS - 1 - key], 1)] = i;
-    }
+    schedule_items(num, n_items, Nkv, job.order, job.work_counter, job.error_flag);
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -997,6 +947,19 @@ extern "C" int wa_trace_read(long long *dst, int max_words) {
 size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p) { return sm100::tuned_plan(p).total; }
 size_t hsa_sm100_status_offset(const wa_hsa_params *p) { return sm100::tuned_plan(p).counter + sizeof(int); }
 
+SchedJob hsa_sm100_sched_job(const wa_hsa_params *p, void *workspace) {
+    const sm100::TunedWs w = sm100::tuned_plan(p);
+    char *ws = (char *)workspace;
+    SchedJob job{};
+    job.order = (int32_t *)(ws + w.order);
+    job.work_counter = (int *)(ws + w.counter);
+    job.error_flag = job.work_counter + 1;
+    job.gate_w = p->gate_w; job.gate_b = p->gate_b; job.gate_dt = p->gate_dtype;
+    job.w_out = (__nv_bfloat16 *)(ws + w.w_bf16);
+    job.b_out = (float *)(ws + w.bias);
+    return job;
+}
+
 static bool device_is_sm100() {
     static int cached = -1;
     if (cached < 0) {
@@ -1022,14 +985,13 @@ bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, c
 }
 
 int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc, const int32_t *index,
-                     const int32_t *num, int Nq, int Nkv, void *workspace, cudaStream_t stream) {
+                     const int32_t *num, int Nq, int Nkv, void *workspace, bool prepared, cudaStream_t stream) {
     using namespace sm100;
-    const TunedWs w = tuned_plan(p);
-    char *ws = (char *)workspace;
-    int32_t *order = (int32_t *)(ws + w.order);
-    int *counter = (int *)(ws + w.counter);
-    __nv_bfloat16 *w_bf16 = (__nv_bfloat16 *)(ws + w.w_bf16);
-    float *bias = (float *)(ws + w.bias);
+    const SchedJob job = hsa_sm100_sched_job(p, workspace);
+    int32_t *order = job.order;
+    int *counter = job.work_counter;
+    __nv_bfloat16 *w_bf16 = job.w_out;
+    float *bias = job.b_out;
 
     CUtensorMap tq, tk, tv, tkc, tvc, tw, tout;
     int rc;
@@ -1042,9 +1004,10 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     if ((rc = make_map_4d(&tout, p->part_sparse ? &p->q : &p->out, p->B, p->Lq, p->H, "out"))) return rc;   // unused in partial mode
 
     const int n_items = p->B * p->H * Nq;
-    schedule_kernel<<<p->gate_w ? 1 + TILE * TILE / 1024 : 1, 1024, 0, stream>>>(
-        num, n_items, Nkv, order, counter, counter + 1, p->gate_w, p->gate_b, p->gate_dtype, w_bf16, bias);
-    if ((rc = check_launch("wa_hsa_forward(schedule)"))) return rc;
+    if (!prepared) {
+        schedule_kernel<<<p->gate_w ? 1 + TILE * TILE / 1024 : 1, 1024, 0, stream>>>(num, n_items, Nkv, job);
+        if ((rc = check_launch("wa_hsa_forward(schedule)"))) return rc;
+    }
 
     Params kp{};
     kp.B = p->B; kp.H = p->H; kp.Lq = p->Lq; kp.Lkv = p->Lkv; kp.Lc = Lc; kp.Nq = Nq; kp.Nkv = Nkv;

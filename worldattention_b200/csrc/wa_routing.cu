@@ -4,7 +4,7 @@
 // of Q and K, then a few hundred short rows), so the kernels are plain coalesced / warp-shuffle
 // code; every reduction that feeds the discrete selection accumulates in float64 and rounds once,
 // which makes the chosen block ids independent of the summation order.
-#include "wa_common.cuh"
+#include "wa_internal.cuh"
 
 namespace wa {
 
@@ -17,9 +17,11 @@ template <bool VEC_BF16>
 __global__ void __launch_bounds__(POOL_THREADS)
 pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, int aligned,
                    float *__restrict__ pooled, View4 x2, int L2, int num_blocks2, int aligned2,
-                   float *__restrict__ pooled2) {
+                   float *__restrict__ pooled2, int *__restrict__ zero, int n_zero) {
     int nb = blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
+    if (n_zero && nb == 0 && h == 0 && b == 0)   // counters of the kernel that follows on the stream
+        for (int i = threadIdx.x; i < n_zero; i += POOL_THREADS) zero[i] = 0;
     if (nb >= num_blocks) {   // second tensor (keys) pooled by the same launch
         nb -= num_blocks;
         x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2;
@@ -39,14 +41,24 @@ pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks,
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (row < rows) {
             const __nv_bfloat16 *p = (const __nv_bfloat16 *)x.ptr + base + lane * 8;
-            for (int t = row; t < n_real; t += rows) {
-                uint4 raw = *reinterpret_cast<const uint4 *>(p + (long long)(t0 + t) * x.sl);
-                const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+            // eight row loads in flight per thread; rows past the end contribute zeros (same sum order as a plain loop)
+            for (int t = row; t < n_real; t += 8 * rows) {
+                uint4 raw[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float2 f = __bfloat1622float2(h2[i]);
-                    acc[2 * i] += f.x;
-                    acc[2 * i + 1] += f.y;
+                for (int u = 0; u < 8; ++u) {
+                    const int tt = t + u * rows;
+                    raw[u] = tt < n_real ? *reinterpret_cast<const uint4 *>(p + (long long)(t0 + tt) * x.sl)
+                                         : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float2 f = __bfloat1622float2(h2[i]);
+                        acc[2 * i] += f.x;
+                        acc[2 * i + 1] += f.y;
+                    }
                 }
             }
         }
@@ -98,54 +110,161 @@ pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks,
 }
 
 // ------------------------------------------------------------------------------------------------
+// Pooling, streaming form for bf16 rows of 8..256 channels (a power of two): one WARP per (batch,
+// block, head), no block-level synchronisation, eight 16-byte row loads in flight per lane.  The
+// D/8 lanes that cover one token row form a group; the 32/(D/8) groups take token rows round-robin
+// and their partial sums are added in group order at the end.
+// ------------------------------------------------------------------------------------------------
+template <int UNROLL>
+__global__ void __launch_bounds__(POOL_THREADS)
+pool_warp_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, int aligned, float *__restrict__ pooled,
+                 View4 x2, int L2, int num_blocks2, int aligned2, float *__restrict__ pooled2, int B,
+                 int *__restrict__ zero, int n_zero) {
+    if (n_zero && blockIdx.x == 0)   // counters of the kernel that follows on the stream
+        for (int i = threadIdx.x; i < n_zero; i += POOL_THREADS) zero[i] = 0;
+    const int lane = threadIdx.x & 31;
+    long long item = (long long)blockIdx.x * (POOL_THREADS / 32) + (threadIdx.x >> 5);   // ((b, block), head), head fastest
+    const long long items1 = (long long)B * num_blocks * H;
+    if (item >= items1) {   // second tensor (keys) pooled by the same launch
+        item -= items1;
+        if (item >= (long long)B * num_blocks2 * H) return;
+        x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2;
+    }
+    const int h = (int)(item % H);
+    const int nb = (int)((item / H) % num_blocks);
+    const int b = (int)(item / ((long long)H * num_blocks));
+    const int t0 = nb * block_size;
+    const int n_real = min(block_size, L - t0);
+    const int lanes_per_row = D >> 3, groups = 32 / lanes_per_row;
+    const int col = (lane % lanes_per_row) * 8, group = lane / lanes_per_row;
+    const __nv_bfloat16 *p = (const __nv_bfloat16 *)x.ptr + (long long)b * x.sb + (long long)h * x.sh +
+                             (long long)t0 * x.sl + col;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int t = group; t < n_real; t += UNROLL * groups) {
+        uint4 raw[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int tt = t + u * groups;
+            raw[u] = tt < n_real ? __ldg(reinterpret_cast<const uint4 *>(p + (long long)tt * x.sl)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h2[i]);
+                acc[2 * i] += f.x;
+                acc[2 * i + 1] += f.y;
+            }
+        }
+    }
+    // group g adds the partial of group g + step: (0 + 1), ((0 + 1) + (2 + 3)), ... a fixed tree
+    for (int step = lanes_per_row; step < 32; step <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], step);
+    }
+    if (group == 0) {
+        float out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            out[i] = aligned ? bf16_round_f((float)((double)acc[i] / (double)block_size))
+                             : __fdiv_rn(bf16_round_f(acc[i]), (float)n_real);
+        float4 *dst = reinterpret_cast<float4 *>(pooled + (((long long)b * H + h) * num_blocks + nb) * (long long)D + col);
+        dst[0] = make_float4(out[0], out[1], out[2], out[3]);
+        dst[1] = make_float4(out[4], out[5], out[6], out[7]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Block attention map.  One CTA per (b, h, query block) row; a warp per key block for the dot.
 // ------------------------------------------------------------------------------------------------
 constexpr int SCORE_THREADS = 256;
 
-__global__ void __launch_bounds__(SCORE_THREADS)
-route_scores_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int Nq, int Nkv,
-                    int D, float scale, float *__restrict__ attn) {
-    const long long row = blockIdx.x;  // (b*H + h)*Nq + i
-    const long long bh = row / Nq;
-    const float *q = qp + row * D;
-    const float *k = kp + bh * (long long)Nkv * D;
-    float *out = attn + row * Nkv;
-    __shared__ double red[SCORE_THREADS / 32];
-    __shared__ float bcast;
+#ifdef WA_ROUTE_TRACE   // tuning aid: per-CTA phase timestamps (ns) of the fused routing kernel
+__device__ long long g_route_trace[4096 * 8];
+#define ROUTE_STAMP(i)                                                                         \
+    do {                                                                                       \
+        if (threadIdx.x == 0 && blockIdx.x < 4096) {                                           \
+            long long t_;                                                                      \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
+            g_route_trace[blockIdx.x * 8 + (i)] = t_;                                          \
+        }                                                                                      \
+    } while (0)
+#else
+#define ROUTE_STAMP(i)
+#endif
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = SCORE_THREADS / 32;
-    for (int j0 = warp * 4; j0 < Nkv; j0 += nwarps * 4) {   // four independent dot products in flight
-        double acc[4] = {0.0, 0.0, 0.0, 0.0};
-        for (int d = lane; d < D; d += 32) {
-            const double qd = (double)q[d];
+// One row: out[j] = softmax_j(q . k_j * scale) with float64 dots and sums, each rounded once to float32.
+// `out` may be shared or global memory; `red` holds >= 32 doubles.  Called by every thread of the CTA.
+__device__ __forceinline__ void row_block_attention(const float *__restrict__ q, const float *__restrict__ k, int Nkv, int D,
+                                                    float scale, float *out, double *red, float *bcast) {
+    const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
+    const bool vec = (D & 3) == 0;
+    for (int j0 = warp * 8; j0 < Nkv; j0 += nwarps * 8) {   // eight independent dot products in flight
+        double acc[8] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+        if (vec) {
+            for (int d = lane * 4; d < D; d += 128) {
+                const float4 qv = *reinterpret_cast<const float4 *>(q + d);
+                float4 kv[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (j0 + u < Nkv) acc[u] = fma(qd, (double)k[(long long)(j0 + u) * D + d], acc[u]);
+                for (int u = 0; u < 8; ++u)
+                    kv[u] = j0 + u < Nkv ? *reinterpret_cast<const float4 *>(k + (long long)(j0 + u) * D + d)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    acc[u] = fma((double)qv.x, (double)kv[u].x, acc[u]);
+                    acc[u] = fma((double)qv.y, (double)kv[u].y, acc[u]);
+                    acc[u] = fma((double)qv.z, (double)kv[u].z, acc[u]);
+                    acc[u] = fma((double)qv.w, (double)kv[u].w, acc[u]);
+                }
+            }
+        } else {
+            for (int d = lane; d < D; d += 32) {
+                const double qd = (double)q[d];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (j0 + u < Nkv) acc[u] = fma(qd, (double)k[(long long)(j0 + u) * D + d], acc[u]);
+            }
         }
+        // transposed reduction: halve the number of live sums at each of the first three exchange steps,
+        // so the eight 32-lane sums cost 9 exchanges instead of 40; lane l ends with dot (l >> 2) & 7
+        const bool b16 = lane & 16, b8 = lane & 8, b4 = lane & 4;
+        double r4[4], r2[2];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const double t = warp_sum_d(acc[u]);
-            if (lane == 0 && j0 + u < Nkv) out[j0 + u] = __fmul_rn((float)t, scale);
+            const double keep = b16 ? acc[u + 4] : acc[u], give = b16 ? acc[u] : acc[u + 4];
+            r4[u] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
         }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const double keep = b8 ? r4[u + 2] : r4[u], give = b8 ? r4[u] : r4[u + 2];
+            r2[u] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+        }
+        double t = (b4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, b4 ? r2[0] : r2[1], 4);
+        t += __shfl_xor_sync(0xffffffffu, t, 2);
+        t += __shfl_xor_sync(0xffffffffu, t, 1);
+        const int u = (lane >> 2) & 7;
+        if ((lane & 3) == 0 && j0 + u < Nkv) out[j0 + u] = __fmul_rn((float)t, scale);
     }
     __syncthreads();
+    ROUTE_STAMP(1);
 
     float m = -INFINITY;
-    for (int j = threadIdx.x; j < Nkv; j += SCORE_THREADS) m = fmaxf(m, out[j]);
+    for (int j = threadIdx.x; j < Nkv; j += T) m = fmaxf(m, out[j]);
     m = warp_max(m);
     if (lane == 0) red[warp] = (double)m;
     __syncthreads();
     if (threadIdx.x == 0) {
         float mm = -INFINITY;
         for (int w = 0; w < nwarps; ++w) mm = fmaxf(mm, (float)red[w]);
-        bcast = mm;
+        *bcast = mm;
     }
     __syncthreads();
-    m = bcast;
+    m = *bcast;
     __syncthreads();
 
     double s = 0.0;
-    for (int j = threadIdx.x; j < Nkv; j += SCORE_THREADS) {
+    for (int j = threadIdx.x; j < Nkv; j += T) {
         float e = (float)exp((double)__fsub_rn(out[j], m));
         out[j] = e;
         s += (double)e;
@@ -156,11 +275,22 @@ route_scores_kernel(const float *__restrict__ qp, const float *__restrict__ kp, 
     if (threadIdx.x == 0) {
         double t = 0.0;
         for (int w = 0; w < nwarps; ++w) t += red[w];
-        bcast = (float)t;
+        *bcast = (float)t;
     }
     __syncthreads();
-    const float denom = bcast;
-    for (int j = threadIdx.x; j < Nkv; j += SCORE_THREADS) out[j] = __fdiv_rn(out[j], denom);
+    const float denom = *bcast;
+    for (int j = threadIdx.x; j < Nkv; j += T) out[j] = __fdiv_rn(out[j], denom);
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(SCORE_THREADS)
+route_scores_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int Nq, int Nkv,
+                    int D, float scale, float *__restrict__ attn) {
+    const long long row = blockIdx.x;  // (b*H + h)*Nq + i
+    const long long bh = row / Nq;
+    __shared__ double red[32];
+    __shared__ float bcast;
+    row_block_attention(qp + row * D, kp + bh * (long long)Nkv * D, Nkv, D, scale, attn + row * Nkv, red, &bcast);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -220,6 +350,32 @@ __global__ void route_sort_kernel(const float *__restrict__ attn, int Nkv, int n
     }
 }
 
+// Mean of a head's Gini rows over (batch, query block) -> the head's cumulative-mass threshold.  256 strided
+// float64 partials, a shuffle tree inside each warp, the eight warp totals added in order.  Called by every
+// thread of a CTA of >= 256 threads; `red` holds >= 8 doubles; the result is valid in every thread.
+__device__ __forceinline__ float head_threshold(const float *gini_rows, int B, int H, int Nq, int h, float tau_min,
+                                                float tau_span, double *red, float *bcast) {
+    const int count = B * Nq, tid = threadIdx.x;
+    if (tid < 256) {
+        double g = 0.0;
+        for (int r = tid; r < count; r += 256) {
+            const int bb = r / Nq, ii = r % Nq;
+            g += (double)__ldcg(&gini_rows[((long long)bb * H + h) * Nq + ii]);
+        }
+        g = warp_sum_d(g);
+        if ((tid & 31) == 0) red[tid >> 5] = g;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        const float head_gini = (float)(t / (double)count);
+        *bcast = __fadd_rn(tau_min, __fmul_rn(head_gini, tau_span));
+    }
+    __syncthreads();
+    return *bcast;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Selection, pass B: per-head threshold, float64 cumulative mass, count (and optional mask).
 // ------------------------------------------------------------------------------------------------
@@ -239,26 +395,9 @@ route_count_kernel(const float *__restrict__ attn, const int32_t *__restrict__ i
     __shared__ float thr_s;
     __shared__ int cnt_s;
 
-    // threshold of this head: mean of the Gini rows over (batch, query block)
-    double g = 0.0;
-    const int count = B * Nq;
-    for (int r = threadIdx.x; r < count; r += SELECT_THREADS) {
-        const int bb = r / Nq, ii = r % Nq;
-        g += (double)gini_rows[((long long)bb * H + h) * Nq + ii];
-    }
-    part[threadIdx.x] = g;
     if (threadIdx.x == 0) cnt_s = 0;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        double t = 0.0;
-        for (int w = 0; w < SELECT_THREADS; ++w) t += part[w];
-        const float head_gini = (float)(t / (double)count);
-        const float thr = __fadd_rn(tau_min, __fmul_rn(head_gini, tau_span));
-        thr_s = thr;
-        if (b == 0 && i == 0) thresholds[h] = thr;
-    }
-    __syncthreads();
-    const float thr = thr_s;
+    const float thr = head_threshold(gini_rows, B, H, Nq, h, tau_min, tau_span, part, &thr_s);
+    if (threadIdx.x == 0 && b == 0 && i == 0) thresholds[h] = thr;
     const float *p = attn + row * Nkv;
     const int32_t *idx = index + row * Nkv;
     uint8_t *mrow = mask ? mask + row * Nkv : nullptr;
@@ -296,6 +435,171 @@ route_count_kernel(const float *__restrict__ attn, const int32_t *__restrict__ i
 }
 
 // ------------------------------------------------------------------------------------------------
+// The forward's routing in ONE launch.  Each CTA owns a (batch, head, query block) row: scores,
+// softmax, sort and the row's Gini term, with the probabilities kept in shared memory.  The CTA that
+// finishes a head last (a counter per head) turns the head's Gini rows into its threshold and counts
+// every row of that head, a warp per row over the sorted probabilities; the CTA that finishes the
+// last head prepares the attention kernel's launch (work order, counters).  Same arithmetic as the
+// three separate kernels above; no CTA ever waits for another.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int B, int H, int Nq, int Nkv, int n_pow2,
+                   int D, float scale, float tau_min, float tau_span, const int32_t *__restrict__ fixed_num,
+                   float *sorted, int32_t *__restrict__ index, int32_t *num, float *__restrict__ thresholds,
+                   float *gini_rows, int *counters, SchedJob job, int gate_per_cta, int sm_count, int slots) {
+    extern __shared__ __align__(16) unsigned char fused_smem[];
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(fused_smem);   // max(n_pow2, threads)
+    float *probs = reinterpret_cast<float *>(keys + max(n_pow2, (int)blockDim.x));    // Nkv
+    __shared__ double red[256];
+    __shared__ float bcast;
+    __shared__ int last_flag;
+
+    const int T = blockDim.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = T >> 5;
+    // CTAs are dealt to the SMs round-robin, so CTAs b, b + sm_count, ... tend to share an SM: give them
+    // neighbouring rows (same head, same pooled keys) so that their key reads can meet in L1
+    const long long row = (long long)(blockIdx.x % sm_count) * slots + blockIdx.x / sm_count;
+    if (row >= (long long)B * H * Nq) return;
+    const long long bh = row / Nq;
+    const int h = (int)(bh % H);
+
+    ROUTE_STAMP(0);
+    if (job.order && job.gate_w) convert_gate_slice(job, (int)row * gate_per_cta, gate_per_cta);
+
+    row_block_attention(qp + row * D, kp + bh * (long long)Nkv * D, Nkv, D, scale, probs, red, &bcast);
+    ROUTE_STAMP(2);
+
+    if (n_pow2 <= T) {
+        // one key per thread in a register: exchange distances below 32 go through shuffles, the rest through smem
+        unsigned long long key = tid < Nkv ? (((unsigned long long)descending_key(probs[tid]) << 32) | (unsigned)tid)
+                                           : 0xFFFFFFFFFFFFFFFFull;
+        for (int k = 2; k <= n_pow2; k <<= 1) {
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                unsigned long long other;
+                if (j >= 32) {
+                    keys[tid] = key;
+                    __syncthreads();
+                    other = keys[tid ^ j];
+                    __syncthreads();
+                } else {
+                    other = __shfl_xor_sync(0xffffffffu, key, j);
+                }
+                const bool keep_min = ((tid & j) == 0) == ((tid & k) == 0);
+                key = (other < key) == keep_min ? other : key;
+            }
+        }
+        keys[tid] = key;
+        __syncthreads();
+    } else {
+        for (int j = tid; j < n_pow2; j += T)
+            keys[j] = j < Nkv ? (((unsigned long long)descending_key(probs[j]) << 32) | (unsigned)j)
+                              : 0xFFFFFFFFFFFFFFFFull;
+        __syncthreads();
+        for (int k = 2; k <= n_pow2; k <<= 1) {
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int i = tid; i < n_pow2; i += T) {
+                    const int ixj = i ^ j;
+                    if (ixj > i) {
+                        const unsigned long long a = keys[i], b = keys[ixj];
+                        const bool up = (i & k) == 0;
+                        if ((a > b) == up) {
+                            keys[i] = b;
+                            keys[ixj] = a;
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+    }
+    ROUTE_STAMP(3);
+    {
+        int32_t *idx = index + row * Nkv;
+        float *srow = sorted + row * Nkv;
+        double acc = 0.0;
+        for (int m = tid; m < Nkv; m += T) {
+            const int id = (int)(keys[m] & 0xFFFFFFFFull);
+            const float pm = probs[id];
+            idx[m] = id;
+            srow[m] = pm;
+            const float w = __fsub_rn((float)(Nkv + 1), __fmul_rn(2.0f, (float)(m + 1)));
+            acc += (double)__fmul_rn(w, pm);
+        }
+        acc = warp_sum_d(acc);
+        if (lane == 0) red[warp] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0.0;
+            for (int w = 0; w < nwarps; ++w) t += red[w];
+            gini_rows[row] = __fdiv_rn((float)t, (float)Nkv);
+        }
+    }
+
+    // ---- last CTA of this head? ------------------------------------------------------------------
+    const int rows_per_head = B * Nq;
+    ROUTE_STAMP(4);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last_flag = atomicAdd(&counters[1 + h], 1) == rows_per_head - 1;
+    __syncthreads();
+    ROUTE_STAMP(5);
+    if (!last_flag) return;
+    __threadfence();
+
+    const float thr = head_threshold(gini_rows, B, H, Nq, h, tau_min, tau_span, red, &bcast);
+    if (tid == 0) thresholds[h] = thr;
+
+    for (int r = warp; r < rows_per_head; r += nwarps) {
+        const int bb = r / Nq, ii = r % Nq;
+        const long long rid = ((long long)bb * H + h) * Nq + ii;
+        if (fixed_num) {
+            if (lane == 0) num[rid] = max(0, min(fixed_num[h], Nkv));
+            continue;
+        }
+        // float64 cumulative mass: a contiguous chunk per lane, lane totals prefixed in lane order
+        const float *p = sorted + rid * Nkv;
+        const int chunk = (Nkv + 31) / 32;
+        const int m0 = min(Nkv, lane * chunk), m1 = min(Nkv, m0 + chunk);
+        double local = 0.0;
+        for (int m = m0; m < m1; ++m) local += (double)__ldcg(p + m);
+        double run = 0.0;
+        for (int w = 0; w < 32; ++w) {
+            const double t = __shfl_sync(0xffffffffu, local, w);
+            if (w < lane) run += t;
+        }
+        int kept = 0;
+        for (int m = m0; m < m1; ++m) {
+            const float pm = __ldcg(p + m);
+            run += (double)pm;
+            kept += __fsub_rn((float)run, pm) < thr;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) kept += __shfl_xor_sync(0xffffffffu, kept, o);
+        if (lane == 0) num[rid] = kept;
+    }
+
+    // ---- last head? ------------------------------------------------------------------------------
+    ROUTE_STAMP(6);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last_flag = atomicAdd(&counters[0], 1) == H - 1;
+    __syncthreads();
+    if (!last_flag || !job.order) return;
+    __threadfence();
+    schedule_items(num, B * H * Nq, Nkv, job.order, job.work_counter, job.error_flag);
+    ROUTE_STAMP(7);
+}
+
+#ifdef WA_ROUTE_TRACE
+}  // namespace wa
+extern "C" int wa_route_trace_read(long long *dst, int n_ctas) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(dst, wa::g_route_trace, (size_t)n_ctas * 8 * sizeof(long long));
+    return 0;
+}
+namespace wa {
+#endif
+
+// ------------------------------------------------------------------------------------------------
 // Mask -> ascending index list.  One warp per row, ballot-ordered compaction.
 // ------------------------------------------------------------------------------------------------
 __global__ void map_to_index_kernel(const uint8_t *__restrict__ mask, long long rows, int Nkv,
@@ -329,22 +633,31 @@ static bool pool_vec_ok(const wa_tensor4 *x, int D) {
 
 // Pools `x` (and, when given, `y`, e.g. queries and keys of one forward) in a single launch.
 int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
-                int block_size, cudaStream_t stream) {
+                int block_size, cudaStream_t stream, int *zero, int n_zero) {
     const int nbx = ceil_div(Lx, block_size), nby = y ? ceil_div(Ly, block_size) : 0;
     View4 vx = make_view(x), vy = y ? make_view(y) : vx;
     dim3 grid(nbx + nby, H, B);
     const bool vec = pool_vec_ok(x, D) && (!y || pool_vec_ok(y, D));
-    if (vec) {
+    const int lanes = D / 8;
+    if (vec && D % 8 == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0 && ((uintptr_t)px % 16 == 0) &&
+        (!y || (uintptr_t)py % 16 == 0)) {
+        const long long items = (long long)B * H * (nbx + nby);
+        const long long ctas = (items + POOL_THREADS / 32 - 1) / (POOL_THREADS / 32);
+        WA_REQUIRE(ctas < (1ll << 31), WA_ERR_UNSUPPORTED, "wa_pool_blocks: too many blocks");
+        pool_warp_kernel<8><<<(unsigned)ctas, POOL_THREADS, 0, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0, px, vy,
+                                                                      Ly, nby, y ? Ly % block_size == 0 : 0, py, B, zero,
+                                                                      n_zero);
+    } else if (vec) {
         const int rows = POOL_THREADS / (D / 8);
         const size_t smem = (size_t)rows * D * sizeof(float);
         WA_REQUIRE(smem <= 48 * 1024, WA_ERR_UNSUPPORTED, "wa_pool_blocks: D=%d too large", D);
         pool_blocks_kernel<true><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
-                                                                       px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py);
+                                                                       px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py, zero, n_zero);
     } else {
         const int rows = D >= POOL_THREADS ? 1 : POOL_THREADS / D;
         const size_t smem = (size_t)rows * (D < POOL_THREADS ? D : POOL_THREADS) * sizeof(double);
         pool_blocks_kernel<false><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
-                                                                        px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py);
+                                                                        px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py, zero, n_zero);
     }
     return check_launch("wa_pool_blocks");
 }
@@ -401,6 +714,37 @@ int route_select_launch(const float *block_attn, int B, int H, int Nq, int Nkv, 
         block_attn, index, gini_scratch, B, H, Nq, Nkv, (float)tau_min, (float)(tau_max - tau_min),
         fixed_num_per_head, num, mask, thresholds);
     return check_launch("wa_route_select(count)");
+}
+}  // namespace wa
+
+namespace wa {
+int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int H, int Nq, int Nkv, int D, double tau_min,
+                       double tau_max, const int32_t *fixed_num_per_head, float *sorted, int32_t *index, int32_t *num,
+                       float *thresholds, float *gini, int *counters, const SchedJob &job, cudaStream_t stream) {
+    int n_pow2 = 1;
+    while (n_pow2 < Nkv) n_pow2 <<= 1;
+    WA_REQUIRE(n_pow2 <= 16384, WA_ERR_UNSUPPORTED, "wa_hsa_forward(routing): at most 16384 key blocks per row, got %d", Nkv);
+    const long long rows = (long long)B * H * Nq;
+    WA_REQUIRE(rows < (1ll << 31), WA_ERR_UNSUPPORTED, "wa_hsa_forward(routing): too many rows");
+    int threads = n_pow2 / 2;
+    threads = threads < 256 ? 256 : (threads > 1024 ? 1024 : threads);
+    const size_t smem = (size_t)(n_pow2 > threads ? n_pow2 : threads) * sizeof(unsigned long long) + (size_t)Nkv * sizeof(float);
+    if (smem > 24 * 1024) {   // static shared memory of the kernel takes ~19 KB of the default 48 KB
+        cudaError_t e = cudaFuncSetAttribute(route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(routing): %s", cudaGetErrorString(e));
+    }
+    const int gate_per_cta = (int)((128 * 128 + rows - 1) / rows);
+    int dev = 0, sm_count = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+        sm_count = 148;
+    if (rows < sm_count) sm_count = (int)rows;
+    const int slots = (int)((rows + sm_count - 1) / sm_count);
+    route_fused_kernel<<<(unsigned)((long long)sm_count * slots), threads, smem, stream>>>(
+        q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2, D, (float)pow((double)D, -0.5), (float)tau_min,
+        (float)(tau_max - tau_min), fixed_num_per_head, sorted, index, num, thresholds, gini, counters, job, gate_per_cta,
+        sm_count, slots);
+    return check_launch("wa_hsa_forward(routing)");
 }
 }  // namespace wa
 
