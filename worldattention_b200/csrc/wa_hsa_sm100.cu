@@ -28,10 +28,11 @@ namespace sm100 {
 
 constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
 constexpr int HALF = 64;             // key tokens per softmax / MMA pipeline step
-constexpr int THREADS = 352;         // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two threads per query row), warp 10 output store
+constexpr int THREADS = 384;         // warp 0 TMA, warp 1 QK products, warps 2..9 softmax (two threads per query row), warp 10 output store, warp 11 PV products
 constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
-constexpr int TMEM_COLS = 512;       // two S buffers: columns [0,128), [128,256); O: [256,384); parked sparse result: [384,448)
+constexpr int TMEM_COLS = 512;       // three S buffers: columns [0,128), [128,256), [256,384); O: [384,512)
+constexpr int S_BUFS = 3;            // score products run up to two tiles ahead of the softmax
 constexpr int Q_STAGES = 2;          // the staged output of item j leaves from one Q buffer while item j+1 loads the other
 constexpr int KV_STAGES = 3;         // shared-memory ring depth for K tiles
 constexpr int V_STAGES = 2;          // shared-memory ring depth for V tiles
@@ -42,8 +43,9 @@ constexpr long long WAIT_CYCLES = 4000000000ll;
 // (event id, clock) pairs from one thread per role to a global buffer.
 #ifdef WA_SM100_TRACE
 constexpr int TRACE_SLOTS = 8192;            // (id, clock) pairs per traced role
-__device__ long long g_trace[3][2 * TRACE_SLOTS];
-__device__ int g_trace_n[3];
+__device__ long long g_trace[4][2 * TRACE_SLOTS];
+__device__ int g_trace_n[4];
+#define WA_TRACE_ROLE ((threadIdx.x >> 5) == 11 ? 3 : ((threadIdx.x >> 5) <= 2 ? (threadIdx.x >> 5) : 4))
 __device__ long long g_cta_stats[1024][6];
 __device__ __forceinline__ unsigned long long wa_globaltimer() {
     unsigned long long t;
@@ -59,10 +61,10 @@ __device__ __forceinline__ unsigned wa_smid() {
 #define WA_STATS_ITEM(n) do { st_items += 1; st_tiles += (n); } while (0)
 #define WA_TRACE(id)                                                                         \
     do {                                                                                     \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) <= 2 &&         \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && WA_TRACE_ROLE <= 3 &&              \
             trace_at < TRACE_SLOTS) {                                                        \
-            g_trace[threadIdx.x >> 5][2 * trace_at] = (id);                                  \
-            g_trace[threadIdx.x >> 5][2 * trace_at + 1] = clock64();                         \
+            g_trace[WA_TRACE_ROLE][2 * trace_at] = (id);                                     \
+            g_trace[WA_TRACE_ROLE][2 * trace_at + 1] = clock64();                            \
             ++trace_at;                                                                      \
         }                                                                                    \
     } while (0)
@@ -76,8 +78,8 @@ __device__ __forceinline__ unsigned wa_smid() {
             g_cta_stats[blockIdx.x][4] = st_tiles;                                           \
             g_cta_stats[blockIdx.x][5] = clock64() - st_c0;                                  \
         }                                                                                    \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) <= 2)           \
-            g_trace_n[threadIdx.x >> 5] = trace_at;                                          \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && WA_TRACE_ROLE <= 3)                \
+            g_trace_n[WA_TRACE_ROLE] = trace_at;                                             \
     } while (0)
 #else
 #define WA_TRACE_DECL
@@ -118,13 +120,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for the whole warp: every lane has finished (and fenced) its part before lane 0 signals.
+__device__ __forceinline__ void warp_arrive(uint64_t *bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"   // %3: the thread may sleep this many ns
         "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
 // Bounded wait.  Returns false after the abort flag is raised or the time budget is spent.
@@ -271,39 +278,48 @@ __device__ __forceinline__ float row_max32(const uint32_t (&r)[32], int col0, in
 }
 
 // 32 scores -> 32 probabilities packed as 16 bf16 pairs; returns their float32 sum.
-// 2^x on the FMA pipe: split x into round(x) + f, f in [-0.5, 0.5], evaluate a cubic for 2^f and add round(x)
-// to the exponent field.  Relative error < 2^-10, below the bf16 rounding of P.  The special-function unit
-// (16 results per clock per SM) is the narrowest pipe of the softmax, so every third element takes this path.
-__device__ __forceinline__ float ex2_poly(float x) {
-    x = fmaxf(x, -125.0f);
-    const float t = x + 12582912.0f;            // 1.5 * 2^23: the integer part of x lands in the low mantissa bits
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(f, 0.0555041f, 0.2402265f);
-    p = fmaf(p, f, 0.6931472f);
-    p = fmaf(p, f, 1.0f);
-    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+// The arithmetic runs on pairs of columns with the packed float32x2 instructions of this architecture (one
+// issue slot for two results).  2^x on the FMA pipe: split x into round(x) + f, f in [-0.5, 0.5], evaluate a
+// cubic for 2^f and add round(x) to the exponent field; relative error < 2^-10, below the bf16 rounding of P.
+// The special-function unit (16 results per clock per SM) is the narrowest pipe of the softmax, so every
+// POLY_EVERY-th pair of columns takes the polynomial instead.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -125.0f);
+    x.y = fmaxf(x.y, -125.0f);
+    const float2 magic = make_float2(12582912.0f, 12582912.0f);   // 1.5 * 2^23: the integer part of x lands in the low mantissa bits
+    const float2 t = __fadd2_rn(x, magic);
+    const float2 f = __fadd2_rn(x, __fadd2_rn(magic, make_float2(-t.x, -t.y)));   // x - (t - magic)
+    float2 q = __ffma2_rn(f, make_float2(0.0555041f, 0.0555041f), make_float2(0.2402265f, 0.2402265f));
+    q = __ffma2_rn(q, f, make_float2(0.6931472f, 0.6931472f));
+    q = __ffma2_rn(q, f, make_float2(1.0f, 1.0f));
+    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
+                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
 }
-constexpr int POLY_EVERY = 3;
+#ifndef WA_POLY_EVERY
+#define WA_POLY_EVERY 4
+#endif
+constexpr int POLY_EVERY = WA_POLY_EVERY;
 
 template <bool MASKED, int OFF>
 __device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&pk)[32], float scale, float m, int col0,
                                             int valid) {
-    float s0 = 0.f, s1 = 0.f;
+    const float2 sc = make_float2(scale, scale), nm = make_float2(-m, -m);
+    float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < 32; j += 2) {
-        const float x0 = fmaf(__uint_as_float(r[j]), scale, -m), x1 = fmaf(__uint_as_float(r[j + 1]), scale, -m);
-        float p0 = (j % POLY_EVERY == 0) ? ex2_poly(x0) : ex2(x0);
-        float p1 = ((j + 1) % POLY_EVERY == 0) ? ex2_poly(x1) : ex2(x1);
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc, nm);
+        float2 pr;
+        if ((j >> 1) % POLY_EVERY == 0) pr = ex2_poly2(x);
+        else pr = make_float2(ex2(x.x), ex2(x.y));
         if (MASKED) {
-            if (col0 + j >= valid) p0 = 0.f;
-            if (col0 + j + 1 >= valid) p1 = 0.f;
+            if (col0 + j >= valid) pr.x = 0.f;
+            if (col0 + j + 1 >= valid) pr.y = 0.f;
         }
-        s0 += p0;
-        s1 += p1;
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+        acc = __fadd2_rn(acc, pr);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(pr.x, pr.y);
         pk[OFF + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
     }
-    return s0 + s1;
+    return acc.x + acc.y;
 }
 
 struct ItemDesc {
@@ -315,7 +331,11 @@ struct Barriers {
     uint64_t item_full[2], item_empty[2];
     uint64_t q_full[Q_STAGES], q_empty[Q_STAGES], out_ready[Q_STAGES];
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
-    uint64_t s_full[2], p_full[2], pv_done, o_done, o_free;
+    // K-type tile g (global count) lives in S buffer g % S_BUFS; it is that buffer's occupancy number g / S_BUFS, which
+    // is the phase of s_full / p_full the tile completes (every tile completes exactly one phase of each).
+    uint64_t s_full[S_BUFS], p_full[S_BUFS];
+    uint64_t s_free[S_BUFS];   // the PV product that read P from the buffer has landed
+    uint64_t o_done, o_free;   // v_empty[s] doubles as "PV product done" for the rescale path
     uint32_t tmem_base;
     int abort_flag;
     ItemDesc items[2];
@@ -348,14 +368,17 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (bar->abort_flag) atomicExch(p.error_flag, 99);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar->item_full[i], 1);
-            mbar_init(&bar->item_empty[i], 1 + 256 + 1);   // MMA leader + every softmax thread + store warp
+            mbar_init(&bar->item_empty[i], 2 + 8 + 1);   // both MMA leaders + every softmax warp + store warp
+        }
+        for (int i = 0; i < S_BUFS; ++i) {
             mbar_init(&bar->s_full[i], 1);
-            mbar_init(&bar->p_full[i], 256);
+            mbar_init(&bar->p_full[i], 8);   // one arrival per softmax warp
+            mbar_init(&bar->s_free[i], 1);
         }
         for (int i = 0; i < Q_STAGES; ++i) {
             mbar_init(&bar->q_full[i], 1);
             mbar_init(&bar->q_empty[i], 1);
-            mbar_init(&bar->out_ready[i], 256);
+            mbar_init(&bar->out_ready[i], 8);
         }
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(&bar->k_full[i], 1);
@@ -365,9 +388,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_init(&bar->v_full[i], 1);
             mbar_init(&bar->v_empty[i], 1);
         }
-        mbar_init(&bar->pv_done, 1);
         mbar_init(&bar->o_done, 1);
-        mbar_init(&bar->o_free, 256);
+        mbar_init(&bar->o_free, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (threadIdx.x >= 64 && threadIdx.x < 64 + TILE) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
@@ -380,7 +402,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bar->tmem_base;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * TILE;   // S buffer b at tmem_s + b * TILE
+    const uint32_t tmem_s = tmem, tmem_o = tmem + S_BUFS * TILE;   // S buffer b at tmem_s + b * TILE
     WA_TRACE_DECL;
     WA_TRACE(0);
     const int lin_tiles = (p.Lc + TILE - 1) / TILE;
@@ -463,24 +485,33 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        // ================= MMA issuer =================
-        // Issue order QK(0), QK(1), PV(0), QK(2), PV(1), ...: the score product of the next tile lands in the
-        // other S buffer while the softmax warps work on the current one; the sequence continues across
-        // work items.  The whole warp runs this role so that operands stay warp-uniform; one elected lane issues.
+        // ================= QK issuer =================
+        // Two warps issue tensor-core work: this one the score products Q.K^T (and the gate product), warp 11 the
+        // P.V products.  One thread blocks for about as long as its products execute, so a single issuer leaves the
+        // pipe idle during its own waits and commits; two issuers cover each other.  Score products run up to two
+        // tiles ahead of the softmax (three S buffers).  Products of different warps are ordered by completion
+        // barriers only.  The whole warp runs the role so that operands stay warp-uniform; one elected lane issues.
         const bool leader = elect_one();
-        constexpr uint32_t IDESC_QK = instr_desc(false, TILE), IDESC_PV = instr_desc(true, TILE);
-        uint32_t jcount = 0, kcount = 0, vcount = 0, ph_p = 0, ph_of = 1;   // ph_of = 1: the first wait passes
-        uint32_t gate_in_buf = 0;   // bit b: S buffer b holds gate scores the softmax warps have not read yet
+        constexpr uint32_t IDESC_QK = instr_desc(false, TILE);
+        uint32_t jcount = 0, kcount = 0;
+        uint32_t occ_pv = 0, occ_gate = 0;   // bit b: S buffer b last held a PV tile / a gate tile
+        uint32_t ph_sf = 0;                  // bit b: parity of the next s_free[b] phase to wait for
         bool ok = true;
 
         auto issue_qk = [&](uint64_t qd, bool is_gate) -> bool {
-            const uint32_t buf = kcount & 1u;
-            if (gate_in_buf & (1u << buf)) {
-                if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (ph_p >> buf) & 1u, abort_flag, p.error_flag, 13)))
+            const uint32_t buf = kcount % S_BUFS;
+            if (occ_gate & (1u << buf)) {
+                // the epilogue has read the gate scores of tile kcount - S_BUFS out of this buffer
+                if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], ((kcount - S_BUFS) / S_BUFS) & 1u, abort_flag, p.error_flag, 13)))
                     return false;
-                ph_p ^= 1u << buf;
-                gate_in_buf &= ~(1u << buf);
+            } else if (occ_pv & (1u << buf)) {
+                // the PV product that read P from this buffer has landed
+                if (!__all_sync(0xffffffffu, mbar_wait(&bar->s_free[buf], (ph_sf >> buf) & 1u, abort_flag, p.error_flag, 19)))
+                    return false;
+                ph_sf ^= 1u << buf;
             }
+            occ_gate &= ~(1u << buf);
+            occ_pv &= ~(1u << buf);
             const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
             if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
             ++kcount;
@@ -498,7 +529,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 tc_commit(&bar->s_full[buf]);
             }
             __syncwarp();
-            if (is_gate) gate_in_buf |= 1u << buf;
+            if (is_gate) occ_gate |= 1u << buf;
+            else occ_pv |= 1u << buf;
             WA_TRACE(4);
             return true;
         };
@@ -511,21 +543,34 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             __syncwarp();
             if (leader) mbar_arrive(&bar->item_empty[slot]);
             if (item < 0) break;
-            const int n_kv = n_sel + lin_tiles;
+            const int n_kv = n_sel + lin_tiles;   // K-type tiles 0 .. n_kv - 1 feed a PV product, tile n_kv is the gate
             const uint32_t qs = jcount % Q_STAGES;
             ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full[qs], (jcount / Q_STAGES) & 1u, abort_flag, p.error_flag, 3));
             if (!ok) break;
             const uint64_t qd = smem_desc(smem_u32(q_s + qs * TILE_BYTES), 16, 1024);
-            const uint32_t g0 = kcount;   // global number of this item's first tile
-            ok = issue_qk(qd, false);
-            for (int t = 0; t < n_kv && ok; ++t) {
-                ok = issue_qk(qd, t + 1 == n_kv);
-                if (!ok) break;
-                const uint32_t buf = (g0 + t) & 1u;
+            for (int t = 0; t <= n_kv && ok; ++t) ok = issue_qk(qd, t == n_kv);
+            ++jcount;
+        }
+    } else if (warp == 11) {
+        // ================= PV issuer =================
+        const bool leader = elect_one();
+        constexpr uint32_t IDESC_PV = instr_desc(true, TILE);
+        uint32_t jcount = 0, g = 0, vcount = 0, ph_of = 1;   // g: global K-type tile count; ph_of = 1: the first wait passes
+        bool ok = true;
+        while (ok) {
+            const uint32_t slot = jcount & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 20));
+            if (!ok) break;
+            const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
+            __syncwarp();
+            if (leader) mbar_arrive(&bar->item_empty[slot]);
+            if (item < 0) break;
+            const int n_kv = n_sel + lin_tiles;
+            for (int t = 0; t < n_kv && ok; ++t, ++g) {
+                const uint32_t buf = g % S_BUFS;
                 const bool first = (t == 0) || (t == n_sel);
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (ph_p >> buf) & 1u, abort_flag, p.error_flag, 5));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (g / S_BUFS) & 1u, abort_flag, p.error_flag, 5));
                 if (!ok) break;
-                ph_p ^= 1u << buf;
                 WA_TRACE(5);
                 const uint32_t vs = vcount % V_STAGES, vpar = (vcount / V_STAGES) & 1u;
                 ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, p.error_flag, 6));
@@ -544,13 +589,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     for (int kk = 0; kk < 8; ++kk)
                         mma_ts(tmem_o, tmem_s + buf * TILE + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
                                !(first && kk == 0));
-                    tc_commit(&bar->v_empty[vs]);
-                    tc_commit(&bar->pv_done);
+                    tc_commit(&bar->v_empty[vs]);   // frees the V stage; the rescale path reads it as "this product has landed"
+                    tc_commit(&bar->s_free[buf]);
                     if (t == n_sel - 1 || t == n_kv - 1) tc_commit(&bar->o_done);
                 }
                 __syncwarp();
                 WA_TRACE(7);
             }
+            ++g;   // the gate tile
             ++jcount;
         }
     } else if (warp == 10) {
@@ -590,9 +636,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int row = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
         const int pair_bar = 2 + (warp & 3);
-        const uint32_t tmem_park = tmem + 3 * TILE + lane_addr + half * 32;   // parked sparse result (bf16 pairs)
         uint32_t jcount = 0, sg = 0;       // items and K-type tiles seen so far
-        uint32_t ph_s = 0, ph_od = 0;
+        uint32_t ph_od = 0;
         uint32_t pv_count = 0;             // PV products requested so far
         bool ok = true;
 
@@ -601,7 +646,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 15));
             if (!ok) break;
             const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
-            mbar_arrive(&bar->item_empty[slot]);
+            warp_arrive(&bar->item_empty[slot]);
             if (item < 0) break;
             const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
             const int n_kv = n_sel + lin_tiles;
@@ -611,18 +656,18 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const bool row_ok = token < p.Lq;
             const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE + half * HALF;
             const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
-            const int gbuf = (sg + n_kv) & 1;
+            const int gbuf = (sg + n_kv) % S_BUFS;
             float inv_l_lin = 0.f;
+            uint32_t park[32];   // the sparse branch's result of this thread's 64 columns (bf16 pairs) until the combine
 
             for (int phase = 0; phase < 2 && ok; ++phase) {
                 const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_kv;
                 float m_used = -INFINITY, l = 0.f;
                 for (int t = t0; t < t1 && ok; ++t) {
-                    const int buf = (sg + t) & 1;
+                    const int buf = (sg + t) % S_BUFS;
                     const uint32_t s_addr = tmem_s + buf * TILE + lane_addr;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], (ph_s >> buf) & 1u, abort_flag, p.error_flag, 8));
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], ((sg + t) / S_BUFS) & 1u, abort_flag, p.error_flag, 8));
                     if (!ok) break;
-                    ph_s ^= 1u << buf;
                     WA_TRACE(2);
                     tc_fence_after();
                     // columns of this thread that hold real tokens (the producer wrote the tile's count)
@@ -644,19 +689,20 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (grow) m_new = mx;
                     if (__any_sync(0xffffffffu, grow && t > t0)) {
                         // every PV requested so far must have landed before the accumulator is touched
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->pv_done, (pv_count - 1u) & 1u, abort_flag, p.error_flag, 9));
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_empty[(pv_count - 1u) % V_STAGES],
+                                                               ((pv_count - 1u) / V_STAGES) & 1u, abort_flag, p.error_flag, 9));
                         if (!ok) break;
                         tc_fence_after();
                         const float f = (grow && t > t0) ? ex2(m_used - m_new) : 1.0f;
                         l *= f;
-                        uint32_t ro[32];
+                        uint32_t ro[16];
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, ro);
+                        for (int c = 0; c < 4; ++c) {   // 16 columns at a time: few live registers beside the tile's scores
+                            TMEM_LD16(tmem_o + lane_addr + half * HALF + c * 16, ro);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) ro[j] = __float_as_uint(__uint_as_float(ro[j]) * f);
-                            TMEM_ST32(tmem_o + lane_addr + half * HALF + c * 32, ro);
+                            for (int j = 0; j < 16; ++j) ro[j] = __float_as_uint(__uint_as_float(ro[j]) * f);
+                            TMEM_ST16(tmem_o + lane_addr + half * HALF + c * 16, ro);
                         }
                         tmem_wait_st();
                     }
@@ -671,11 +717,13 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         sum = exp_pack32<true, 0>(r0, pk, p.scale_log2, m_used, 0, valid);
                         sum += exp_pack32<true, 16>(r1, pk, p.scale_log2, m_used, 32, valid);
                     }
+                    WA_TRACE(20);
                     TMEM_ST32(s_addr + half * 32, pk);
                     l += sum;
                     tmem_wait_st();
+                    WA_TRACE(21);
                     tc_fence_before();
-                    mbar_arrive(&bar->p_full[buf]);
+                    warp_arrive(&bar->p_full[buf]);
                     WA_TRACE(3);
                     ++pv_count;
                 }
@@ -697,7 +745,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
                 if (phase == 0) {
                     // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park it
-                    // in 64 spare tensor-memory columns (two bf16 per column) until the final combine.
+                    // in registers (two bf16 per word) until the final combine.
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
@@ -718,21 +766,18 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                 }
                             }
                         } else {
-                            uint32_t pk16[16];
 #pragma unroll
                             for (int j = 0; j < 32; j += 2) {
                                 __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j]) * inv_l,
                                                                            __uint_as_float(r[j + 1]) * inv_l);
-                                pk16[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                                park[c * 16 + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
                             }
-                            TMEM_ST16(tmem_park + c * 16, pk16);
                         }
                     }
-                    if (!p.part_sparse) tmem_wait_st();
                     if (p.lse_sparse && row_ok && half == 0) p.lse_sparse[lse_off] = lse;
                     if (t1 > t0) {
                         tc_fence_before();
-                        mbar_arrive(&bar->o_free);
+                        warp_arrive(&bar->o_free);
                     }
                 } else {
                     inv_l_lin = inv_l;
@@ -742,9 +787,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             // ---- gate tile + combine ----
             if (ok) {
                 WA_TRACE(18);
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], (ph_s >> gbuf) & 1u, abort_flag, p.error_flag, 10));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], ((sg + n_kv) / S_BUFS) & 1u, abort_flag, p.error_flag, 10));
                 if (ok) {
-                    ph_s ^= 1u << gbuf;
                     tc_fence_after();
                     WA_TRACE(13);
 #pragma unroll
@@ -752,15 +796,13 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         uint32_t g[32], o[32];
                         TMEM_LD32(tmem_s + gbuf * TILE + lane_addr + half * HALF + c * 32, g);
                         TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, o);
-                        uint32_t sp_cur[16];   // parked sparse result of these 32 columns, two bf16 per word
-                        TMEM_LD16(tmem_park + c * 16, sp_cur);
                         tmem_wait_ld();
                         WA_TRACE(14);
                         if (c == 1) {
                             // gate scores and the linear accumulator are in registers: release both to the MMA warp
                             tc_fence_before();
-                            mbar_arrive(&bar->p_full[gbuf]);
-                            mbar_arrive(&bar->o_free);
+                            warp_arrive(&bar->p_full[gbuf]);
+                            warp_arrive(&bar->o_free);
                         }
                         if (p.part_linear) {
                             if (row_ok) {
@@ -779,7 +821,6 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             const int cc = half * 8 + c * 4 + (j >> 3);
                             uint4 *slot = reinterpret_cast<uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 +
                                                                     (((cc & 7) ^ (row & 7)) << 4));
-                            const __nv_bfloat162 *sp2 = reinterpret_cast<const __nv_bfloat162 *>(&sp_cur[j >> 1]);
                             uint4 qv = make_uint4(0, 0, 0, 0);
                             if (!p.has_gate) qv = *slot;   // the gate-less path needs q itself: read it before overwriting
                             const __nv_bfloat162 *q2 = reinterpret_cast<const __nv_bfloat162 *>(&qv);
@@ -799,9 +840,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                 }
                                 const float g0 = fmaf(tanh_approx(0.5f * z0), 0.5f, 0.5f);   // sigmoid, one special-function op
                                 const float g1 = fmaf(tanh_approx(0.5f * z1), 0.5f, 0.5f);
-                                const float2 s2 = __bfloat1622float2(sp2[e]);
-                                const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, g0, s2.x);
-                                const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, g1, s2.y);
+                                const uint32_t sp = park[c * 16 + (j >> 1) + e];   // two bf16: low half = even column
+                                const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, g0, __uint_as_float(sp << 16));
+                                const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, g1, __uint_as_float(sp & 0xffff0000u));
                                 __nv_bfloat162 h2 = __floats2bfloat162_rn(r0, r1);
                                 w[e] = *reinterpret_cast<uint32_t *>(&h2);
                             }
@@ -814,7 +855,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             // Hand the staged tile to the store warp (in partial-output mode nothing was staged, but the Q stage
             // is released the same way).
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&bar->out_ready[qs]);
+            warp_arrive(&bar->out_ready[qs]);
             WA_TRACE(10);
             sg += n_kv + 1;
             ++jcount;
@@ -930,10 +971,10 @@ extern "C" int wa_stats_read(long long *dst, int n_ctas) {
 }
 extern "C" int wa_trace_read(long long *dst, int max_words) {
     // concatenates the three roles' (id, clock) pairs; returns the number of 64-bit words written
-    int n[3] = {0, 0, 0}, out = 0;
+    int n[4] = {0, 0, 0, 0}, out = 0;
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(n, sm100::g_trace_n, sizeof(n));
-    for (int r = 0; r < 3; ++r) {
+    for (int r = 0; r < 4; ++r) {
         const int words = 2 * n[r];
         if (out + words > max_words) break;
         cudaMemcpyFromSymbol(dst + out, sm100::g_trace, (size_t)words * sizeof(long long),
