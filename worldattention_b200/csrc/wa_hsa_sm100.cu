@@ -28,7 +28,9 @@ namespace sm100 {
 
 constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
 constexpr int HALF = 64;             // key tokens per softmax / MMA pipeline step
-constexpr int THREADS = 384;         // warp 0 TMA, warp 1 QK products, warps 2..9 softmax (two threads per query row), warp 10 output store, warp 11 PV products
+constexpr int THREADS = 384;         // warps 0..7 softmax (two threads per query row), warp 8 TMA, warp 9 QK products, warp 10 output store, warp 11 PV products
+constexpr int REGS_SOFTMAX = 224;    // register budget per thread after the roles split (two warpgroups of softmax warps)
+constexpr int REGS_OTHER = 56;       // ... and of the warpgroup that holds the four single-purpose warps; 256*224 + 128*56 = 384*168
 constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
 constexpr int TMEM_COLS = 512;       // three S buffers: columns [0,128), [128,256), [256,384); O: [384,512)
@@ -45,7 +47,7 @@ constexpr long long WAIT_CYCLES = 4000000000ll;
 constexpr int TRACE_SLOTS = 8192;            // (id, clock) pairs per traced role
 __device__ long long g_trace[4][2 * TRACE_SLOTS];
 __device__ int g_trace_n[4];
-#define WA_TRACE_ROLE ((threadIdx.x >> 5) == 11 ? 3 : ((threadIdx.x >> 5) <= 2 ? (threadIdx.x >> 5) : 4))
+#define WA_TRACE_ROLE ((threadIdx.x >> 5) == 0 ? 2 : (threadIdx.x >> 5) == 8 ? 0 : (threadIdx.x >> 5) == 9 ? 1 : (threadIdx.x >> 5) == 11 ? 3 : 4)
 __device__ long long g_cta_stats[1024][6];
 __device__ __forceinline__ unsigned long long wa_globaltimer() {
     unsigned long long t;
@@ -393,7 +395,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (threadIdx.x >= 64 && threadIdx.x < 64 + TILE) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
-    if (warp == 0) {
+    if (warp == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
                      "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -407,7 +409,11 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     WA_TRACE(0);
     const int lin_tiles = (p.Lc + TILE - 1) / TILE;
 
-    if (warp == 0) {
+    // The softmax threads keep 64 scores, the packed probabilities and the parked sparse result in registers; the
+    // other four warps need few.  Shift the register file accordingly (whole warpgroups, as the instruction requires).
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHER));
+    if (warp == 8) {
         // ================= producer: work queue + TMA =================
         if (lane == 0) {
             uint32_t jcount = 0, kcount = 0, vcount = 0;
@@ -484,7 +490,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 ++jcount;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 9) {
         // ================= QK issuer =================
         // Two warps issue tensor-core work: this one the score products Q.K^T (and the gate product), warp 11 the
         // P.V products.  One thread blocks for about as long as its products execute, so a single issuer leaves the
@@ -627,12 +633,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores have landed before the CTA exits
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
         // ================= softmax / epilogue: two threads per query row (64 score columns each) ==========
-        // Warps 2..5 own columns [0,64), warps 6..9 columns [64,128) of the same rows (a warp may only touch
+        // Warps 0..3 own columns [0,64), warps 4..7 columns [64,128) of the same rows (a warp may only touch
         // the 32 tensor-memory lanes selected by warp % 4).  The two threads of a row meet at a 64-thread
         // named barrier once per tile to agree on the row maximum.
-        const int half = (warp - 2) >> 2;
+        const int half = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
         const int pair_bar = 2 + (warp & 3);
@@ -657,7 +665,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE + half * HALF;
             const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
             const int gbuf = (sg + n_kv) % S_BUFS;
-            float inv_l_lin = 0.f;
+            float inv_l_lin = 0.f, inv_l_sp = 0.f;
             uint32_t park[32];   // the sparse branch's result of this thread's 64 columns (bf16 pairs) until the combine
 
             for (int phase = 0; phase < 2 && ok; ++phase) {
@@ -726,58 +734,67 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     warp_arrive(&bar->p_full[buf]);
                     WA_TRACE(3);
                     ++pv_count;
+                    if (phase == 1 && t == t0 && n_sel > 0) {
+                        // The sparse branch's accumulator: its last PV product had this whole tile to land.  Normalise,
+                        // round to bf16 (the reference stores this branch in bf16) and park it in registers (two bf16
+                        // per word) until the combine; then the linear branch's first PV product may overwrite it.
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
+                        if (!ok) break;
+                        ph_od ^= 1u;
+                        tc_fence_after();
+                        WA_TRACE(12);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {   // 16 columns at a time
+                            uint32_t ro[16];
+                            TMEM_LD16(tmem_o + lane_addr + half * HALF + c * 16, ro);
+                            tmem_wait_ld();
+                            if (p.part_sparse) {
+                                if (row_ok) {
+#pragma unroll
+                                    for (int j = 0; j < 16; j += 4) {
+                                        float4 o4 = make_float4(__uint_as_float(ro[j]) * inv_l_sp, __uint_as_float(ro[j + 1]) * inv_l_sp,
+                                                                __uint_as_float(ro[j + 2]) * inv_l_sp, __uint_as_float(ro[j + 3]) * inv_l_sp);
+                                        *reinterpret_cast<float4 *>(p.part_sparse + part_off + c * 16 + j) = o4;
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; j += 2) {
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(ro[j]) * inv_l_sp,
+                                                                               __uint_as_float(ro[j + 1]) * inv_l_sp);
+                                    park[c * 8 + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
+                                }
+                            }
+                        }
+                        tc_fence_before();
+                        warp_arrive(&bar->o_free);
+                    }
                 }
                 if (!ok) break;
-                // ---- end of a branch: total row sum, then read the accumulator ----
+                // ---- end of a branch: total row sum.  The accumulator itself is read out later, when the PV products
+                // have surely landed: the sparse one after the first tile of the linear branch (above), the linear one
+                // in the combine after the gate values have been computed. ----
                 // (the exchange buffer of parity t1 was last read two tiles ago, so it is free here)
                 bar->xch[t1 & 1][half][row] = l;
                 asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
                 l += bar->xch[t1 & 1][half ^ 1][row];
                 asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // the next branch's first tile reuses this buffer
-                if (t1 > t0) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
-                    if (!ok) break;
-                    ph_od ^= 1u;
-                    tc_fence_after();
-                    WA_TRACE(12);
-                }
                 const float inv_l = l > 0.f ? 1.0f / l : 0.f;
                 const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
                 if (phase == 0) {
-                    // sparse branch: normalise, round to bf16 (the reference stores this branch in bf16) and park it
-                    // in registers (two bf16 per word) until the final combine.
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t r[32];
-                        if (t1 > t0) {
-                            TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, r);
-                            tmem_wait_ld();
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) r[j] = 0u;
-                        }
+                    inv_l_sp = inv_l;
+                    if (p.lse_sparse && row_ok && half == 0) p.lse_sparse[lse_off] = lse;
+                    if (n_sel == 0) {   // no selected block: the sparse term is zero and there is no accumulator to wait for
                         if (p.part_sparse) {
                             if (row_ok) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 4) {
-                                    float4 o4 = make_float4(__uint_as_float(r[j]) * inv_l, __uint_as_float(r[j + 1]) * inv_l,
-                                                            __uint_as_float(r[j + 2]) * inv_l, __uint_as_float(r[j + 3]) * inv_l);
-                                    *reinterpret_cast<float4 *>(p.part_sparse + part_off + c * 32 + j) = o4;
-                                }
+                                for (int j = 0; j < HALF; j += 4)
+                                    *reinterpret_cast<float4 *>(p.part_sparse + part_off + j) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 2) {
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j]) * inv_l,
-                                                                           __uint_as_float(r[j + 1]) * inv_l);
-                                park[c * 16 + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
-                            }
+                            for (int j = 0; j < 32; ++j) park[j] = 0u;
                         }
-                    }
-                    if (p.lse_sparse && row_ok && half == 0) p.lse_sparse[lse_off] = lse;
-                    if (t1 > t0) {
-                        tc_fence_before();
-                        warp_arrive(&bar->o_free);
                     }
                 } else {
                     inv_l_lin = inv_l;
@@ -785,71 +802,104 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
             }
             // ---- gate tile + combine ----
+            // gate values of this thread's 64 columns, rounded to bf16 (two per word) as the reference's gate is;
+            // computed while the last PV product of the linear branch is still in flight
+            uint32_t gpk[32];
             if (ok) {
                 WA_TRACE(18);
                 ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], ((sg + n_kv) / S_BUFS) & 1u, abort_flag, p.error_flag, 10));
-                if (ok) {
-                    tc_fence_after();
-                    WA_TRACE(13);
+            }
+            if (ok) {
+                tc_fence_after();
+                WA_TRACE(13);
+                if (!p.part_linear) {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t g[32], o[32];
-                        TMEM_LD32(tmem_s + gbuf * TILE + lane_addr + half * HALF + c * 32, g);
-                        TMEM_LD32(tmem_o + lane_addr + half * HALF + c * 32, o);
-                        tmem_wait_ld();
-                        WA_TRACE(14);
-                        if (c == 1) {
-                            // gate scores and the linear accumulator are in registers: release both to the MMA warp
-                            tc_fence_before();
-                            warp_arrive(&bar->p_full[gbuf]);
-                            warp_arrive(&bar->o_free);
-                        }
-                        if (p.part_linear) {
-                            if (row_ok) {
+                    for (int c = 0; c < 4; ++c) {   // 16 columns at a time
+                        if (p.has_gate) {
+                            uint32_t g[16];
+                            TMEM_LD16(tmem_s + gbuf * TILE + lane_addr + half * HALF + c * 16, g);
+                            tmem_wait_ld();
 #pragma unroll
-                                for (int j = 0; j < 32; j += 4) {
-                                    float4 o4 = make_float4(__uint_as_float(o[j]) * inv_l_lin, __uint_as_float(o[j + 1]) * inv_l_lin,
-                                                            __uint_as_float(o[j + 2]) * inv_l_lin, __uint_as_float(o[j + 3]) * inv_l_lin);
-                                    *reinterpret_cast<float4 *>(p.part_linear + part_off + c * 32 + j) = o4;
-                                }
-                            }
-                            continue;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            // 16-byte chunk `cc` of this row inside the swizzled 128 x 128 bf16 tile that held Q
-                            const int cc = half * 8 + c * 4 + (j >> 3);
-                            uint4 *slot = reinterpret_cast<uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 +
-                                                                    (((cc & 7) ^ (row & 7)) << 4));
-                            uint4 qv = make_uint4(0, 0, 0, 0);
-                            if (!p.has_gate) qv = *slot;   // the gate-less path needs q itself: read it before overwriting
-                            const __nv_bfloat162 *q2 = reinterpret_cast<const __nv_bfloat162 *>(&qv);
-                            uint4 o4;
-                            uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int col = half * HALF + c * 32 + j + 2 * e;
-                                float z0, z1;
-                                if (p.has_gate) {
-                                    z0 = __uint_as_float(g[j + 2 * e]) + bar->bias[col];
-                                    z1 = __uint_as_float(g[j + 2 * e + 1]) + bar->bias[col + 1];
-                                } else {
-                                    const float2 qf = __bfloat1622float2(q2[e]);
-                                    z0 = qf.x;
-                                    z1 = qf.y;
-                                }
+                            for (int j = 0; j < 16; j += 2) {
+                                const int col = half * HALF + c * 16 + j;
+                                const float z0 = __uint_as_float(g[j]) + bar->bias[col], z1 = __uint_as_float(g[j + 1]) + bar->bias[col + 1];
                                 const float g0 = fmaf(tanh_approx(0.5f * z0), 0.5f, 0.5f);   // sigmoid, one special-function op
                                 const float g1 = fmaf(tanh_approx(0.5f * z1), 0.5f, 0.5f);
-                                const uint32_t sp = park[c * 16 + (j >> 1) + e];   // two bf16: low half = even column
-                                const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, g0, __uint_as_float(sp << 16));
-                                const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, g1, __uint_as_float(sp & 0xffff0000u));
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(r0, r1);
-                                w[e] = *reinterpret_cast<uint32_t *>(&h2);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
+                                gpk[c * 8 + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
                             }
-                            *slot = o4;
+                        } else {
+                            // no gate module: gate = sigmoid(q); q sits in the swizzled tile that the output overwrites below
+#pragma unroll
+                            for (int j = 0; j < 16; j += 8) {
+                                const int cc = half * 8 + c * 2 + (j >> 3);
+                                const uint4 qv = *reinterpret_cast<const uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 +
+                                                                                  (((cc & 7) ^ (row & 7)) << 4));
+                                const uint32_t *qw = reinterpret_cast<const uint32_t *>(&qv);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float g0 = fmaf(tanh_approx(0.5f * __uint_as_float(qw[e] << 16)), 0.5f, 0.5f);
+                                    const float g1 = fmaf(tanh_approx(0.5f * __uint_as_float(qw[e] & 0xffff0000u)), 0.5f, 0.5f);
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
+                                    gpk[c * 8 + (j >> 1) + e] = *reinterpret_cast<uint32_t *>(&h2);
+                                }
+                            }
                         }
-                        WA_TRACE(15);
                     }
+                }
+                // the gate scores are consumed: their S buffer goes back to the QK warp
+                tc_fence_before();
+                warp_arrive(&bar->p_full[gbuf]);
+                if (lin_tiles > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
+                    ph_od ^= 1u;
+                    tc_fence_after();
+                    WA_TRACE(12);
+                }
+            }
+            if (ok) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {   // 16 columns at a time
+                    uint32_t o[16];
+                    TMEM_LD16(tmem_o + lane_addr + half * HALF + c * 16, o);
+                    tmem_wait_ld();
+                    WA_TRACE(14);
+                    if (c == 3) {
+                        // the linear accumulator is in registers: the next item's PV products may overwrite it
+                        tc_fence_before();
+                        warp_arrive(&bar->o_free);
+                    }
+                    if (p.part_linear) {
+                        if (row_ok) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4) {
+                                float4 o4 = make_float4(__uint_as_float(o[j]) * inv_l_lin, __uint_as_float(o[j + 1]) * inv_l_lin,
+                                                        __uint_as_float(o[j + 2]) * inv_l_lin, __uint_as_float(o[j + 3]) * inv_l_lin);
+                                *reinterpret_cast<float4 *>(p.part_linear + part_off + c * 16 + j) = o4;
+                            }
+                        }
+                        continue;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j += 8) {
+                        // 16-byte chunk `cc` of this row inside the swizzled 128 x 128 bf16 tile that held Q
+                        const int cc = half * 8 + c * 2 + (j >> 3);
+                        uint4 o4;
+                        uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t sp = park[c * 8 + (j >> 1) + e];   // two bf16: low half = even column
+                            const uint32_t gg = gpk[c * 8 + (j >> 1) + e];
+                            const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, __uint_as_float(gg << 16),
+                                                  __uint_as_float(sp << 16));
+                            const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, __uint_as_float(gg & 0xffff0000u),
+                                                  __uint_as_float(sp & 0xffff0000u));
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(r0, r1);
+                            w[e] = *reinterpret_cast<uint32_t *>(&h2);
+                        }
+                        *reinterpret_cast<uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = o4;
+                    }
+                    WA_TRACE(15);
                 }
             }
             // Hand the staged tile to the store warp (in partial-output mode nothing was staged, but the Q stage
@@ -867,7 +917,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     WA_TRACE_FLUSH;
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) {
+    if (warp == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
