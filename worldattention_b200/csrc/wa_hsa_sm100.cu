@@ -418,11 +418,13 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (lane == 0) {
             uint32_t jcount = 0, kcount = 0, vcount = 0;
             bool ok = true;
+            // Work queue: the first item of a CTA is fixed by its index (no round trip to the counter before the first
+            // load); later items come from the counter, which is asked for the next position one item ahead.
+            int at = blockIdx.x;
             while (ok) {
                 const uint32_t slot = jcount & 1u;
                 ok = mbar_wait(&bar->item_empty[slot], ((jcount >> 1) & 1u) ^ 1u, abort_flag, p.error_flag, 11);
                 if (!ok) break;
-                const int at = atomicAdd(p.work_counter, 1);
                 int item = -1, n_sel = 0;
                 if (at < p.n_items) {
                     item = p.order[at];
@@ -432,6 +434,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 bar->items[slot].n_sel = n_sel;
                 mbar_arrive(&bar->item_full[slot]);
                 if (item < 0) break;
+                at = (int)gridDim.x + atomicAdd(p.work_counter, 1);   // consumed at the top of the next round
                 const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
                 const int32_t *ids = p.index + (long long)item * p.Nkv;
                 const int n_kv = n_sel + lin_tiles;
@@ -722,8 +725,18 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         sum = exp_pack32<false, 0>(r0, pk, p.scale_log2, m_used, 0, 0);
                         sum += exp_pack32<false, 16>(r1, pk, p.scale_log2, m_used, 0, 0);
                     } else {
-                        sum = exp_pack32<true, 0>(r0, pk, p.scale_log2, m_used, 0, valid);
-                        sum += exp_pack32<true, 16>(r1, pk, p.scale_log2, m_used, 32, valid);
+                        // ragged tile (the last one of a branch): 32-column chunks without a real token cost nothing
+                        sum = 0.f;
+                        if (valid > 0) sum = exp_pack32<true, 0>(r0, pk, p.scale_log2, m_used, 0, valid);
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) pk[j] = 0u;
+                        }
+                        if (valid > 32) sum += exp_pack32<true, 16>(r1, pk, p.scale_log2, m_used, 32, valid);
+                        else {
+#pragma unroll
+                            for (int j = 16; j < 32; ++j) pk[j] = 0u;
+                        }
                     }
                     WA_TRACE(20);
                     TMEM_ST32(s_addr + half * 32, pk);
