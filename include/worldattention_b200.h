@@ -104,6 +104,14 @@ int wa_route_select_static(const float *block_attn, int B, int H, int Nq, int Nk
 int wa_map_to_index(const uint8_t *mask, int B, int H, int Nq, int Nkv, int32_t *index,
                     int32_t *num, void *stream);
 
+/* Restriction of a routing decision to the key blocks [block_lo, block_hi) that one KV shard owns (no reference
+ * counterpart: the reference is single-device).  Per row: the selected ids (first num entries of index, clamped to
+ * [0, Nkv)) that fall in the range, rebased to the shard, duplicates collapsed, ascending; then the shard's other
+ * blocks, ascending, so that every row of local_index [rows, block_hi - block_lo] is a permutation.
+ * local_num [rows] = number of selected blocks of the shard.  At most 16384 blocks per shard. */
+int wa_route_local_selection(const int32_t *index, const int32_t *num, long long rows, int Nkv, int block_lo,
+                             int block_hi, int32_t *local_index, int32_t *local_num, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Attention branches -- wan/modules/hsa/block_sparse_torch.py, block_sparse_triton.py,
  * attention.py

@@ -167,3 +167,27 @@ def test_partial_output_mode_merges_to_the_full_result(wa):
     got = branches.gate_combine(q, back(sp).to(torch.bfloat16), back(li), hsa.gate_lin, round_bf16=True)
     max_abs, mean_rel = attention_error(to_np(got), to_np(want))
     assert max_abs < MAX_ABS and mean_rel < MEAN_REL, (max_abs, mean_rel)
+
+
+def test_head_slices_of_a_resident_cache_equal_the_full_call(wa):
+    """Heads are independent: the layer on a strided head slice of q/k/v/compressed cache gives that slice of the
+    full result bit for bit (what the pipelined end-to-end step and the head-split sharding rely on)."""
+    heads, q_len, kv_len, seg = 6, 700, 3120, 1560
+    rng = np.random.default_rng(11)
+    q, k, v = (to_gpu(_draw(rng, (1, n, heads, D), s), "bf16") for n, s in ((q_len, 0.3), (kv_len, 0.3), (kv_len, 1.0)))
+    hsa = wa.hsa.HSAAttention(heads, D, block_size=128, proj_segment_len=seg).to(dev())
+    wa.hsa_stage.init_hsa_parameters(hsa)
+    with torch.no_grad():
+        hsa.gate_lin.weight.normal_(0, 0.05)
+        kc, vc = hsa.compress_kv_cache(k, v)
+    topk = torch.tensor([3, 9, 1, 25, 4, 16], dtype=torch.int32, device=dev())
+    common = dict(k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=128,
+                  proj_segment_len=seg, return_routing=True)
+    full, (_, num, _, used) = wa.hsa.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, topk_per_head=topk, **common)
+    assert used
+    for hs in (slice(0, 2), slice(2, 6)):
+        part, (_, num_p, _, used_p) = wa.hsa.hsa_attention(q[:, :, hs], k[:, :, hs], v[:, :, hs], k_coarse=kc[:, :, hs],
+                                                           v_coarse=vc[:, :, hs], topk_per_head=topk[hs], **common)
+        assert used_p and not q[:, :, hs].is_contiguous()
+        assert torch.equal(num_p, num[:, hs])
+        assert torch.equal(part, full[:, :, hs])

@@ -61,6 +61,7 @@ SIGNATURES = {
     "wa_route_select": [_vp, _i, _i, _i, _i, _d, _d, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "wa_route_select_static": [_vp, _i, _i, _i, _i, _d, _d, _vp, _vp, _vp, _vp, _vp, _vp],
     "wa_map_to_index": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "wa_route_local_selection": [_vp, _vp, C.c_longlong, _i, _i, _i, _vp, _vp, _vp],
     "wa_block_sparse_forward": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i,
                                 _vp, _vp],
     "wa_compress_kv": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp],

@@ -621,9 +621,63 @@ __global__ void map_to_index_kernel(const uint8_t *__restrict__ mask, long long 
     if (lane == 0) num[row] = n;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Selection of one KV shard.  One warp per row: a bitmap of the shard's blocks in shared memory,
+// then two ballot-ordered compactions (selected blocks, then the rest).
+// ------------------------------------------------------------------------------------------------
+constexpr int LOCAL_SEL_WARPS = 8;
+
+__global__ void __launch_bounds__(LOCAL_SEL_WARPS * 32)
+local_selection_kernel(const int32_t *__restrict__ index, const int32_t *__restrict__ num, long long rows, int Nkv,
+                       int block_lo, int width, int words, int32_t *__restrict__ local_index,
+                       int32_t *__restrict__ local_num) {
+    extern __shared__ unsigned int sel_bitmap[];   // [warps][words]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * LOCAL_SEL_WARPS + warp;
+    if (row >= rows) return;
+    unsigned int *bm = sel_bitmap + warp * words;
+    for (int w = lane; w < words; w += 32) bm[w] = 0u;
+    __syncwarp();
+    const int32_t *idx = index + row * Nkv;
+    const int n = max(0, min(num[row], Nkv));
+    for (int j = lane; j < n; j += 32) {
+        const int id = max(0, min(idx[j], Nkv - 1)) - block_lo;
+        if (id >= 0 && id < width) atomicOr(&bm[id >> 5], 1u << (id & 31));
+    }
+    __syncwarp();
+    int32_t *out = local_index + row * width;
+    int at = 0;
+    for (int pass = 0; pass < 2; ++pass) {   // members first, then the rest
+        for (int base = 0; base < width; base += 32) {
+            const int c = base + lane;
+            const bool member = c < width && ((bm[base >> 5] >> lane) & 1u);
+            const bool take = c < width && (pass == 0 ? member : !member);
+            const unsigned bal = __ballot_sync(0xffffffffu, take);
+            if (take) out[at + __popc(bal & ((1u << lane) - 1u))] = c;
+            at += __popc(bal);
+        }
+        if (pass == 0 && lane == 0) local_num[row] = at;
+    }
+}
+
 }  // namespace wa
 
 using namespace wa;
+
+extern "C" int wa_route_local_selection(const int32_t *index, const int32_t *num, long long rows, int Nkv, int block_lo,
+                                        int block_hi, int32_t *local_index, int32_t *local_num, void *stream) {
+    WA_REQUIRE(index && num && local_index && local_num, WA_ERR_ARG, "wa_route_local_selection: null pointer");
+    WA_REQUIRE(rows > 0 && Nkv > 0 && block_lo >= 0 && block_hi > block_lo, WA_ERR_ARG,
+               "wa_route_local_selection: need rows > 0, Nkv > 0 and a non-empty block range");
+    const int width = block_hi - block_lo;
+    WA_REQUIRE(width <= 16384, WA_ERR_UNSUPPORTED, "wa_route_local_selection: at most 16384 blocks per shard, got %d", width);
+    const int words = (width + 31) / 32;
+    const long long ctas = (rows + LOCAL_SEL_WARPS - 1) / LOCAL_SEL_WARPS;
+    WA_REQUIRE(ctas < (1ll << 31), WA_ERR_UNSUPPORTED, "wa_route_local_selection: too many rows");
+    local_selection_kernel<<<(unsigned)ctas, LOCAL_SEL_WARPS * 32, (size_t)LOCAL_SEL_WARPS * words * sizeof(unsigned int),
+                             (cudaStream_t)stream>>>(index, num, rows, Nkv, block_lo, width, words, local_index, local_num);
+    return check_launch("wa_route_local_selection");
+}
 
 namespace wa {
 static bool pool_vec_ok(const wa_tensor4 *x, int D) {

@@ -86,6 +86,17 @@ def local_selection(index: torch.Tensor, num: torch.Tensor, block_lo: int, block
     global selection.
     """
     nkv = index.shape[-1]
+    if index.is_cuda:   # one launch instead of a dozen tensor operations
+        from . import _lib
+        width = max(block_hi - block_lo, 1)
+        index_c, num_c = index.to(torch.int32).contiguous(), num.to(torch.int32).contiguous()
+        rows = num_c.numel()
+        local_index = torch.empty(index.shape[:-1] + (width,), dtype=torch.int32, device=index.device)
+        local_num = torch.empty(num.shape, dtype=torch.int32, device=index.device)
+        _lib.check(_lib.lib().wa_route_local_selection(index_c.data_ptr(), num_c.data_ptr(), rows, nkv, block_lo,
+                                                       block_lo + width, local_index.data_ptr(), local_num.data_ptr(),
+                                                       _lib.stream_ptr(index.device)))
+        return local_index, local_num
     slots = torch.arange(nkv, device=index.device).view(*([1] * (index.dim() - 1)), nkv)
     selected = slots < num.unsqueeze(-1).long()
     ids = index.long().clamp(0, nkv - 1)
@@ -188,7 +199,10 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
             o_l = torch.zeros_like(o_s)
             l_l = torch.full_like(l_s, float("-inf"))
 
-    # exchange + merge (rows ordered [B, H, Lq] to match the normalisers)
+    if world > 1 and bsz == 1:
+        return _merge_by_query_rows(hsa_module, q, o_s, l_s, o_l, l_l, rank, world, group)
+
+    # single rank or batched input: merge everything everywhere (rows ordered [B, H, Lq] to match the normalisers)
     def rows(o):
         return o.permute(0, 2, 1, 3).reshape(1, bsz * heads * q_len, head_dim)
 
@@ -204,6 +218,43 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     sparse = sparse.to(torch.bfloat16).contiguous()       # the reference stores the sparse branch in bf16
     return branches.gate_combine(q, sparse, linear.contiguous(), hsa_module.gate_lin,
                                  round_bf16=q.dtype == torch.bfloat16)
+
+
+def _merge_by_query_rows(hsa_module, q, o_s, l_s, o_l, l_l, rank: int, world: int, group):
+    """Exchange of the shard partials by query rows (B = 1).
+
+    Rank j receives rows `[j*rp, (j+1)*rp)` of every rank's partial outputs and normalisers (an all-to-all: each
+    rank sends and receives (world-1)/world of one partial set instead of gathering all of them), merges and
+    gate-combines its rows, and the finished bf16 rows are all-gathered.  `o_*`: float32 `[1, Lq, H, D]`,
+    `l_*`: float32 `[1, H, Lq]`.
+    """
+    _, q_len, heads, head_dim = q.shape
+    rp = -(-q_len // world)
+    pad = rp * world - q_len
+
+    def exchange(x):   # [Lq, ...] -> [world, rp, ...]: slice j of every rank
+        if pad:
+            x = torch.cat([x, x.new_zeros((pad,) + tuple(x.shape[1:]))])
+        x = x.contiguous()
+        recv = torch.empty_like(x)
+        dist.all_to_all_single(recv, x, group=group)
+        return recv.view(world, rp, *x.shape[1:])
+
+    os_, ol_ = exchange(o_s[0]), exchange(o_l[0])                  # [W, rp, H, D]
+    ls_, ll_ = exchange(l_s[0].t()), exchange(l_l[0].t())          # [W, rp, H]
+    sp, _ = merge_partials(os_.view(world, rp * heads, head_dim), ls_.reshape(world, rp * heads))
+    li, _ = merge_partials(ol_.view(world, rp * heads, head_dim), ll_.reshape(world, rp * heads))
+    lo = rank * rp
+    n = max(0, min(q_len, lo + rp) - lo)
+    out_rows = q.new_zeros((1, rp, heads, head_dim))
+    if n > 0:
+        sparse = sp.view(1, rp, heads, head_dim)[:, :n].to(torch.bfloat16).contiguous()   # the reference stores this branch in bf16
+        linear = li.view(1, rp, heads, head_dim)[:, :n].contiguous()
+        out_rows[:, :n] = branches.gate_combine(q[:, lo:lo + n], sparse, linear, hsa_module.gate_lin,
+                                                round_bf16=q.dtype == torch.bfloat16)
+    full = q.new_empty((world * rp, heads, head_dim))
+    dist.all_gather_into_tensor(full, out_rows[0].contiguous(), group=group)
+    return full[:q_len].unsqueeze(0)
 
 
 def _pool_blhd(x: torch.Tensor, block_size: int) -> torch.Tensor:
