@@ -479,22 +479,26 @@ def main():
 
     # One GPU: the heads are independent, so the step is pipelined over head groups on separate streams -- group g+1's
     # rows cross PCIe while group g computes and group g-1's output returns (the copies are most of the step).
-    E2E_GROUPS = 3 if (mode == "single" and HEADS % 3 == 0) else 1
+    E2E_GROUPS = int(os.environ.get("WA_E2E_GROUPS", "3")) if mode == "single" else 1
     e2e_note = "one stream: copy in, append + compress, layer, copy out"
     if E2E_GROUPS > 1:
         hg = HEADS // E2E_GROUPS
-        e2e_note = (f"{E2E_GROUPS} head groups of {hg} heads, one stream each: copy in, append + compress, layer "
-                    f"(`hsa_attention` on the group's heads), copy out; groups overlap")
+        e2e_note = (f"{E2E_GROUPS} head groups of {hg} heads, each with its own resident cache tensors and stream: copy in, "
+                    f"append + compress, layer (`hsa_attention` on the group's heads), copy out; groups overlap")
         streams = [torch.cuda.Stream(device=dev) for _ in range(E2E_GROUPS)]
         done = [torch.cuda.Event() for _ in range(E2E_GROUPS)]
+        arrived = [torch.cuda.Event() for _ in range(E2E_GROUPS)]
         grp = []
         for g in range(E2E_GROUPS):
             hs = slice(g * hg, (g + 1) * hg)
+            # the group's resident state lives in tensors of its own ([B, L, H/G, D], heads of the group only), so the
+            # rows that arrive land with plain contiguous copies
             grp.append(dict(
-                hs=hs,
                 q_h=q_new_h[:, :, hs].contiguous().pin_memory(), k_h=k_new_h[:, :, hs].contiguous().pin_memory(),
                 v_h=v_new_h[:, :, hs].contiguous().pin_memory(),
                 out_h=torch.empty((1, q_len, hg, HEAD_DIM), dtype=torch.bfloat16, pin_memory=True),
+                q=q[:, :, hs].contiguous(), k=k[:, :, hs].contiguous(), v=v[:, :, hs].contiguous(),
+                kc=kc[:, :, hs].contiguous(), vc=vc[:, :, hs].contiguous(),
                 topk=hsa.topk_per_head[hs].contiguous()))
 
     def e2e_step_grouped():
@@ -502,21 +506,28 @@ def main():
         start.record()
         for g, st in enumerate(streams):
             d = grp[g]
-            hs = d["hs"]
             with torch.cuda.stream(st), torch.no_grad():
-                st.wait_event(start)
-                q[:, :, hs].copy_(d["q_h"], non_blocking=True)
-                k[:, kv_len - new:, hs].copy_(d["k_h"], non_blocking=True)
-                v[:, kv_len - new:, hs].copy_(d["v_h"], non_blocking=True)
-                kn, vn = _compress_blhd(k[:, kv_len - new:, hs], v[:, kv_len - new:, hs], segment_len=FRAME_TOKENS,
+                st.wait_event(start if g == 0 else arrived[g - 1])   # one group's rows at a time on the link
+                d["q"].copy_(d["q_h"], non_blocking=True)
+                d["k"][:, kv_len - new:].copy_(d["k_h"], non_blocking=True)
+                d["v"][:, kv_len - new:].copy_(d["v_h"], non_blocking=True)
+                arrived[g].record(st)
+                kn, vn = _compress_blhd(d["k"][:, kv_len - new:], d["v"][:, kv_len - new:], segment_len=FRAME_TOKENS,
                                         k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, block_size=block)
-                kc[:, kc.shape[1] - kn.shape[1]:, hs].copy_(kn)
-                vc[:, vc.shape[1] - vn.shape[1]:, hs].copy_(vn)
-                out = wa.hsa.hsa_attention(q[:, :, hs], k[:, :, hs], v[:, :, hs], k_coarse=kc[:, :, hs], v_coarse=vc[:, :, hs],
+                d["kc"][:, d["kc"].shape[1] - kn.shape[1]:].copy_(kn)
+                d["vc"][:, d["vc"].shape[1] - vn.shape[1]:].copy_(vn)
+                out = wa.hsa.hsa_attention(d["q"], d["k"], d["v"], k_coarse=d["kc"], v_coarse=d["vc"],
                                            k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
                                            block_size=block, proj_segment_len=FRAME_TOKENS, topk_per_head=d["topk"],
                                            force_generic=args.force_generic)
-                d["out_h"].copy_(out, non_blocking=True)
+                d["out"] = out
+        # outputs leave after the last group's rows have arrived: on this platform a device-to-host copy that runs
+        # against a host-to-device copy slows both down several times
+        for g, st in enumerate(streams):
+            d = grp[g]
+            with torch.cuda.stream(st):
+                st.wait_event(arrived[E2E_GROUPS - 1])
+                d["out_h"].copy_(d["out"], non_blocking=True)
                 done[g].record(st)
         for ev in done:
             torch.cuda.current_stream().wait_event(ev)
