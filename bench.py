@@ -36,6 +36,9 @@ WORKLOADS = {
     # name: (q frames, kv frames, block, top-k policy)
     "c2": dict(q_frames=3, kv_frames=21, block=128, topk="adaptive", seed=1, scale=1.0 / math.sqrt(HEAD_DIM)),
     "c5": dict(q_frames=3, kv_frames=480, block=64, topk=32, seed=4, scale=1.0),
+    # the long-horizon cache with 128-token blocks (the shape the tcgen05 kernel covers); top-16 blocks = the same
+    # 2048 selected tokens per query row as top-32 at 64-token blocks
+    "c5-128": dict(q_frames=3, kv_frames=480, block=128, topk=16, seed=4, scale=1.0),
 }
 L2_FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one hsa_fwd_sm100_kernel launch on workload c2

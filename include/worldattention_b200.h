@@ -183,6 +183,14 @@ typedef struct wa_hsa_params {
      * normaliser `[B, H, Lq]` (-inf where the branch saw no key), for wa_merge_partials. */
     const int32_t *index_in, *num_in;
     float *part_sparse, *part_linear, *lse_sparse, *lse_linear;
+    /* Pooled-key cache (no reference counterpart: the reference pools the whole key cache on every call).
+     * k_pooled: float32 `[B, H, Nkv, D]` (Nkv = ceil(Lkv / block_size)) that the caller keeps across calls on a
+     * growing cache.  Its first k_pooled_valid blocks already hold the block means of k -- blocks that were complete
+     * at an earlier call and have not changed since.  The call pools only the blocks from k_pooled_valid on into it
+     * and routes on the whole buffer (results are identical to pooling everything).  NULL: the pooled keys live in
+     * the workspace and every block is pooled.  Ignored when index_in is set. */
+    float *k_pooled;
+    int32_t k_pooled_valid, reserved2;
 } wa_hsa_params;
 
 /* Bytes of workspace wa_hsa_forward needs for these sizes (pointers in `p` are ignored). */

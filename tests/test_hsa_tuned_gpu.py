@@ -191,3 +191,70 @@ def test_head_slices_of_a_resident_cache_equal_the_full_call(wa):
         assert used_p and not q[:, :, hs].is_contiguous()
         assert torch.equal(num_p, num[:, hs])
         assert torch.equal(part, full[:, :, hs])
+
+
+def test_64_token_blocks_take_the_tcgen05_kernel_for_the_linear_branch(wa):
+    """Routing block size 64 (the reference class's default): the sparse branch runs on the SIMT kernel, the linear
+    branch on the tcgen05 kernel; the result matches the oracle and the all-SIMT path."""
+    heads, q_len, kv_len, seg, bs = 3, 500, 2100, 700, 64
+    rng = np.random.default_rng(21)
+    q = _draw(rng, (1, q_len, heads, D), 0.3)
+    k = _draw(rng, (1, kv_len, heads, D), 0.3)
+    v = _draw(rng, (1, kv_len, heads, D), 1.0)
+    ek = _proj(math.ceil(seg / bs), seg, bs, rng)
+    gw = (rng.standard_normal((D, D)) * 0.05).astype(np.float32)
+    gb = (rng.standard_normal((D,)) * 0.3).astype(np.float32)
+    lin = torch.nn.Linear(D, D).to(dev())
+    with torch.no_grad():
+        lin.weight.copy_(to_gpu(gw)); lin.bias.copy_(to_gpu(gb))
+    topk = [5, 12, 0]
+    kwargs = dict(k_proj_mat=to_gpu(ek, "bf16"), v_proj_mat=to_gpu(ek, "bf16"), gate_lin=lin, block_size=bs,
+                  proj_segment_len=seg, topk_per_head=torch.tensor(topk, dtype=torch.int32), return_routing=True)
+    args = [to_gpu(x, "bf16") for x in (q, k, v)]
+    launches0 = wa._lib.lib().wa_launch_count()
+    out, (index, num, _, used) = wa.hsa.hsa_attention(*args, check_status=True, **kwargs)
+    launches_hybrid = wa._lib.lib().wa_launch_count() - launches0
+    ref, (index_g, num_g, _, _) = wa.hsa.hsa_attention(*args, force_generic=True, **kwargs)
+    assert not used                                   # the fused kernel itself needs 128-token blocks
+    assert torch.equal(index, index_g) and torch.equal(num, num_g)
+    want = O.hsa_attention(q, k, v, k_proj_mat=ek, v_proj_mat=ek, gate_weight=gw, gate_bias=gb, block_size=bs,
+                           proj_segment_len=seg, dtype="bf16", topk_per_head=topk)
+    max_abs, mean_rel = attention_error(to_np(out), want)
+    assert max_abs < MAX_ABS and mean_rel < MEAN_REL, ("vs oracle", max_abs, mean_rel)
+    max_abs_g, mean_rel_g = attention_error(to_np(out), to_np(ref))
+    assert max_abs_g < MAX_ABS and mean_rel_g < MEAN_REL, ("vs generic", max_abs_g, mean_rel_g)
+    assert launches_hybrid >= 6                       # pooling, routing, compress, sparse, schedule + tcgen05 linear, combine
+
+
+def test_pooled_key_cache_gives_the_same_result_and_only_pools_new_blocks(wa):
+    """The caller-kept pooled-key buffer: a first call fills it, a later call on the grown cache trusts the rows of
+    the blocks that were complete before and pools only the rest; outputs and routing equal the plain call."""
+    heads, q_len, kv_old, kv_len, seg = 3, 300, 1560, 3120, 1560
+    rng = np.random.default_rng(31)
+    q, k, v = (to_gpu(_draw(rng, (1, n, heads, D), s), "bf16") for n, s in ((q_len, 0.3), (kv_len, 0.3), (kv_len, 1.0)))
+    hsa = wa.hsa.HSAAttention(heads, D, block_size=128, proj_segment_len=seg).to(dev())
+    wa.hsa_stage.init_hsa_parameters(hsa)
+    with torch.no_grad():
+        hsa.gate_lin.weight.normal_(0, 0.05)
+    common = dict(k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=128,
+                  proj_segment_len=seg, return_routing=True)
+    nb_old, nb_new = -(-kv_old // 128), -(-kv_len // 128)
+    # call 1 on the old cache fills the buffer
+    cache_old = torch.full((1, heads, nb_old, D), float("nan"), device=dev())
+    out1, (idx1, num1, _, _) = wa.hsa.hsa_attention(q, k[:, :kv_old], v[:, :kv_old], k_pooled_cache=cache_old, **common)
+    plain1, (pidx1, pnum1, _, _) = wa.hsa.hsa_attention(q, k[:, :kv_old], v[:, :kv_old], **common)
+    assert torch.equal(out1, plain1) and torch.equal(idx1, pidx1) and torch.equal(num1, pnum1)
+    assert torch.isfinite(cache_old).all()
+    # call 2 on the grown cache: the blocks that were complete (kv_old // 128) are trusted, the rest recomputed
+    valid = kv_old // 128
+    cache_new = torch.full((1, heads, nb_new, D), float("nan"), device=dev())
+    cache_new[:, :, :valid] = cache_old[:, :, :valid]
+    out2, (idx2, num2, _, used) = wa.hsa.hsa_attention(q, k, v, k_pooled_cache=cache_new, k_pooled_valid=valid, **common)
+    plain2, (pidx2, pnum2, _, _) = wa.hsa.hsa_attention(q, k, v, **common)
+    assert used and torch.equal(out2, plain2) and torch.equal(idx2, pidx2) and torch.equal(num2, pnum2)
+    assert torch.isfinite(cache_new).all()
+    # the trusted rows are really not recomputed: a poisoned trusted row changes the routing
+    cache_bad = cache_new.clone()
+    cache_bad[:, :, 0] = 50.0
+    _, (idx3, _, _, _) = wa.hsa.hsa_attention(q, k, v, k_pooled_cache=cache_bad, k_pooled_valid=valid, **common)
+    assert not torch.equal(idx3, pidx2) and torch.equal(cache_bad[:, :, 0], torch.full_like(cache_bad[:, :, 0], 50.0))

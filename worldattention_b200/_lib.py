@@ -38,6 +38,7 @@ class HsaParams(C.Structure):
         ("thresholds_out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("index_in", C.c_void_p), ("num_in", C.c_void_p), ("part_sparse", C.c_void_p), ("part_linear", C.c_void_p),
         ("lse_sparse", C.c_void_p), ("lse_linear", C.c_void_p),
+        ("k_pooled", C.c_void_p), ("k_pooled_valid", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 

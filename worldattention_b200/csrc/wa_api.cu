@@ -18,9 +18,12 @@ unsigned long long &launch_counter() {
 static bool g_profile = false;
 static cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
 static bool g_ev_valid = false;
+static int g_profile_pause = 0;
+
+void profile_pause(bool on) { g_profile_pause += on ? 1 : -1; }
 
 void profile_mark(bool begin, cudaStream_t stream) {
-    if (!g_profile) return;
+    if (!g_profile || g_profile_pause > 0) return;
     if (!g_ev0) {
         if (cudaEventCreate(&g_ev0) != cudaSuccess || cudaEventCreate(&g_ev1) != cudaSuccess) {
             g_ev0 = g_ev1 = nullptr;
@@ -154,7 +157,10 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
                "%s: workspace of %zu bytes required, got %zu", what, w.total, p->workspace_bytes);
     WA_REQUIRE((uintptr_t)p->workspace % 256 == 0, WA_ERR_ALIGN, "%s: workspace must be 256-byte aligned", what);
     char *ws = (char *)p->workspace;
-    float *q_pooled = (float *)(ws + w.q_pooled), *k_pooled = (float *)(ws + w.k_pooled);
+    float *q_pooled = (float *)(ws + w.q_pooled), *k_pooled = p->k_pooled ? p->k_pooled : (float *)(ws + w.k_pooled);
+    const int k_first = p->k_pooled ? p->k_pooled_valid : 0;
+    WA_REQUIRE(k_first >= 0 && k_first <= w.Nkv, WA_ERR_ARG, "%s: k_pooled_valid must be in [0, %d], got %d", what, w.Nkv, k_first);
+    WA_REQUIRE(!p->k_pooled || (uintptr_t)p->k_pooled % 16 == 0, WA_ERR_ALIGN, "%s: k_pooled must be 16-byte aligned", what);
     float *block_attn = (float *)(ws + w.block_attn);
     int32_t *index = p->index_out ? p->index_out : (int32_t *)(ws + w.index);
     int32_t *num = p->num_out ? p->num_out : (int32_t *)(ws + w.num);
@@ -193,7 +199,7 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
         // pooling, then scores + sort + thresholds + counts (+ the tcgen05 kernel's work order) in one launch
         int *counters = (int *)(ws + w.counters);
         if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream,
-                              counters, p->H + 1)))
+                              counters, p->H + 1, k_first)))
             return rc;
         SchedJob job{};
         if (tuned) job = hsa_sm100_sched_job(p, ws + w.tuned);
@@ -242,9 +248,15 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
                                  num, w.Nkv, nullptr, /*round_in=*/1, /*round_out=*/1, nullptr, stream);
     profile_mark(false, stream);
     if (rc) return rc;
-    if ((rc = wa_linear_branch(&p->q, &kc, &vc, &linear, p->B, p->H, p->Lq, Lc, p->D, lin_dtype == WA_BF16, nullptr,
-                               stream)))
+    if (!(p->flags & WA_HSA_FORCE_GENERIC) && hsa_sm100_linear_supported(p, Lc, &kc, &vc)) {
+        // routing block size other than 128: the sparse branch ran on the SIMT kernel above, but the linear branch
+        // does not depend on the block size and takes the tcgen05 kernel (float32 result, as in the fused path)
+        linear.dtype = WA_F32;
+        if ((rc = hsa_sm100_launch_linear(p, Lc, &kc, &vc, (float *)linear.ptr, ws + w.tuned, stream))) return rc;
+    } else if ((rc = wa_linear_branch(&p->q, &kc, &vc, &linear, p->B, p->H, p->Lq, Lc, p->D, lin_dtype == WA_BF16, nullptr,
+                                      stream))) {
         return rc;
+    }
     return wa_gate_combine(&p->q, &sparse, &linear, &p->out, p->B, p->Lq, p->H, p->D, p->gate_w, p->gate_b,
                            p->gate_dtype, lin_dtype == WA_BF16, stream);
 }

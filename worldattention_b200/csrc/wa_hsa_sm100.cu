@@ -1010,7 +1010,7 @@ static int max_grid() {
 }
 
 struct TunedWs {
-    size_t order, counter, w_bf16, bias, total;
+    size_t order, counter, w_bf16, bias, zeros, total;
 };
 static TunedWs tuned_plan(const wa_hsa_params *p) {
     TunedWs w{};
@@ -1020,6 +1020,7 @@ static TunedWs tuned_plan(const wa_hsa_params *p) {
     w.counter = c; c = align_up(c + 2 * sizeof(int), 256);
     w.w_bf16 = c; c = align_up(c + (size_t)TILE * TILE * 2, 256);
     w.bias = c; c = align_up(c + TILE * sizeof(float), 256);
+    w.zeros = c; c = align_up(c + items * sizeof(int32_t), 256);   // an all-zero `num` for the linear-branch-only launch
     w.total = c;
     return w;
 }
@@ -1139,6 +1140,38 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     profile_mark(false, stream);
     return check_launch("wa_hsa_forward(tcgen05)");
+}
+
+// The linear branch alone on the tcgen05 kernel (any routing block size): every item runs with an empty selection
+// and the normalised float32 result goes to `linear_out` [B, Lq, H, 128].
+bool hsa_sm100_linear_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc) {
+    using namespace sm100;
+    if (p->D != TILE || Lc <= 0 || p->part_sparse) return false;
+    if (!view_ok(&p->q) || !view_ok(&p->k) || !view_ok(&p->v) || !view_ok(kc) || !view_ok(vc)) return false;
+    if (p->out.dtype != WA_BF16 || !p->out.ptr || (uintptr_t)p->out.ptr % 16 || p->out.stride_h % 8 || p->out.stride_l % 8 ||
+        p->out.stride_b % 8)
+        return false;
+    if ((long long)p->B * p->H * ceil_div(p->Lq, TILE) > (1 << 24)) return false;
+    return device_is_sm100() && encode_fn() != nullptr;
+}
+
+int hsa_sm100_launch_linear(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc, float *linear_out,
+                            void *workspace, cudaStream_t stream) {
+    using namespace sm100;
+    WA_REQUIRE((uintptr_t)linear_out % 16 == 0, WA_ERR_ALIGN, "wa_hsa_forward(tcgen05 linear): output must be 16-byte aligned");
+    const TunedWs w = tuned_plan(p);
+    int32_t *zeros = (int32_t *)((char *)workspace + w.zeros);
+    const int nq = ceil_div(p->Lq, TILE);
+    cudaError_t e = cudaMemsetAsync(zeros, 0, (size_t)p->B * p->H * nq * sizeof(int32_t), stream);
+    if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05 linear): %s", cudaGetErrorString(e));
+    wa_hsa_params pl = *p;
+    pl.part_sparse = nullptr; pl.lse_sparse = nullptr; pl.lse_linear = nullptr;
+    pl.part_linear = linear_out;
+    profile_pause(true);   // the timing bracket of this forward belongs to the sparse-branch kernel
+    const int rc = hsa_sm100_launch(&pl, Lc, kc, vc, zeros /*never read: no item selects a block*/, zeros, nq, 1, workspace, false,
+                                    stream);
+    profile_pause(false);
+    return rc;
 }
 
 }  // namespace wa

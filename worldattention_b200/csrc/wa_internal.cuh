@@ -78,9 +78,10 @@ __device__ inline void convert_gate_slice(const SchedJob &job, int first, int co
     }
 }
 
-// routing (wa_routing.cu): pools x and optionally y in one launch; zeroes `n_zero` ints at `zero` on the way
+// routing (wa_routing.cu): pools x and optionally y in one launch; zeroes `n_zero` ints at `zero` on the way.
+// `y_first_block`: the first blocks of y are already pooled in py (rows [0, y_first_block) per batch and head).
 int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
-                int block_size, cudaStream_t stream, int *zero = nullptr, int n_zero = 0);
+                int block_size, cudaStream_t stream, int *zero = nullptr, int n_zero = 0, int y_first_block = 0);
 
 // routing (wa_routing.cu): scores, sort, Gini thresholds and counts in ONE launch (plus `job` when its order is set).
 // `sorted` ([rows, Nkv] float32) and `gini` ([rows]) are scratch; `counters` are H + 1 ints that are zero on entry.
@@ -90,6 +91,7 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
 
 // optional CUDA-event bracket around the attention kernel (wa_api.cu)
 void profile_mark(bool begin, cudaStream_t stream);
+void profile_pause(bool on);   // nested launches that must not move the bracket
 
 // tcgen05 fused HSA kernel (wa_hsa_sm100.cu)
 size_t hsa_sm100_workspace_bytes(const wa_hsa_params *p);
@@ -100,5 +102,10 @@ SchedJob hsa_sm100_sched_job(const wa_hsa_params *p, void *workspace);
 int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc,
                      const int32_t *index, const int32_t *num, int Nq, int Nkv, void *workspace,
                      bool prepared, cudaStream_t stream);
+
+// the linear branch alone on the tcgen05 kernel (bf16, head_dim 128; any routing block size): float32 [B, Lq, H, 128]
+bool hsa_sm100_linear_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc);
+int hsa_sm100_launch_linear(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc, float *linear_out,
+                            void *workspace, cudaStream_t stream);
 
 }  // namespace wa

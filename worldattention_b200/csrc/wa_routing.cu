@@ -17,21 +17,22 @@ template <bool VEC_BF16>
 __global__ void __launch_bounds__(POOL_THREADS)
 pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, int aligned,
                    float *__restrict__ pooled, View4 x2, int L2, int num_blocks2, int aligned2,
-                   float *__restrict__ pooled2, int *__restrict__ zero, int n_zero) {
+                   float *__restrict__ pooled2, int out_blocks2, int *__restrict__ zero, int n_zero) {
     int nb = blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
     if (n_zero && nb == 0 && h == 0 && b == 0)   // counters of the kernel that follows on the stream
         for (int i = threadIdx.x; i < n_zero; i += POOL_THREADS) zero[i] = 0;
+    int out_blocks = num_blocks;   // rows per (batch, head) of the output buffer
     if (nb >= num_blocks) {   // second tensor (keys) pooled by the same launch
         nb -= num_blocks;
-        x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2;
+        x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2; out_blocks = out_blocks2;
     }
     const int t0 = nb * block_size;
     const int n_real = min(block_size, L - t0);
     extern __shared__ double pool_smem[];  // [rows_in_flight][D]
 
     const long long base = (long long)b * x.sb + (long long)h * x.sh;
-    float *dst = pooled + (((long long)b * H + h) * num_blocks + nb) * (long long)D;
+    float *dst = pooled + (((long long)b * H + h) * out_blocks + nb) * (long long)D;
 
     if (VEC_BF16) {
         // 8 bf16 per thread per token; lanes_per_row threads cover one token row.
@@ -118,17 +119,18 @@ pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks,
 template <int UNROLL>
 __global__ void __launch_bounds__(POOL_THREADS)
 pool_warp_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, int aligned, float *__restrict__ pooled,
-                 View4 x2, int L2, int num_blocks2, int aligned2, float *__restrict__ pooled2, int B,
+                 View4 x2, int L2, int num_blocks2, int aligned2, float *__restrict__ pooled2, int out_blocks2, int B,
                  int *__restrict__ zero, int n_zero) {
     if (n_zero && blockIdx.x == 0)   // counters of the kernel that follows on the stream
         for (int i = threadIdx.x; i < n_zero; i += POOL_THREADS) zero[i] = 0;
     const int lane = threadIdx.x & 31;
     long long item = (long long)blockIdx.x * (POOL_THREADS / 32) + (threadIdx.x >> 5);   // ((b, block), head), head fastest
     const long long items1 = (long long)B * num_blocks * H;
+    int out_blocks = num_blocks;   // rows per (batch, head) of the output buffer
     if (item >= items1) {   // second tensor (keys) pooled by the same launch
         item -= items1;
         if (item >= (long long)B * num_blocks2 * H) return;
-        x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2;
+        x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2; out_blocks = out_blocks2;
     }
     const int h = (int)(item % H);
     const int nb = (int)((item / H) % num_blocks);
@@ -169,7 +171,7 @@ pool_warp_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, i
         for (int i = 0; i < 8; ++i)
             out[i] = aligned ? bf16_round_f((float)((double)acc[i] / (double)block_size))
                              : __fdiv_rn(bf16_round_f(acc[i]), (float)n_real);
-        float4 *dst = reinterpret_cast<float4 *>(pooled + (((long long)b * H + h) * num_blocks + nb) * (long long)D + col);
+        float4 *dst = reinterpret_cast<float4 *>(pooled + (((long long)b * H + h) * out_blocks + nb) * (long long)D + col);
         dst[0] = make_float4(out[0], out[1], out[2], out[3]);
         dst[1] = make_float4(out[4], out[5], out[6], out[7]);
     }
@@ -687,8 +689,20 @@ static bool pool_vec_ok(const wa_tensor4 *x, int D) {
 
 // Pools `x` (and, when given, `y`, e.g. queries and keys of one forward) in a single launch.
 int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
-                int block_size, cudaStream_t stream, int *zero, int n_zero) {
-    const int nbx = ceil_div(Lx, block_size), nby = y ? ceil_div(Ly, block_size) : 0;
+                int block_size, cudaStream_t stream, int *zero, int n_zero, int y_first_block) {
+    const int nbx = ceil_div(Lx, block_size);
+    const int nby_all = y ? ceil_div(Ly, block_size) : 0;   // rows per (batch, head) of py
+    const int y_aligned = y ? Ly % block_size == 0 : 0;
+    wa_tensor4 y_tail;
+    if (y && y_first_block >= nby_all) y = nullptr;   // every key block is pooled already
+    if (y && y_first_block > 0) {   // the first blocks of y are pooled already: start at token y_first_block * block_size
+        y_tail = *y;
+        y_tail.ptr = (char *)y->ptr + (size_t)y_first_block * block_size * y->stride_l * dtype_size(y->dtype);
+        y = &y_tail;
+        Ly -= y_first_block * block_size;
+        py += (size_t)y_first_block * D;
+    }
+    const int nby = y ? ceil_div(Ly, block_size) : 0;
     View4 vx = make_view(x), vy = y ? make_view(y) : vx;
     dim3 grid(nbx + nby, H, B);
     const bool vec = pool_vec_ok(x, D) && (!y || pool_vec_ok(y, D));
@@ -699,19 +713,19 @@ int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int
         const long long ctas = (items + POOL_THREADS / 32 - 1) / (POOL_THREADS / 32);
         WA_REQUIRE(ctas < (1ll << 31), WA_ERR_UNSUPPORTED, "wa_pool_blocks: too many blocks");
         pool_warp_kernel<8><<<(unsigned)ctas, POOL_THREADS, 0, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0, px, vy,
-                                                                      Ly, nby, y ? Ly % block_size == 0 : 0, py, B, zero,
+                                                                      Ly, nby, y_aligned, py, nby_all, B, zero,
                                                                       n_zero);
     } else if (vec) {
         const int rows = POOL_THREADS / (D / 8);
         const size_t smem = (size_t)rows * D * sizeof(float);
         WA_REQUIRE(smem <= 48 * 1024, WA_ERR_UNSUPPORTED, "wa_pool_blocks: D=%d too large", D);
         pool_blocks_kernel<true><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
-                                                                       px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py, zero, n_zero);
+                                                                       px, vy, Ly, nby, y_aligned, py, nby_all, zero, n_zero);
     } else {
         const int rows = D >= POOL_THREADS ? 1 : POOL_THREADS / D;
         const size_t smem = (size_t)rows * (D < POOL_THREADS ? D : POOL_THREADS) * sizeof(double);
         pool_blocks_kernel<false><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
-                                                                        px, vy, Ly, nby, y ? Ly % block_size == 0 : 0, py, zero, n_zero);
+                                                                        px, vy, Ly, nby, y_aligned, py, nby_all, zero, n_zero);
     }
     return check_launch("wa_pool_blocks");
 }
@@ -725,7 +739,7 @@ extern "C" int wa_pool_blocks(const wa_tensor4 *x, int B, int L, int H, int D, i
                "wa_pool_blocks: sizes must be positive (B=%d L=%d H=%d D=%d block=%d)", B, L, H, D,
                block_size);
     WA_REQUIRE(H <= 65535 && B <= 65535, WA_ERR_UNSUPPORTED, "wa_pool_blocks: B, H must be <= 65535");
-    return pool_launch(x, L, pooled, nullptr, 0, nullptr, B, H, D, block_size, (cudaStream_t)stream);
+    return pool_launch(x, L, pooled, nullptr, 0, nullptr, B, H, D, block_size, (cudaStream_t)stream, nullptr, 0, 0);
 }
 
 extern "C" int wa_route_scores(const float *q_pooled, const float *k_pooled, int B, int H, int Nq,
