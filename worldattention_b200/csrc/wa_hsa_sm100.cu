@@ -38,7 +38,7 @@ constexpr int S_BUFS = 3;            // score products run up to two tiles ahead
 constexpr int Q_STAGES = 2;          // the staged output of item j leaves from one Q buffer while item j+1 loads the other
 constexpr int KV_STAGES = 3;         // shared-memory ring depth for K tiles
 constexpr int V_STAGES = 2;          // shared-memory ring depth for V tiles
-constexpr int SMEM_BYTES = (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES + 3072 /*barriers, bias, exchange*/;
+constexpr int SMEM_BYTES = (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES + 3072 /*barriers, bias*/;
 constexpr long long WAIT_CYCLES = 4000000000ll;
 
 // Optional event trace for kernel tuning (compile with -DWA_SM100_TRACE): CTA 0 appends
@@ -226,6 +226,24 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),            \
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory")
 
+// Quad-row shapes: a 16-row group of lanes is read so that thread t holds rows t/4 and t/4+8 and, per 8-column step j,
+// the column pair 8j + 2(t%4), +1 of each (registers 4j..4j+3: row A pair, row B pair) -- a row lives in one quad.
+// The 16x128b store is the matching shape for 32-bit words: registers 2j, 2j+1 = word 4j + t%4 of row A, row B.
+#define TMEM_LDQ64(taddr, r) \
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];" \
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]) \
+        : "r"(taddr) : "memory")
+#define TMEM_LDQ16(taddr, r) \
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];" \
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) \
+        : "r"(taddr) : "memory")
+#define TMEM_STQ16(taddr, r) \
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" \
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory")
+#define TMEM_STP32(taddr, r) \
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" \
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory")
+
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -268,19 +286,7 @@ __host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major, int n) {
            | ((uint32_t)(TILE >> 4) << 24);
 }
 
-template <bool MASKED>
-__device__ __forceinline__ float row_max32(const uint32_t (&r)[32], int col0, int valid) {
-    float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-        if (!MASKED || col0 + j < valid) m0 = fmaxf(m0, __uint_as_float(r[j]));
-        if (!MASKED || col0 + j + 1 < valid) m1 = fmaxf(m1, __uint_as_float(r[j + 1]));
-    }
-    return fmaxf(m0, m1);
-}
-
-// 32 scores -> 32 probabilities packed as 16 bf16 pairs; returns their float32 sum.
-// The arithmetic runs on pairs of columns with the packed float32x2 instructions of this architecture (one
+// Softmax arithmetic.  It runs on pairs of columns with the packed float32x2 instructions of this architecture (one
 // issue slot for two results).  2^x on the FMA pipe: split x into round(x) + f, f in [-0.5, 0.5], evaluate a
 // cubic for 2^f and add round(x) to the exponent field; relative error < 2^-10, below the bf16 rounding of P.
 // The special-function unit (16 results per clock per SM) is the narrowest pipe of the softmax, so every
@@ -302,26 +308,40 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
 #endif
 constexpr int POLY_EVERY = WA_POLY_EVERY;
 
-template <bool MASKED, int OFF>
-__device__ __forceinline__ float exp_pack32(const uint32_t (&r)[32], uint32_t (&pk)[32], float scale, float m, int col0,
-                                            int valid) {
-    const float2 sc = make_float2(scale, scale), nm = make_float2(-m, -m);
-    float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-        const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc, nm);
-        float2 pr;
-        if ((j >> 1) % POLY_EVERY == 0) pr = ex2_poly2(x);
-        else pr = make_float2(ex2(x.x), ex2(x.y));
-        if (MASKED) {
-            if (col0 + j >= valid) pr.x = 0.f;
-            if (col0 + j + 1 >= valid) pr.y = 0.f;
-        }
-        acc = __fadd2_rn(acc, pr);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(pr.x, pr.y);
-        pk[OFF + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
+
+// One 8-column step of a quad-row tile: this thread's column pair of row A (x0, x1) and of row B (x2, x3)
+// -> probabilities, packed to one bf16 pair per row; row sums accumulate in accA / accB (packed float32x2).
+template <bool POLY, bool MASKED>
+__device__ __forceinline__ void exp_step(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, float2 sc, float2 nmA, float2 nmB,
+                                         float2 &accA, float2 &accB, uint32_t &pkA, uint32_t &pkB, int col, int valid) {
+    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(x0), __uint_as_float(x1)), sc, nmA);
+    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(x2), __uint_as_float(x3)), sc, nmB);
+    float2 pa, pb;
+    if (POLY) {
+        pa = ex2_poly2(xa);
+        pb = ex2_poly2(xb);
+    } else {
+        pa = make_float2(ex2(xa.x), ex2(xa.y));
+        pb = make_float2(ex2(xb.x), ex2(xb.y));
     }
-    return acc.x + acc.y;
+    if (MASKED) {
+        if (col >= valid) pa.x = pb.x = 0.f;
+        if (col + 1 >= valid) pa.y = pb.y = 0.f;
+    }
+    accA = __fadd2_rn(accA, pa);
+    accB = __fadd2_rn(accB, pb);
+    __nv_bfloat162 ha = __floats2bfloat162_rn(pa.x, pa.y), hb = __floats2bfloat162_rn(pb.x, pb.y);
+    pkA = *reinterpret_cast<uint32_t *>(&ha);
+    pkB = *reinterpret_cast<uint32_t *>(&hb);
+}
+
+__device__ __forceinline__ float quad_max(float x) {
+    x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
+    return fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
+}
+__device__ __forceinline__ float quad_sum(float x) {
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    return x + __shfl_xor_sync(0xffffffffu, x, 2);
 }
 
 struct ItemDesc {
@@ -343,7 +363,6 @@ struct Barriers {
     ItemDesc items[2];
     int valid[8];            // real token count of the K-type tiles in flight, ring indexed by global tile number
     float bias[TILE];        // gate bias
-    float xch[2][2][TILE];   // row-maximum exchange between the two threads of a row: [tile parity][half][row]
 };
 
 static_assert(sizeof(Barriers) <= 3072, "barrier block exceeds its shared-memory budget");
@@ -639,18 +658,22 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
-        // ================= softmax / epilogue: two threads per query row (64 score columns each) ==========
-        // Warps 0..3 own columns [0,64), warps 4..7 columns [64,128) of the same rows (a warp may only touch
-        // the 32 tensor-memory lanes selected by warp % 4).  The two threads of a row meet at a 64-thread
-        // named barrier once per tile to agree on the row maximum.
-        const int half = warp >> 2;
-        const int row = (warp & 3) * 32 + lane;
-        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
-        const int pair_bar = 2 + (warp & 3);
+        // ================= softmax / epilogue: a quad of threads per query row =================
+        // A warp may only touch the 32 tensor-memory lanes (rows) selected by warp % 4; warps w and w + 4 share that
+        // row group and take 16 rows each.  Scores are read in the quad-row shape: thread t holds rows t/4 and t/4 + 8
+        // of its 16 and, of each, the column pairs 8j + 2(t%4), +1 (32 columns per row).  A row therefore lives in
+        // one quad of one warp: the row maximum and the row sum are two shuffles, no shared memory, no rendezvous of
+        // warps -- the eight softmax warps run independently and drift apart, so the arithmetic of one covers the
+        // tensor-memory round trips and barrier waits of the other on the same scheduler.
+        const int rg = warp & 3, hb = warp >> 2;            // row group (32 rows), 16-row half inside it
+        const int g = lane >> 2, c2 = lane & 3;
+        const int rowA = rg * 32 + hb * 16 + g, rowB = rowA + 8;
+        const uint32_t lane_addr = ((uint32_t)(rg * 32 + hb * 16)) << 16;
         uint32_t jcount = 0, sg = 0;       // items and K-type tiles seen so far
         uint32_t ph_od = 0;
         uint32_t pv_count = 0;             // PV products requested so far
         bool ok = true;
+        const float2 sc = make_float2(p.scale_log2, p.scale_log2);
 
         while (ok) {
             const uint32_t slot = jcount & 1u;
@@ -663,17 +686,19 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const int n_kv = n_sel + lin_tiles;
             const uint32_t qs = jcount % Q_STAGES;
             uint8_t *q_stage = q_s + qs * TILE_BYTES;
-            const int token = qb * TILE + row;
-            const bool row_ok = token < p.Lq;
-            const long long part_off = (((long long)b * p.Lq + token) * p.H + h) * TILE + half * HALF;
-            const long long lse_off = ((long long)b * p.H + h) * p.Lq + token;
+            const int tokenA = qb * TILE + rowA, tokenB = tokenA + 8;
+            const bool okA = tokenA < p.Lq, okB = tokenB < p.Lq;
+            // float32 offsets of this thread's first column pair in the partial outputs, and of the rows' normalisers
+            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * TILE + 2 * c2;
+            const long long partB = partA + 8ll * p.H * TILE;
+            const long long lseA = ((long long)b * p.H + h) * p.Lq + tokenA, lseB = lseA + 8;
             const int gbuf = (sg + n_kv) % S_BUFS;
-            float inv_l_lin = 0.f, inv_l_sp = 0.f;
-            uint32_t park[32];   // the sparse branch's result of this thread's 64 columns (bf16 pairs) until the combine
+            float inv_linA = 0.f, inv_linB = 0.f, inv_spA = 0.f, inv_spB = 0.f;
+            uint32_t park[32];   // the sparse branch's result: word 2j = row A, 2j + 1 = row B, bf16 pair of step j
 
             for (int phase = 0; phase < 2 && ok; ++phase) {
                 const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_kv;
-                float m_used = -INFINITY, l = 0.f;
+                float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;   // l: this thread's columns only
                 for (int t = t0; t < t1 && ok; ++t) {
                     const int buf = (sg + t) % S_BUFS;
                     const uint32_t s_addr = tmem_s + buf * TILE + lane_addr;
@@ -681,66 +706,96 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (!ok) break;
                     WA_TRACE(2);
                     tc_fence_after();
-                    // columns of this thread that hold real tokens (the producer wrote the tile's count)
-                    const int valid = max(0, min(HALF, bar->valid[(sg + t) & 7] - half * HALF));
-                    uint32_t r0[32], r1[32];
-                    TMEM_LD32(s_addr + half * HALF, r0);
-                    TMEM_LD32(s_addr + half * HALF + 32, r1);
+                    const int valid = min(TILE, bar->valid[(sg + t) & 7]);   // real tokens in the tile (the producer wrote the count)
+                    uint32_t r[64];
+                    TMEM_LDQ64(s_addr, r);
                     tmem_wait_ld();
-                    float mx;
-                    if (valid == HALF) mx = fmaxf(row_max32<false>(r0, 0, 0), row_max32<false>(r1, 0, 0));
-                    else mx = fmaxf(row_max32<true>(r0, 0, valid), row_max32<true>(r1, 32, valid));
-                    bar->xch[t & 1][half][row] = mx;
-                    asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-                    mx = fmaxf(mx, bar->xch[t & 1][half ^ 1][row]) * p.scale_log2;
+                    float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
+                    if (valid == TILE) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            xa0 = fmaxf(xa0, __uint_as_float(r[4 * j]));
+                            xa1 = fmaxf(xa1, __uint_as_float(r[4 * j + 1]));
+                            xb0 = fmaxf(xb0, __uint_as_float(r[4 * j + 2]));
+                            xb1 = fmaxf(xb1, __uint_as_float(r[4 * j + 3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int col = 8 * j + 2 * c2;
+                            if (col < valid) {
+                                xa0 = fmaxf(xa0, __uint_as_float(r[4 * j]));
+                                xb0 = fmaxf(xb0, __uint_as_float(r[4 * j + 2]));
+                            }
+                            if (col + 1 < valid) {
+                                xa1 = fmaxf(xa1, __uint_as_float(r[4 * j + 1]));
+                                xb1 = fmaxf(xb1, __uint_as_float(r[4 * j + 3]));
+                            }
+                        }
+                    }
+                    const float mxA = quad_max(fmaxf(xa0, xa1)) * p.scale_log2, mxB = quad_max(fmaxf(xb0, xb1)) * p.scale_log2;
                     WA_TRACE(8);
-                    // lazy rescale: only when the running maximum grows by more than 2^8
-                    float m_new = m_used;
-                    const bool grow = mx > m_used + 8.0f;
-                    if (grow) m_new = mx;
-                    if (__any_sync(0xffffffffu, grow && t > t0)) {
+                    // lazy rescale: only when a running maximum grows by more than 2^8
+                    float mA_new = mA, mB_new = mB;
+                    const bool growA = mxA > mA + 8.0f, growB = mxB > mB + 8.0f;
+                    if (growA) mA_new = mxA;
+                    if (growB) mB_new = mxB;
+                    if (__any_sync(0xffffffffu, (growA || growB) && t > t0)) {
                         // every PV requested so far must have landed before the accumulator is touched
                         ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_empty[(pv_count - 1u) % V_STAGES],
                                                                ((pv_count - 1u) / V_STAGES) & 1u, abort_flag, p.error_flag, 9));
                         if (!ok) break;
                         tc_fence_after();
-                        const float f = (grow && t > t0) ? ex2(m_used - m_new) : 1.0f;
-                        l *= f;
-                        uint32_t ro[16];
+                        const float fA = (growA && t > t0) ? ex2(mA - mA_new) : 1.0f, fB = (growB && t > t0) ? ex2(mB - mB_new) : 1.0f;
+                        lA *= fA;
+                        lB *= fB;
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {   // 16 columns at a time: few live registers beside the tile's scores
-                            TMEM_LD16(tmem_o + lane_addr + half * HALF + c * 16, ro);
+                        for (int c = 0; c < 4; ++c) {   // 32 columns at a time
+                            uint32_t ro[16];
+                            TMEM_LDQ16(tmem_o + lane_addr + c * 32, ro);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) ro[j] = __float_as_uint(__uint_as_float(ro[j]) * f);
-                            TMEM_ST16(tmem_o + lane_addr + half * HALF + c * 16, ro);
+                            for (int j = 0; j < 4; ++j) {
+                                ro[4 * j] = __float_as_uint(__uint_as_float(ro[4 * j]) * fA);
+                                ro[4 * j + 1] = __float_as_uint(__uint_as_float(ro[4 * j + 1]) * fA);
+                                ro[4 * j + 2] = __float_as_uint(__uint_as_float(ro[4 * j + 2]) * fB);
+                                ro[4 * j + 3] = __float_as_uint(__uint_as_float(ro[4 * j + 3]) * fB);
+                            }
+                            TMEM_STQ16(tmem_o + lane_addr + c * 32, ro);
                         }
                         tmem_wait_st();
                     }
-                    m_used = m_new;
-                    // p = 2^(s*c - m), row sum, pack to bf16, write P over the consumed S columns
+                    mA = mA_new;
+                    mB = mB_new;
+                    // p = 2^(s*c - m), row sums, pack to bf16, write P over the consumed S columns
                     uint32_t pk[32];
-                    float sum;
-                    if (valid == HALF) {
-                        sum = exp_pack32<false, 0>(r0, pk, p.scale_log2, m_used, 0, 0);
-                        sum += exp_pack32<false, 16>(r1, pk, p.scale_log2, m_used, 0, 0);
-                    } else {
-                        // ragged tile (the last one of a branch): 32-column chunks without a real token cost nothing
-                        sum = 0.f;
-                        if (valid > 0) sum = exp_pack32<true, 0>(r0, pk, p.scale_log2, m_used, 0, valid);
-                        else {
+                    const float2 nmA = make_float2(-mA, -mA), nmB = make_float2(-mB, -mB);
+                    float2 accA = make_float2(0.f, 0.f), accB = make_float2(0.f, 0.f);
+                    if (valid == TILE) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) pk[j] = 0u;
+                        for (int j = 0; j < 16; ++j) {
+                            if (j % POLY_EVERY == 0)
+                                exp_step<true, false>(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3], sc, nmA, nmB, accA, accB,
+                                                      pk[2 * j], pk[2 * j + 1], 0, 0);
+                            else
+                                exp_step<false, false>(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3], sc, nmA, nmB, accA, accB,
+                                                       pk[2 * j], pk[2 * j + 1], 0, 0);
                         }
-                        if (valid > 32) sum += exp_pack32<true, 16>(r1, pk, p.scale_log2, m_used, 32, valid);
-                        else {
+                    } else {
+                        // ragged tile (the last one of a branch): 8-column steps without a real token cost nothing
 #pragma unroll
-                            for (int j = 16; j < 32; ++j) pk[j] = 0u;
+                        for (int j = 0; j < 16; ++j) {
+                            if (8 * j < valid)
+                                exp_step<false, true>(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3], sc, nmA, nmB, accA, accB,
+                                                      pk[2 * j], pk[2 * j + 1], 8 * j + 2 * c2, valid);
+                            else
+                                pk[2 * j] = pk[2 * j + 1] = 0u;
                         }
                     }
                     WA_TRACE(20);
-                    TMEM_ST32(s_addr + half * 32, pk);
-                    l += sum;
+                    TMEM_STP32(s_addr, pk);
+                    lA += accA.x + accA.y;
+                    lB += accB.x + accB.y;
                     tmem_wait_st();
                     WA_TRACE(21);
                     tc_fence_before();
@@ -749,33 +804,29 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     ++pv_count;
                     if (phase == 1 && t == t0 && n_sel > 0) {
                         // The sparse branch's accumulator: its last PV product had this whole tile to land.  Normalise,
-                        // round to bf16 (the reference stores this branch in bf16) and park it in registers (two bf16
-                        // per word) until the combine; then the linear branch's first PV product may overwrite it.
+                        // round to bf16 (the reference stores this branch in bf16) and park it in registers until the
+                        // combine; then the linear branch's first PV product may overwrite it.
                         ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
                         if (!ok) break;
                         ph_od ^= 1u;
                         tc_fence_after();
                         WA_TRACE(12);
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {   // 16 columns at a time
+                        for (int c = 0; c < 4; ++c) {   // 32 columns at a time
                             uint32_t ro[16];
-                            TMEM_LD16(tmem_o + lane_addr + half * HALF + c * 16, ro);
+                            TMEM_LDQ16(tmem_o + lane_addr + c * 32, ro);
                             tmem_wait_ld();
-                            if (p.part_sparse) {
-                                if (row_ok) {
 #pragma unroll
-                                    for (int j = 0; j < 16; j += 4) {
-                                        float4 o4 = make_float4(__uint_as_float(ro[j]) * inv_l_sp, __uint_as_float(ro[j + 1]) * inv_l_sp,
-                                                                __uint_as_float(ro[j + 2]) * inv_l_sp, __uint_as_float(ro[j + 3]) * inv_l_sp);
-                                        *reinterpret_cast<float4 *>(p.part_sparse + part_off + c * 16 + j) = o4;
-                                    }
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 16; j += 2) {
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(ro[j]) * inv_l_sp,
-                                                                               __uint_as_float(ro[j + 1]) * inv_l_sp);
-                                    park[c * 8 + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
+                            for (int j = 0; j < 4; ++j) {
+                                const float a0 = __uint_as_float(ro[4 * j]) * inv_spA, a1 = __uint_as_float(ro[4 * j + 1]) * inv_spA;
+                                const float b0 = __uint_as_float(ro[4 * j + 2]) * inv_spB, b1 = __uint_as_float(ro[4 * j + 3]) * inv_spB;
+                                if (p.part_sparse) {
+                                    if (okA) *reinterpret_cast<float2 *>(p.part_sparse + partA + 8 * (4 * c + j)) = make_float2(a0, a1);
+                                    if (okB) *reinterpret_cast<float2 *>(p.part_sparse + partB + 8 * (4 * c + j)) = make_float2(b0, b1);
+                                } else {
+                                    __nv_bfloat162 ha = __floats2bfloat162_rn(a0, a1), hbv = __floats2bfloat162_rn(b0, b1);
+                                    park[2 * (4 * c + j)] = *reinterpret_cast<uint32_t *>(&ha);
+                                    park[2 * (4 * c + j) + 1] = *reinterpret_cast<uint32_t *>(&hbv);
                                 }
                             }
                         }
@@ -784,25 +835,27 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     }
                 }
                 if (!ok) break;
-                // ---- end of a branch: total row sum.  The accumulator itself is read out later, when the PV products
-                // have surely landed: the sparse one after the first tile of the linear branch (above), the linear one
-                // in the combine after the gate values have been computed. ----
-                // (the exchange buffer of parity t1 was last read two tiles ago, so it is free here)
-                bar->xch[t1 & 1][half][row] = l;
-                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-                l += bar->xch[t1 & 1][half ^ 1][row];
-                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // the next branch's first tile reuses this buffer
-                const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-                const float lse = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                // ---- end of a branch: total row sums (the four threads of a quad hold the parts of a row).  The
+                // accumulator itself is read out later, when the PV products have surely landed: the sparse one after
+                // the first tile of the linear branch (above), the linear one in the combine. ----
+                lA = quad_sum(lA);
+                lB = quad_sum(lB);
+                const float invA = lA > 0.f ? 1.0f / lA : 0.f, invB = lB > 0.f ? 1.0f / lB : 0.f;
+                const float lsA = lA > 0.f ? (mA + log2f(lA)) * 0.6931471805599453f : -INFINITY;
+                const float lsB = lB > 0.f ? (mB + log2f(lB)) * 0.6931471805599453f : -INFINITY;
                 if (phase == 0) {
-                    inv_l_sp = inv_l;
-                    if (p.lse_sparse && row_ok && half == 0) p.lse_sparse[lse_off] = lse;
+                    inv_spA = invA;
+                    inv_spB = invB;
+                    if (p.lse_sparse && c2 == 0) {
+                        if (okA) p.lse_sparse[lseA] = lsA;
+                        if (okB) p.lse_sparse[lseB] = lsB;
+                    }
                     if (n_sel == 0) {   // no selected block: the sparse term is zero and there is no accumulator to wait for
                         if (p.part_sparse) {
-                            if (row_ok) {
 #pragma unroll
-                                for (int j = 0; j < HALF; j += 4)
-                                    *reinterpret_cast<float4 *>(p.part_sparse + part_off + j) = make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int j = 0; j < 16; ++j) {
+                                if (okA) *reinterpret_cast<float2 *>(p.part_sparse + partA + 8 * j) = make_float2(0.f, 0.f);
+                                if (okB) *reinterpret_cast<float2 *>(p.part_sparse + partB + 8 * j) = make_float2(0.f, 0.f);
                             }
                         } else {
 #pragma unroll
@@ -810,14 +863,22 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         }
                     }
                 } else {
-                    inv_l_lin = inv_l;
-                    if (p.lse_linear && row_ok && half == 0) p.lse_linear[lse_off] = lse;
+                    inv_linA = invA;
+                    inv_linB = invB;
+                    if (p.lse_linear && c2 == 0) {
+                        if (okA) p.lse_linear[lseA] = lsA;
+                        if (okB) p.lse_linear[lseB] = lsB;
+                    }
                 }
             }
             // ---- gate tile + combine ----
-            // gate values of this thread's 64 columns, rounded to bf16 (two per word) as the reference's gate is;
-            // computed while the last PV product of the linear branch is still in flight
+            // gate values of this thread's columns, rounded to bf16 as the reference's gate is (word 2j = row A, 2j + 1 =
+            // row B); computed while the last PV product of the linear branch is still in flight
             uint32_t gpk[32];
+            // byte offset of this thread's 4 bytes inside 16-byte chunk j of a row in the swizzled 128 x 128 bf16 tiles
+            auto tile_off = [&](int row, int j) -> int {
+                return (j >> 3) * HALF_BYTES + row * 128 + (((j & 7) ^ (row & 7)) << 4) + 4 * c2;
+            };
             if (ok) {
                 WA_TRACE(18);
                 ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], ((sg + n_kv) / S_BUFS) & 1u, abort_flag, p.error_flag, 10));
@@ -827,36 +888,38 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 WA_TRACE(13);
                 if (!p.part_linear) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {   // 16 columns at a time
+                    for (int c = 0; c < 4; ++c) {   // 32 columns at a time
+                        uint32_t gsc[16];
                         if (p.has_gate) {
-                            uint32_t g[16];
-                            TMEM_LD16(tmem_s + gbuf * TILE + lane_addr + half * HALF + c * 16, g);
+                            TMEM_LDQ16(tmem_s + gbuf * TILE + lane_addr + c * 32, gsc);
                             tmem_wait_ld();
+                        }
 #pragma unroll
-                            for (int j = 0; j < 16; j += 2) {
-                                const int col = half * HALF + c * 16 + j;
-                                const float z0 = __uint_as_float(g[j]) + bar->bias[col], z1 = __uint_as_float(g[j + 1]) + bar->bias[col + 1];
-                                const float g0 = fmaf(tanh_approx(0.5f * z0), 0.5f, 0.5f);   // sigmoid, one special-function op
-                                const float g1 = fmaf(tanh_approx(0.5f * z1), 0.5f, 0.5f);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
-                                gpk[c * 8 + (j >> 1)] = *reinterpret_cast<uint32_t *>(&h2);
+                        for (int j = 0; j < 4; ++j) {
+                            const int jj = 4 * c + j;
+                            float zA0, zA1, zB0, zB1;
+                            if (p.has_gate) {
+                                const float2 bias2 = *reinterpret_cast<const float2 *>(&bar->bias[8 * jj + 2 * c2]);
+                                zA0 = __uint_as_float(gsc[4 * j]) + bias2.x;
+                                zA1 = __uint_as_float(gsc[4 * j + 1]) + bias2.y;
+                                zB0 = __uint_as_float(gsc[4 * j + 2]) + bias2.x;
+                                zB1 = __uint_as_float(gsc[4 * j + 3]) + bias2.y;
+                            } else {
+                                // no gate module: gate = sigmoid(q); q sits in the swizzled tile that the output overwrites below
+                                const uint32_t qa = *reinterpret_cast<const uint32_t *>(q_stage + tile_off(rowA, jj));
+                                const uint32_t qbv = *reinterpret_cast<const uint32_t *>(q_stage + tile_off(rowB, jj));
+                                zA0 = __uint_as_float(qa << 16);
+                                zA1 = __uint_as_float(qa & 0xffff0000u);
+                                zB0 = __uint_as_float(qbv << 16);
+                                zB1 = __uint_as_float(qbv & 0xffff0000u);
                             }
-                        } else {
-                            // no gate module: gate = sigmoid(q); q sits in the swizzled tile that the output overwrites below
-#pragma unroll
-                            for (int j = 0; j < 16; j += 8) {
-                                const int cc = half * 8 + c * 2 + (j >> 3);
-                                const uint4 qv = *reinterpret_cast<const uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 +
-                                                                                  (((cc & 7) ^ (row & 7)) << 4));
-                                const uint32_t *qw = reinterpret_cast<const uint32_t *>(&qv);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float g0 = fmaf(tanh_approx(0.5f * __uint_as_float(qw[e] << 16)), 0.5f, 0.5f);
-                                    const float g1 = fmaf(tanh_approx(0.5f * __uint_as_float(qw[e] & 0xffff0000u)), 0.5f, 0.5f);
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(g0, g1);
-                                    gpk[c * 8 + (j >> 1) + e] = *reinterpret_cast<uint32_t *>(&h2);
-                                }
-                            }
+                            // sigmoid, one special-function op per element
+                            __nv_bfloat162 ga = __floats2bfloat162_rn(fmaf(tanh_approx(0.5f * zA0), 0.5f, 0.5f),
+                                                                       fmaf(tanh_approx(0.5f * zA1), 0.5f, 0.5f));
+                            __nv_bfloat162 gb = __floats2bfloat162_rn(fmaf(tanh_approx(0.5f * zB0), 0.5f, 0.5f),
+                                                                       fmaf(tanh_approx(0.5f * zB1), 0.5f, 0.5f));
+                            gpk[2 * jj] = *reinterpret_cast<uint32_t *>(&ga);
+                            gpk[2 * jj + 1] = *reinterpret_cast<uint32_t *>(&gb);
                         }
                     }
                 }
@@ -872,9 +935,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (ok) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {   // 16 columns at a time
+                for (int c = 0; c < 4; ++c) {   // 32 columns at a time
                     uint32_t o[16];
-                    TMEM_LD16(tmem_o + lane_addr + half * HALF + c * 16, o);
+                    TMEM_LDQ16(tmem_o + lane_addr + c * 32, o);
                     tmem_wait_ld();
                     WA_TRACE(14);
                     if (c == 3) {
@@ -882,35 +945,24 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tc_fence_before();
                         warp_arrive(&bar->o_free);
                     }
-                    if (p.part_linear) {
-                        if (row_ok) {
 #pragma unroll
-                            for (int j = 0; j < 16; j += 4) {
-                                float4 o4 = make_float4(__uint_as_float(o[j]) * inv_l_lin, __uint_as_float(o[j + 1]) * inv_l_lin,
-                                                        __uint_as_float(o[j + 2]) * inv_l_lin, __uint_as_float(o[j + 3]) * inv_l_lin);
-                                *reinterpret_cast<float4 *>(p.part_linear + part_off + c * 16 + j) = o4;
-                            }
+                    for (int j = 0; j < 4; ++j) {
+                        const int jj = 4 * c + j;
+                        const float a0 = __uint_as_float(o[4 * j]) * inv_linA, a1 = __uint_as_float(o[4 * j + 1]) * inv_linA;
+                        const float b0 = __uint_as_float(o[4 * j + 2]) * inv_linB, b1 = __uint_as_float(o[4 * j + 3]) * inv_linB;
+                        if (p.part_linear) {
+                            if (okA) *reinterpret_cast<float2 *>(p.part_linear + partA + 8 * jj) = make_float2(a0, a1);
+                            if (okB) *reinterpret_cast<float2 *>(p.part_linear + partB + 8 * jj) = make_float2(b0, b1);
+                            continue;
                         }
-                        continue;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; j += 8) {
-                        // 16-byte chunk `cc` of this row inside the swizzled 128 x 128 bf16 tile that held Q
-                        const int cc = half * 8 + c * 2 + (j >> 3);
-                        uint4 o4;
-                        uint32_t *w = reinterpret_cast<uint32_t *>(&o4);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const uint32_t sp = park[c * 8 + (j >> 1) + e];   // two bf16: low half = even column
-                            const uint32_t gg = gpk[c * 8 + (j >> 1) + e];
-                            const float r0 = fmaf(__uint_as_float(o[j + 2 * e]) * inv_l_lin, __uint_as_float(gg << 16),
-                                                  __uint_as_float(sp << 16));
-                            const float r1 = fmaf(__uint_as_float(o[j + 2 * e + 1]) * inv_l_lin, __uint_as_float(gg & 0xffff0000u),
-                                                  __uint_as_float(sp & 0xffff0000u));
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(r0, r1);
-                            w[e] = *reinterpret_cast<uint32_t *>(&h2);
-                        }
-                        *reinterpret_cast<uint4 *>(q_stage + (cc >> 3) * HALF_BYTES + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = o4;
+                        const uint32_t spA = park[2 * jj], spB = park[2 * jj + 1], gA = gpk[2 * jj], gB = gpk[2 * jj + 1];   // low half = even column
+                        __nv_bfloat162 ra = __floats2bfloat162_rn(fmaf(a0, __uint_as_float(gA << 16), __uint_as_float(spA << 16)),
+                                                                   fmaf(a1, __uint_as_float(gA & 0xffff0000u), __uint_as_float(spA & 0xffff0000u)));
+                        __nv_bfloat162 rb = __floats2bfloat162_rn(fmaf(b0, __uint_as_float(gB << 16), __uint_as_float(spB << 16)),
+                                                                   fmaf(b1, __uint_as_float(gB & 0xffff0000u), __uint_as_float(spB & 0xffff0000u)));
+                        // the finished tile is staged in the shared-memory stage that held Q (the layout the TMA store expects)
+                        *reinterpret_cast<uint32_t *>(q_stage + tile_off(rowA, jj)) = *reinterpret_cast<uint32_t *>(&ra);
+                        *reinterpret_cast<uint32_t *>(q_stage + tile_off(rowB, jj)) = *reinterpret_cast<uint32_t *>(&rb);
                     }
                     WA_TRACE(15);
                 }
