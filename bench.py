@@ -219,10 +219,13 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(name, n_gpus):
+def workload_config(name, n_gpus, mode=None):
     spec = WORKLOADS[name]
-    sharding = "none" if n_gpus == 1 else ("head-split, no data-path collective (outputs stay head-sharded)"
-                                           if HEADS % n_gpus == 0 and n_gpus <= 4 else "kv-shard + LSE merge over NCCL")
+    if mode is None:
+        mode = "single" if n_gpus == 1 else ("heads" if HEADS % n_gpus == 0 and n_gpus <= 4 else "kv")
+    sharding = {"single": "none", "heads": "head-split, no data-path collective (outputs stay head-sharded)",
+                "kv": "kv-shard: pooled keys all-gathered, partial outputs exchanged by query rows (all-to-all), LSE merge, "
+                      "finished rows all-gathered (NCCL)"}[mode]
     return {
         "workload": f"{name}: HSA layer forward, B=1 H={HEADS} D={HEAD_DIM}, q={spec['q_frames'] * FRAME_TOKENS} "
                     f"kv={spec['kv_frames'] * FRAME_TOKENS} tokens, block {spec['block']}, top-k {spec['topk']}, seed {spec['seed']}",
@@ -612,7 +615,7 @@ def main():
         "metric": "hsa_fwd_chunks_per_s", "value": args.steps / (total_ms * 1e-3), "unit": "chunks/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, world),
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, world, mode),
         "roofline": {
             "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
             "frac": (achieved / peak_tf) if achieved else None,
