@@ -294,6 +294,33 @@ def bench_hkv(dev, steps=5, layers=30, pages_total=480, pages_hot=64, topk=16):
         if it >= 2:
             gather_ms.append(ev2.elapsed_time(ev3))
             total_ms.append(ev0.elapsed_time(ev1))
+    # ---- the same retrieval without the host in the loop: one scoring launch for all layers, records built on the
+    # device from the device-resident ids (a table of page addresses stands for the residency map), one gather ----
+    from worldattention_b200.hkv.install import build_records_device, gather_records_device
+    from worldattention_b200.hkv.retrieval import score_and_topk_layers
+    want_k, want_v = cache[0].clone(), cache[1].clone()
+    page_stride = page_tokens * row * esz
+    slot_of = torch.arange(pages_total, dtype=torch.int64, device=dev) % pages_hot
+    src_k = pool[0].data_ptr() + slot_of * page_stride
+    src_v = pool[1].data_ptr() + slot_of * page_stride
+    layer_common = dict(src_layer_stride=pages_hot * page_stride, src_token_stride=row, dst_layer_stride=topk * page_stride,
+                        dst_token_stride=row, page_tokens=page_tokens, head_dim=HEAD_DIM)
+    dev_ms = []
+    for it in range(steps + 2):
+        cache.zero_()
+        torch.cuda.synchronize()
+        ev0.record()
+        _, ids_dev, _ = score_and_topk_layers(query, centroids, topk, groups=HEADS)
+        rec_k = build_records_device(ids_dev, src_k, dst=cache[0], rotate=True, **layer_common)
+        rec_v = build_records_device(ids_dev, src_v, dst=cache[1], rotate=False, **layer_common)
+        recs = torch.cat([rec_k, rec_v])
+        gather_records_device(recs, max_tokens=page_tokens, row_elems=HEAD_DIM, head_dim=HEAD_DIM, dtype=torch.bfloat16,
+                              rotations=rot, n_temporal=nt)
+        ev1.record()
+        ev1.synchronize()
+        if it >= 2:
+            dev_ms.append(ev0.elapsed_time(ev1))
+    same_as_host_path = bool(torch.equal(cache[0], want_k) and torch.equal(cache[1], want_v))
     moved = 2.0 * 2 * layers * HEADS * topk * page_tokens * HEAD_DIM * esz     # K and V, read + write
     # spot check: first selected page of layer 0 / head 0, values are copied verbatim
     src0 = pool[1, 0, int(slots[0, 0, 0]), :, 0]
@@ -304,6 +331,8 @@ def bench_hkv(dev, steps=5, layers=30, pages_total=480, pages_hot=64, topk=16):
                         f"of {page_tokens} tokens gathered from a {pages_hot}-page HBM-hot pool, keys re-rotated",
             "gather_ms": float(np.mean(gather_ms)), "gather_gbs": gbs, "hbm_peak_gbs": peak_gbs,
             "gather_frac_of_hbm": gbs / peak_gbs, "bytes_moved": moved, "retrieval_ms_end_to_end": float(np.mean(total_ms)),
+            "retrieval_ms_device_resident": float(np.mean(dev_ms)), "device_resident_equals_host_path": same_as_host_path,
+            "retrieval_gbs_device_resident": moved / (float(np.mean(dev_ms)) * 1e-3) / 1e9,
             "records": int(rec.shape[0]), "verbatim_value_check": ok}
 
 

@@ -224,6 +224,13 @@ int wa_hkv_score_topk(const float *page_index, const float *query, int P, int G,
                       float scale, int topk, float *scores, int32_t *top_ids, float *top_scores,
                       void *stream);
 
+/* The same for `layers` page indexes at once (no reference counterpart: the reference scores layer 0 only):
+ * page_index `[layers, P, G*Dg]`, query `[G*Dg]` shared by the layers (query_layer_stride = 0) or one per layer
+ * (stride in floats); scores `[layers, G, P]`, top_ids / top_scores `[layers, G, topk]`. */
+int wa_hkv_score_topk_layers(const float *page_index, const float *query, int layers, int P, int G, int Dg,
+                             long long query_layer_stride, float scale, int topk, float *scores, int32_t *top_ids,
+                             float *top_scores, void *stream);
+
 /* One page copy of the install step (cache.py:229-246).  `row_elems` contiguous elements per
  * token (H*D for whole-token pages, D for one head), token rows `src_stride` / `dst_stride`
  * elements apart.  `rot` >= 0 selects `rotations[rot]` (shift_temporal_rope, rope.py:50-67) and
@@ -235,6 +242,19 @@ typedef struct wa_page_copy {
     int32_t n_tokens;
     int32_t rot;
 } wa_page_copy;
+
+/* Builds the copy records of a per-head retrieval on the device, where the selected ids are (no reference
+ * counterpart: the reference walks Python lists on the host).  top_ids `[layers, heads, topk]` (topk <= 64, -1 =
+ * none); page_src `[P]`: device address of each page's first token (layer 0, head 0), 0 = not resident.  Per
+ * (layer, head) the resident ids are put in ascending (chronological) order and record r copies page r of that order,
+ * head `head` only (head_dim elements per token, token rows src_token_stride / dst_token_stride elements apart),
+ * from page_src[id] + layer * src_layer_stride to dst_base + layer * dst_layer_stride + r * page_tokens token rows;
+ * rot = r when `rotate` is set, else -1.  Records of absent pages get n_tokens = 0 and are counted in *missing
+ * (optional, caller zeroes it).  records `[layers * heads * topk]`.  Strides of layers in bytes. */
+int wa_hkv_build_records(const int32_t *top_ids, int layers, int heads, int topk, const long long *page_src, int P,
+                         long long src_layer_stride, long long src_token_stride, void *dst_base,
+                         long long dst_layer_stride, long long dst_token_stride, int page_tokens, int head_dim,
+                         int elem_size, int rotate, wa_page_copy *records, int32_t *missing, void *stream);
 
 /* `copies` is a device array of `n` records; `rotations` device float `[R, nt, 2]`. */
 int wa_hkv_gather_pages(const wa_page_copy *copies, int n, int max_tokens, int row_elems,

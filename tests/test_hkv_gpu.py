@@ -220,3 +220,52 @@ def test_apply_truncates_to_capacity_and_skips_rerope_when_disabled(wa, golden):
     want = np.concatenate([g["c1_l0_k"][:, 0:8], g["c1_l0_k"][:, 16:20]], axis=1)
     assert np.array_equal(to_np(small[0]["k"]), want)    # verbatim: re-rotation disabled
     assert int(small[0]["local_end_index"]) == 12 and int(small[0]["global_end_index"]) == 40 * ft
+
+
+def test_device_resident_retrieval_matches_the_host_formulation(wa):
+    """Scoring of all layers in one launch and copy records built on the device give the same installed cache as
+    the per-layer scoring + host-built records."""
+    from worldattention_b200.hkv.install import (build_records_device, gather_pages, gather_records_device,
+                                                  per_head_records)
+    from worldattention_b200.hkv.retrieval import score_and_topk, score_and_topk_layers
+    layers, heads, d, pages, hot, tok, topk = 3, 4, 16, 20, 6, 5, 4
+    g = torch.Generator().manual_seed(7)
+    row = heads * d
+    centroids = torch.randn((layers, pages, row), generator=g).to(dev())
+    query = torch.randn((row,), generator=g).to(dev())
+    pool = torch.randn((2, layers, hot, tok, heads, d), generator=g).to(dev()).bfloat16()
+    nt = 3
+    rot = torch.randn((topk, nt, 2), generator=g)
+    rot = (rot / rot.norm(dim=-1, keepdim=True)).to(dev()).contiguous()
+    # host formulation
+    ids = torch.stack([score_and_topk(query, centroids[l], topk, groups=heads)[1] for l in range(layers)])
+    scores_l, ids_l, vals_l = score_and_topk_layers(query, centroids, topk, groups=heads)
+    assert torch.equal(ids, ids_l)
+    chron = np.sort(ids.cpu().numpy(), axis=-1)
+    slots = chron % hot
+    esz = 2
+    common = dict(src_page_stride=tok * row * esz, src_layer_stride=hot * tok * row * esz, dst_layer_stride=topk * tok * row * esz,
+                  page_tokens=tok, heads=heads, head_dim=d, elem_size=esz)
+    want = torch.zeros((2, layers, topk * tok, heads, d), dtype=torch.bfloat16, device=dev())
+    rot_ids = np.broadcast_to(np.arange(topk, dtype=np.int32), slots.shape)
+    rec = np.concatenate([
+        per_head_records(slots, src_base=pool[0].data_ptr(), dst_base=want[0].data_ptr(), rot=rot_ids, **common),
+        per_head_records(slots, src_base=pool[1].data_ptr(), dst_base=want[1].data_ptr(), rot=None, **common)])
+    gather_pages(rec, max_tokens=tok, row_elems=d, head_dim=d, dtype=torch.bfloat16, device=dev(), rotations=rot, n_temporal=nt)
+    # device formulation; page 3 is declared absent in a second run
+    got = torch.zeros_like(want)
+    slot_of = torch.arange(pages, dtype=torch.int64, device=dev()) % hot
+    page_stride = tok * row * esz
+    lc = dict(src_layer_stride=hot * page_stride, src_token_stride=row, dst_layer_stride=topk * page_stride, dst_token_stride=row,
+              page_tokens=tok, head_dim=d)
+    rk = build_records_device(ids_l, pool[0].data_ptr() + slot_of * page_stride, dst=got[0], rotate=True, **lc)
+    rv = build_records_device(ids_l, pool[1].data_ptr() + slot_of * page_stride, dst=got[1], rotate=False, **lc)
+    gather_records_device(torch.cat([rk, rv]), max_tokens=tok, row_elems=d, head_dim=d, dtype=torch.bfloat16, rotations=rot,
+                          n_temporal=nt)
+    assert torch.equal(got, want)
+    missing = torch.zeros((1,), dtype=torch.int32, device=dev())
+    src = pool[1].data_ptr() + slot_of * page_stride
+    absent_id = int(ids_l[0, 0, 0])
+    src[absent_id] = 0
+    build_records_device(ids_l, src, dst=got[1], rotate=False, missing=missing, **lc)
+    assert int(missing.item()) == int((ids_l == absent_id).sum().item())

@@ -74,6 +74,9 @@ SIGNATURES = {
     "wa_hsa_status": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
     "wa_hkv_page_centroids": [_T4P, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "wa_hkv_score_topk": [_vp, _vp, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp],
+    "wa_hkv_score_topk_layers": [_vp, _vp, _i, _i, _i, _i, C.c_longlong, _f, _i, _vp, _vp, _vp, _vp],
+    "wa_hkv_build_records": [_vp, _i, _i, _i, _vp, _i, C.c_longlong, C.c_longlong, _vp, C.c_longlong, C.c_longlong,
+                             _i, _i, _i, _i, _vp, _vp, _vp],
     "wa_hkv_gather_pages": [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
 }
 _RESTYPES = {"wa_last_error": C.c_char_p, "wa_hsa_workspace_bytes": C.c_size_t,

@@ -89,10 +89,18 @@ __device__ __forceinline__ unsigned long long rank_key(float s, int id) {
 __global__ void __launch_bounds__(ST_THREADS)
 score_topk_kernel(const float *__restrict__ page_index, const float *__restrict__ query, int P, int G, int Dg,
                   float scale, int topk, float *__restrict__ scores, int32_t *__restrict__ top_ids,
-                  float *__restrict__ top_scores) {
+                  float *__restrict__ top_scores, long long query_layer_stride) {
     __shared__ unsigned long long red[ST_THREADS / 32];
     __shared__ unsigned long long prev_s;
     const int g = blockIdx.x;
+    {   // blockIdx.y: one page index per layer (`[layers, P, G*Dg]`), outputs `[layers, G, ...]`
+        const long long l = blockIdx.y;
+        page_index += l * P * G * Dg;
+        query += l * query_layer_stride;
+        scores += l * G * P;
+        if (top_ids) top_ids += l * G * topk;
+        if (top_scores) top_scores += l * G * topk;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float *q = query + (long long)g * Dg;
     float *sc = scores + (long long)g * P;
@@ -280,7 +288,98 @@ extern "C" int wa_hkv_score_topk(const float *page_index, const float *query, in
     WA_REQUIRE(topk <= 0 || (top_ids && top_scores), WA_ERR_ARG, "%s: top-k outputs are null", what);
     WA_REQUIRE(P > 0 && G > 0 && Dg > 0, WA_ERR_ARG, "%s: sizes must be positive", what);
     score_topk_kernel<<<G, ST_THREADS, 0, (cudaStream_t)stream>>>(page_index, query, P, G, Dg, scale, topk, scores,
-                                                                  top_ids, top_scores);
+                                                                  top_ids, top_scores, 0);
+    return check_launch(what);
+}
+
+extern "C" int wa_hkv_score_topk_layers(const float *page_index, const float *query, int layers, int P, int G, int Dg,
+                                        long long query_layer_stride, float scale, int topk, float *scores,
+                                        int32_t *top_ids, float *top_scores, void *stream) {
+    const char *what = "wa_hkv_score_topk_layers";
+    WA_REQUIRE(page_index && query && scores, WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(topk <= 0 || (top_ids && top_scores), WA_ERR_ARG, "%s: top-k outputs are null", what);
+    WA_REQUIRE(layers > 0 && P > 0 && G > 0 && Dg > 0, WA_ERR_ARG, "%s: sizes must be positive", what);
+    WA_REQUIRE(layers <= 65535, WA_ERR_UNSUPPORTED, "%s: at most 65535 layers", what);
+    score_topk_kernel<<<dim3(G, layers), ST_THREADS, 0, (cudaStream_t)stream>>>(page_index, query, P, G, Dg, scale, topk, scores,
+                                                                               top_ids, top_scores, query_layer_stride);
+    return check_launch(what);
+}
+
+namespace wa {
+// Copy records for the selected pages of every (layer, head) list, built where the ids are: one warp per list sorts
+// its ids (chronological = ascending page id; absent ids last) and writes `topk` records.
+__global__ void __launch_bounds__(128)
+build_records_kernel(const int32_t *__restrict__ top_ids, int n_lists, int heads, int topk, const long long *__restrict__ page_src,
+                     int P, long long src_layer_stride, long long src_token_stride, unsigned long long dst_base,
+                     long long dst_layer_stride, long long dst_token_stride, int page_tokens, int head_dim, int elem_size,
+                     int rotate, wa_page_copy *__restrict__ records, int32_t *__restrict__ missing) {
+    const int list = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (list >= n_lists) return;
+    const int layer = list / heads, head = list % heads;
+    // up to 64 ids per list: two keys per lane, bitonic sort across the warp (absent / out-of-range ids sort last)
+    unsigned int key[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = lane + 32 * u;
+        int id = r < topk ? top_ids[(long long)list * topk + r] : -1;
+        key[u] = (id >= 0 && id < P && page_src[id] != 0) ? (unsigned)id : 0xFFFFFFFFu;
+    }
+    for (int k = 2; k <= 64; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const unsigned int a0 = key[0], a1 = key[1];
+            // element i = lane + 32 u; its partner i ^ j is the lane's other register when j = 32
+            const unsigned int o0 = j == 32 ? a1 : __shfl_xor_sync(0xffffffffu, a0, j);
+            const unsigned int o1 = j == 32 ? a0 : __shfl_xor_sync(0xffffffffu, a1, j);
+            const bool min0 = ((lane & j) == 0) == ((lane & k) == 0);
+            const bool min1 = (((lane + 32) & j) == 0) == (((lane + 32) & k) == 0);
+            key[0] = (o0 < a0) == min0 ? o0 : a0;
+            key[1] = (o1 < a1) == min1 ? o1 : a1;
+        }
+    }
+    int absent = 0;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = lane + 32 * u;
+        if (r < topk) {
+            wa_page_copy rec;
+            const bool present = key[u] != 0xFFFFFFFFu;
+            const unsigned long long src = present ? (unsigned long long)page_src[key[u]] : 0ull;
+            rec.src = reinterpret_cast<const void *>(src + (unsigned long long)(layer * src_layer_stride) +
+                                                     (unsigned long long)head * head_dim * elem_size);
+            rec.dst = reinterpret_cast<void *>(dst_base + (unsigned long long)(layer * dst_layer_stride) +
+                                               ((unsigned long long)r * page_tokens * dst_token_stride + (unsigned long long)head * head_dim) *
+                                                   elem_size);
+            rec.src_stride = src_token_stride;
+            rec.dst_stride = dst_token_stride;
+            rec.n_tokens = present ? page_tokens : 0;
+            rec.rot = rotate ? r : -1;
+            records[(long long)list * topk + r] = rec;
+            absent += present ? 0 : 1;
+        }
+    }
+    if (missing) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) absent += __shfl_xor_sync(0xffffffffu, absent, o);
+        if (lane == 0 && absent) atomicAdd(missing, absent);
+    }
+}
+}  // namespace wa
+
+extern "C" int wa_hkv_build_records(const int32_t *top_ids, int layers, int heads, int topk, const long long *page_src, int P,
+                                    long long src_layer_stride, long long src_token_stride, void *dst_base,
+                                    long long dst_layer_stride, long long dst_token_stride, int page_tokens, int head_dim,
+                                    int elem_size, int rotate, wa_page_copy *records, int32_t *missing, void *stream) {
+    const char *what = "wa_hkv_build_records";
+    WA_REQUIRE(top_ids && page_src && dst_base && records, WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(layers > 0 && heads > 0 && topk > 0 && P > 0 && page_tokens > 0 && head_dim > 0, WA_ERR_ARG,
+               "%s: sizes must be positive", what);
+    WA_REQUIRE(topk <= 64, WA_ERR_UNSUPPORTED, "%s: at most 64 pages per list, got %d", what, topk);
+    WA_REQUIRE(elem_size == 2 || elem_size == 4, WA_ERR_ARG, "%s: element size must be 2 or 4", what);
+    const long long n_lists = (long long)layers * heads;
+    WA_REQUIRE(n_lists < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: too many lists", what);
+    wa::build_records_kernel<<<(unsigned)((n_lists + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
+        top_ids, (int)n_lists, heads, topk, page_src, P, src_layer_stride, src_token_stride, (unsigned long long)dst_base,
+        dst_layer_stride, dst_token_stride, page_tokens, head_dim, elem_size, rotate, records, missing);
     return check_launch(what);
 }
 

@@ -48,6 +48,42 @@ def per_head_records(page_ids: np.ndarray, *, src_base: int, src_page_stride: in
     return rec.reshape(-1)
 
 
+def build_records_device(top_ids: torch.Tensor, page_src: torch.Tensor, *, src_layer_stride: int, src_token_stride: int,
+                         dst: torch.Tensor, dst_layer_stride: int, dst_token_stride: int, page_tokens: int,
+                         head_dim: int, rotate: bool, missing: torch.Tensor | None = None) -> torch.Tensor:
+    """Copy records for a per-head retrieval, built on the device from the device-resident top-k ids.
+
+    `top_ids` int32 `[layers, heads, k]` (as `score_and_topk_layers` returns them), `page_src` int64 `[P]` device
+    addresses of the pages' first tokens (layer 0, head 0; 0 = not resident).  Per (layer, head) the pages are
+    installed in ascending id (chronological) order into consecutive `page_tokens`-row slots of `dst`
+    (`[layers, capacity, heads, head_dim]`-like, strides given).  Returns the records as a uint8 device tensor
+    for `gather_pages(..., records_dev=...)`; nothing crosses to the host.
+    """
+    dev = _lib.require_cuda(top_ids, page_src, dst)
+    layers, heads, k = top_ids.shape
+    ids = top_ids.to(torch.int32).contiguous()
+    src = page_src.to(torch.int64).contiguous()
+    records = torch.empty((layers * heads * k * RECORD_DTYPE.itemsize,), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.lib().wa_hkv_build_records(
+        ids.data_ptr(), layers, heads, k, src.data_ptr(), src.shape[0], int(src_layer_stride), int(src_token_stride),
+        dst.data_ptr(), int(dst_layer_stride), int(dst_token_stride), int(page_tokens), int(head_dim), dst.element_size(),
+        1 if rotate else 0, records.data_ptr(), _lib.ptr(missing), _lib.stream_ptr(dev)))
+    return records
+
+
+def gather_records_device(records_dev: torch.Tensor, *, max_tokens: int, row_elems: int, head_dim: int, dtype: torch.dtype,
+                          rotations: torch.Tensor | None = None, n_temporal: int = 0) -> None:
+    """Run the page-copy kernel over records that already live on the device (`build_records_device`)."""
+    n = records_dev.numel() // RECORD_DTYPE.itemsize
+    lib = _lib.lib()
+    base = records_dev.data_ptr()
+    for start in range(0, n, 65535):
+        count = min(65535, n - start)
+        _lib.check(lib.wa_hkv_gather_pages(base + start * RECORD_DTYPE.itemsize, count, max_tokens, row_elems, head_dim,
+                                           _lib.dtype_code(dtype), _lib.ptr(rotations), n_temporal,
+                                           _lib.stream_ptr(records_dev.device)))
+
+
 def gather_pages(records: np.ndarray, *, max_tokens: int, row_elems: int, head_dim: int, dtype: torch.dtype,
                  device: torch.device, rotations: torch.Tensor | None = None, n_temporal: int = 0,
                  records_dev: torch.Tensor | None = None) -> torch.Tensor:

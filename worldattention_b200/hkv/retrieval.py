@@ -82,6 +82,34 @@ def score_and_topk(query_vec: torch.Tensor, page_index: torch.Tensor, topk: int,
     return scores, ids[:, :k], vals[:, :k]
 
 
+def score_and_topk_layers(query_vec: torch.Tensor, page_index: torch.Tensor, topk: int, *, groups: int = 1,
+                          scale: Optional[float] = None):
+    """`score_and_topk` for a stack of page indexes `[layers, P, dim]` in ONE launch (no host loop).
+
+    `query_vec` is `[dim]` (shared by the layers) or `[layers, dim]`.  Returns scores `[layers, G, P]` and
+    top-k ids / scores `[layers, G, topk]`, all on the device.
+    """
+    dev = _lib.require_cuda(page_index)
+    layers, pages, dim = page_index.shape
+    if dim % groups:
+        raise ValueError(f"index dim {dim} is not divisible into {groups} groups")
+    index = page_index.float().contiguous()
+    query = query_vec.to(device=dev, dtype=torch.float32).contiguous()
+    if tuple(query.shape) not in ((dim,), (layers, dim)):
+        raise ValueError(f"query must be [{dim}] or [{layers}, {dim}], got {tuple(query.shape)}")
+    stride = dim if query.dim() == 2 else 0
+    if scale is None:
+        scale = float(dim // groups) ** 0.5
+    k = max(0, min(int(topk), pages))
+    scores = torch.empty((layers, groups, pages), device=dev, dtype=torch.float32)
+    ids = torch.empty((layers, groups, max(k, 1)), device=dev, dtype=torch.int32)
+    vals = torch.empty((layers, groups, max(k, 1)), device=dev, dtype=torch.float32)
+    _lib.check(_lib.lib().wa_hkv_score_topk_layers(
+        index.data_ptr(), query.data_ptr(), layers, pages, groups, dim // groups, stride, float(scale or 0.0), k,
+        scores.data_ptr(), ids.data_ptr(), vals.data_ptr(), _lib.stream_ptr(dev)))
+    return scores, ids[..., :k], vals[..., :k]
+
+
 def score_pages(query_vec: torch.Tensor, page_index: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
     """Affinity `alpha_j = (Qbar . Kbar_j) / sqrt(dim)` for every page (retrieval.py:75-89)."""
     if page_index.numel() == 0:
