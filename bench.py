@@ -501,6 +501,37 @@ def main():
     total_ms = float(total_ms.item())
     ms_per_step = total_ms / args.steps
 
+    # ---- KV-sharded runs: the head split on the same ranks, for comparison (extra, not the headline) ------------------
+    head_split_alt = None
+    if mode == "kv" and HEADS >= world:
+        plan_a = sharded.plan_head_split(HEADS, world, topk_all.tolist())
+        mine_a = plan_a[rank]
+        qa, ka, va = (x[:, :, mine_a].contiguous() for x in (q, k, v))
+        with torch.no_grad():
+            kca, vca = hsa.compress_kv_cache(ka, va)
+        topk_a = topk_all[mine_a].to(dev)
+
+        def forward_alt():
+            with torch.no_grad():
+                return wa.hsa.hsa_attention(qa, ka, va, k_coarse=kca, v_coarse=vca, k_proj_mat=hsa.k_proj_mat,
+                                            v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=block,
+                                            proj_segment_len=FRAME_TOKENS, topk_per_head=topk_a)
+        alt_ms = []
+        barrier()
+        for it in range(3 + min(args.steps, 30)):
+            flush_l2()
+            ev0.record()
+            forward_alt()
+            ev1.record()
+            ev1.synchronize()
+            if it >= 3:
+                alt_ms.append(ev0.elapsed_time(ev1))
+        alt_total = torch.tensor([float(np.mean(alt_ms))], dtype=torch.float64, device=dev)
+        dist.all_reduce(alt_total, op=dist.ReduceOp.MAX)
+        head_split_alt = {"sharding": "head-split, uneven (longest-processing-time on the per-head top-k), no collective",
+                          "heads_per_rank": [len(x) for x in plan_a], "ms_per_step": float(alt_total.item())}
+        del qa, ka, va, kca, vca
+
     # ---- the same step with the pooled keys of the cached frames kept by the caller (extra, not the headline) -------
     # In the causal pipeline only the chunk's own rows of the key cache change between forwards; the block means of
     # the older frames can stay resident next to the compressed cache, and the call then pools the new blocks only.
@@ -660,6 +691,7 @@ def main():
                 "equals_single_call": e2e_same},
         "gpu_launches": int(launches),
         "pooled_key_cache": pooled_cache,
+        "head_split_on_the_same_ranks": head_split_alt,
         "clocks": clocks,
         "wall_s": wall,
     }
