@@ -136,10 +136,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
+// Non-blocking test of a barrier phase.
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false after the abort flag is raised or the time budget is spent.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *error_flag,
                                           int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test(bar, parity)) return true;   // the common case: the phase is over already
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
