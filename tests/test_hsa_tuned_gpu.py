@@ -193,13 +193,11 @@ def test_head_slices_of_a_resident_cache_equal_the_full_call(wa):
         assert torch.equal(part, full[:, :, hs])
 
 
-def test_64_token_blocks_take_the_tcgen05_kernel_for_the_linear_branch(wa):
-    """Routing block size 64 (the reference class's default): the sparse branch runs on the SIMT kernel, the linear
-    branch on the tcgen05 kernel; the result matches the oracle and the all-SIMT path."""
-    heads, q_len, kv_len, seg, bs = 3, 500, 2100, 700, 64
-    rng = np.random.default_rng(21)
-    q = _draw(rng, (1, q_len, heads, D), 0.3)
-    k = _draw(rng, (1, kv_len, heads, D), 0.3)
+def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3):
+    bs = 64
+    rng = np.random.default_rng(seed)
+    q = _draw(rng, (1, q_len, heads, D), scale)
+    k = _draw(rng, (1, kv_len, heads, D), scale)
     v = _draw(rng, (1, kv_len, heads, D), 1.0)
     ek = _proj(math.ceil(seg / bs), seg, bs, rng)
     gw = (rng.standard_normal((D, D)) * 0.05).astype(np.float32)
@@ -207,23 +205,33 @@ def test_64_token_blocks_take_the_tcgen05_kernel_for_the_linear_branch(wa):
     lin = torch.nn.Linear(D, D).to(dev())
     with torch.no_grad():
         lin.weight.copy_(to_gpu(gw)); lin.bias.copy_(to_gpu(gb))
-    topk = [5, 12, 0]
+    tk = None if topk is None else torch.tensor(topk, dtype=torch.int32)
     kwargs = dict(k_proj_mat=to_gpu(ek, "bf16"), v_proj_mat=to_gpu(ek, "bf16"), gate_lin=lin, block_size=bs,
-                  proj_segment_len=seg, topk_per_head=torch.tensor(topk, dtype=torch.int32), return_routing=True)
+                  proj_segment_len=seg, topk_per_head=tk, return_routing=True)
     args = [to_gpu(x, "bf16") for x in (q, k, v)]
-    launches0 = wa._lib.lib().wa_launch_count()
     out, (index, num, _, used) = wa.hsa.hsa_attention(*args, check_status=True, **kwargs)
-    launches_hybrid = wa._lib.lib().wa_launch_count() - launches0
-    ref, (index_g, num_g, _, _) = wa.hsa.hsa_attention(*args, force_generic=True, **kwargs)
-    assert not used                                   # the fused kernel itself needs 128-token blocks
+    ref, (index_g, num_g, _, used_g) = wa.hsa.hsa_attention(*args, force_generic=True, **kwargs)
+    assert used and not used_g
     assert torch.equal(index, index_g) and torch.equal(num, num_g)
-    want = O.hsa_attention(q, k, v, k_proj_mat=ek, v_proj_mat=ek, gate_weight=gw, gate_bias=gb, block_size=bs,
+    want = O.hsa_attention(q, k, v, k_proj_mat=ek, v_proj_mat=ek, gate_weight=O.bf16_round(gw), gate_bias=gb, block_size=bs,
                            proj_segment_len=seg, dtype="bf16", topk_per_head=topk)
     max_abs, mean_rel = attention_error(to_np(out), want)
     assert max_abs < MAX_ABS and mean_rel < MEAN_REL, ("vs oracle", max_abs, mean_rel)
     max_abs_g, mean_rel_g = attention_error(to_np(out), to_np(ref))
     assert max_abs_g < MAX_ABS and mean_rel_g < MEAN_REL, ("vs generic", max_abs_g, mean_rel_g)
-    assert launches_hybrid >= 6                       # pooling, routing, compress, sparse, schedule + tcgen05 linear, combine
+
+
+def test_64_token_blocks_run_on_the_tcgen05_kernel(wa):
+    """Routing block size 64 (the reference class's default): a work item is a 64-row query block and a key tile holds
+    two selected blocks.  Odd and even counts, an empty head, ragged query and key tails."""
+    _run_case_64(wa, seed=21, heads=3, q_len=500, kv_len=2100, seg=700, topk=[5, 12, 0])
+
+
+def test_64_token_blocks_with_the_ragged_last_key_block_anywhere_in_the_list(wa):
+    """Every key block selected (33 blocks, the last one 40 tokens): the short block sits wherever the routing order puts
+    it, in the first or the second half of a tile; cumulative-mass routing for the second case."""
+    _run_case_64(wa, seed=22, heads=2, q_len=200, kv_len=2088, seg=696, topk=[33, 32])
+    _run_case_64(wa, seed=23, heads=2, q_len=130, kv_len=1000, seg=500, topk=None, scale=0.5)
 
 
 def test_pooled_key_cache_gives_the_same_result_and_only_pools_new_blocks(wa):

@@ -189,7 +189,7 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
     const int lin_dtype = vc.dtype;
     const bool tuned = !(p->flags & WA_HSA_FORCE_GENERIC) && hsa_sm100_supported(p, Lc, &kc, &vc);
     WA_REQUIRE(tuned || !(p->flags & WA_HSA_REQUIRE_TUNED), WA_ERR_UNSUPPORTED,
-               "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 128)", what);
+               "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 64 or 128)", what);
 
     bool prepared = false;
     if (p->index_in) {

@@ -92,6 +92,8 @@ __device__ __forceinline__ unsigned wa_smid() {
 
 struct Params {
     int B, H, Lq, Lkv, Lc, Nq, Nkv;
+    int blk;       // routing block size: 128, or 64 (a work item is then a 64-row query block in a 128-row tile whose
+                   // upper rows are computed and dropped, and a key tile holds two selected 64-token blocks)
     int n_items;
     const int32_t *index;   // [B,H,Nq,Nkv]
     const int32_t *num;     // [B,H,Nq]
@@ -382,6 +384,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget exceeded");
 // The three roles run their own loops over work items and meet only at mbarriers, so the producer
 // prefetches the next item's Q/K/V and the MMA warp starts its first products while the softmax
 // warps are still in the previous item's epilogue.
+template <int BLK>   // routing block size: 128, or 64 (see Params::blk)
 __global__ void __launch_bounds__(THREADS, 1)
 hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
@@ -459,14 +462,16 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     item = p.order[at];
                     n_sel = max(0, min(p.num[item], p.Nkv));
                 }
+                // the other roles count sparse TILES: with 64-token blocks a tile holds two selected blocks
+                const int n_st = BLK == TILE ? n_sel : (n_sel + 1) >> 1;
                 bar->items[slot].item = item;
-                bar->items[slot].n_sel = n_sel;
+                bar->items[slot].n_sel = n_st;
                 mbar_arrive(&bar->item_full[slot]);
                 if (item < 0) break;
                 at = (int)gridDim.x + atomicAdd(p.work_counter, 1);   // consumed at the top of the next round
                 const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
                 const int32_t *ids = p.index + (long long)item * p.Nkv;
-                const int n_kv = n_sel + lin_tiles;
+                const int n_kv = n_st + lin_tiles;
                 WA_STATS_ITEM(n_kv + 1);
 
                 const uint32_t qs = jcount % Q_STAGES;
@@ -474,28 +479,46 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (!ok) break;
                 uint8_t *qdst = q_s + qs * TILE_BYTES;
                 mbar_expect_tx(&bar->q_full[qs], TILE_BYTES);
-                tma_load_4d(qdst, &tm_q, &bar->q_full[qs], 0, h, qb * TILE, b);
-                tma_load_4d(qdst + HALF_BYTES, &tm_q, &bar->q_full[qs], 64, h, qb * TILE, b);
+                tma_load_4d(qdst, &tm_q, &bar->q_full[qs], 0, h, qb * BLK, b);
+                tma_load_4d(qdst + HALF_BYTES, &tm_q, &bar->q_full[qs], 64, h, qb * BLK, b);
 
                 for (int t = 0; t <= n_kv && ok; ++t) {
                     const uint32_t ks = kcount % KV_STAGES, kpar = ((kcount / KV_STAGES) & 1u) ^ 1u;
                     ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, p.error_flag, 1);
                     if (!ok) break;
                     uint8_t *kdst = k_s + ks * TILE_BYTES;
-                    int id = 0;
-                    if (t < n_sel) {
-                        id = max(0, min(ids[t], p.Nkv - 1));
-                        bar->valid[kcount & 7] = min(TILE, p.Lkv - id * TILE);
+                    // real tokens of the tile: low byte = of its first 64 keys, next byte = of its last 64
+                    int id = 0, id2 = 0, valid = 0;
+                    if (t < n_st) {
+                        if (BLK == TILE) {
+                            id = max(0, min(ids[t], p.Nkv - 1));
+                            const int n = min(TILE, p.Lkv - id * TILE);
+                            valid = min(n, HALF) | (max(0, n - HALF) << 8);
+                        } else {   // two 64-token blocks; a missing second block repeats the first and is masked out
+                            id = max(0, min(ids[2 * t], p.Nkv - 1));
+                            const bool two = 2 * t + 1 < n_sel;
+                            id2 = two ? max(0, min(ids[2 * t + 1], p.Nkv - 1)) : id;
+                            valid = min(HALF, p.Lkv - id * HALF) | ((two ? min(HALF, p.Lkv - id2 * HALF) : 0) << 8);
+                        }
                     } else {
-                        bar->valid[kcount & 7] = min(TILE, p.Lc - (t - n_sel) * TILE);
+                        const int n = max(0, min(TILE, p.Lc - (t - n_st) * TILE));
+                        valid = min(n, HALF) | (max(0, n - HALF) << 8);
                     }
+                    bar->valid[kcount & 7] = valid;
                     ++kcount;
                     mbar_expect_tx(&bar->k_full[ks], TILE_BYTES);
-                    if (t < n_sel) {
-                        tma_load_4d(kdst, &tm_k, &bar->k_full[ks], 0, h, id * TILE, b);
-                        tma_load_4d(kdst + HALF_BYTES, &tm_k, &bar->k_full[ks], 64, h, id * TILE, b);
+                    if (t < n_st) {
+                        if (BLK == TILE) {
+                            tma_load_4d(kdst, &tm_k, &bar->k_full[ks], 0, h, id * TILE, b);
+                            tma_load_4d(kdst + HALF_BYTES, &tm_k, &bar->k_full[ks], 64, h, id * TILE, b);
+                        } else {   // 64-row boxes: rows 0..63 of each half-tile from the first block, 64..127 from the second
+                            tma_load_4d(kdst, &tm_k, &bar->k_full[ks], 0, h, id * HALF, b);
+                            tma_load_4d(kdst + HALF_BYTES / 2, &tm_k, &bar->k_full[ks], 0, h, id2 * HALF, b);
+                            tma_load_4d(kdst + HALF_BYTES, &tm_k, &bar->k_full[ks], 64, h, id * HALF, b);
+                            tma_load_4d(kdst + HALF_BYTES + HALF_BYTES / 2, &tm_k, &bar->k_full[ks], 64, h, id2 * HALF, b);
+                        }
                     } else if (t < n_kv) {
-                        const int c = (t - n_sel) * TILE;
+                        const int c = (t - n_st) * TILE;
                         tma_load_4d(kdst, &tm_kc, &bar->k_full[ks], 0, h, c, b);
                         tma_load_4d(kdst + HALF_BYTES, &tm_kc, &bar->k_full[ks], 64, h, c, b);
                     } else {
@@ -509,11 +532,18 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         ++vcount;
                         uint8_t *vdst = v_s + vs * TILE_BYTES;
                         mbar_expect_tx(&bar->v_full[vs], TILE_BYTES);
-                        if (t < n_sel) {
-                            tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * TILE, b);
-                            tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * TILE, b);
+                        if (t < n_st) {
+                            if (BLK == TILE) {
+                                tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * TILE, b);
+                                tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * TILE, b);
+                            } else {
+                                tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * HALF, b);
+                                tma_load_4d(vdst + HALF_BYTES / 2, &tm_v, &bar->v_full[vs], 0, h, id2 * HALF, b);
+                                tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * HALF, b);
+                                tma_load_4d(vdst + HALF_BYTES + HALF_BYTES / 2, &tm_v, &bar->v_full[vs], 64, h, id2 * HALF, b);
+                            }
                         } else {
-                            const int c = (t - n_sel) * TILE;
+                            const int c = (t - n_st) * TILE;
                             tma_load_4d(vdst, &tm_vc, &bar->v_full[vs], 0, h, c, b);
                             tma_load_4d(vdst + HALF_BYTES, &tm_vc, &bar->v_full[vs], 64, h, c, b);
                         }
@@ -655,8 +685,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (!ok) break;
                 if (!p.part_linear) {
                     // rows beyond q_len are clipped by the tensor map
-                    tma_store_4d(&tm_out, q_s + qs * TILE_BYTES, 0, h, qb * TILE, b);
-                    tma_store_4d(&tm_out, q_s + qs * TILE_BYTES + HALF_BYTES, 64, h, qb * TILE, b);
+                    // (with 64-token blocks the map's box is 64 rows: the tile's upper rows belong to the next item)
+                    tma_store_4d(&tm_out, q_s + qs * TILE_BYTES, 0, h, qb * BLK, b);
+                    tma_store_4d(&tm_out, q_s + qs * TILE_BYTES + HALF_BYTES, 64, h, qb * BLK, b);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the Q stage is reusable afterwards
                 }
@@ -696,8 +727,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const int n_kv = n_sel + lin_tiles;
             const uint32_t qs = jcount % Q_STAGES;
             uint8_t *q_stage = q_s + qs * TILE_BYTES;
-            const int tokenA = qb * TILE + rowA, tokenB = tokenA + 8;
-            const bool okA = tokenA < p.Lq, okB = tokenB < p.Lq;
+            const int tokenA = qb * BLK + rowA, tokenB = tokenA + 8;
+            const bool okA = rowA < BLK && tokenA < p.Lq, okB = rowB < BLK && tokenB < p.Lq;
             // float32 offsets of this thread's first column pair in the partial outputs, and of the rows' normalisers
             const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * TILE + 2 * c2;
             const long long partB = partA + 8ll * p.H * TILE;
@@ -716,12 +747,17 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (!ok) break;
                     WA_TRACE(2);
                     tc_fence_after();
-                    const int valid = min(TILE, bar->valid[(sg + t) & 7]);   // real tokens in the tile (the producer wrote the count)
+                    // real tokens of the tile's first and last 64 keys (the producer wrote the counts); key column c is real
+                    // when c < v0 (c < 64) or c - 64 < v1: per 8-column step j that is c < lim(j)
+                    const int vword = bar->valid[(sg + t) & 7];
+                    const int v0 = vword & 0xff, v1 = (vword >> 8) & 0xff;
+                    const bool full = vword == (HALF | (HALF << 8));
+                    const int lim_lo = v0, lim_hi = HALF + v1;
                     uint32_t r[64];
                     TMEM_LDQ64(s_addr, r);
                     tmem_wait_ld();
                     float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
-                    if (valid == TILE) {
+                    if (full) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             xa0 = fmaxf(xa0, __uint_as_float(r[4 * j]));
@@ -732,12 +768,12 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     } else {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const int col = 8 * j + 2 * c2;
-                            if (col < valid) {
+                            const int col = 8 * j + 2 * c2, lim = j < 8 ? lim_lo : lim_hi;
+                            if (col < lim) {
                                 xa0 = fmaxf(xa0, __uint_as_float(r[4 * j]));
                                 xb0 = fmaxf(xb0, __uint_as_float(r[4 * j + 2]));
                             }
-                            if (col + 1 < valid) {
+                            if (col + 1 < lim) {
                                 xa1 = fmaxf(xa1, __uint_as_float(r[4 * j + 1]));
                                 xb1 = fmaxf(xb1, __uint_as_float(r[4 * j + 3]));
                             }
@@ -781,7 +817,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     uint32_t pk[32];
                     const float2 nmA = make_float2(-mA, -mA), nmB = make_float2(-mB, -mB);
                     float2 accA = make_float2(0.f, 0.f), accB = make_float2(0.f, 0.f);
-                    if (valid == TILE) {
+                    if (full) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             if (j % POLY_EVERY == 0)
@@ -795,9 +831,10 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         // ragged tile (the last one of a branch): 8-column steps without a real token cost nothing
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            if (8 * j < valid)
+                            const int lim = j < 8 ? lim_lo : lim_hi;
+                            if (8 * j < lim)
                                 exp_step<false, true>(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3], sc, nmA, nmB, accA, accB,
-                                                      pk[2 * j], pk[2 * j + 1], 8 * j + 2 * c2, valid);
+                                                      pk[2 * j], pk[2 * j + 1], 8 * j + 2 * c2, lim);
                             else
                                 pk[2 * j] = pk[2 * j + 1] = 0u;
                         }
@@ -1027,14 +1064,14 @@ static EncodeTiledFn encode_fn() {
 }
 
 // `[B, L, H, 128]` bf16 view -> 4-D map (d, h, token, batch), box 64 x 1 x 128 x 1, 128-byte swizzle.
-static int make_map_4d(CUtensorMap *map, const wa_tensor4 *t, int B, int L, int H, const char *name) {
+static int make_map_4d(CUtensorMap *map, const wa_tensor4 *t, int B, int L, int H, const char *name, int box_rows = TILE) {
     EncodeTiledFn fn = encode_fn();
     WA_REQUIRE(fn, WA_ERR_DEVICE, "tcgen05 path: cuTensorMapEncodeTiled is unavailable");
     cuuint64_t dims[4] = {(cuuint64_t)TILE, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)B};
     cuuint64_t strides[3] = {(cuuint64_t)t->stride_h * 2, (cuuint64_t)t->stride_l * 2, (cuuint64_t)t->stride_b * 2};
     if (B == 1) strides[2] = strides[1] * (cuuint64_t)L;   // unused extent: any legal stride
     if (H == 1) strides[0] = 256;
-    cuuint32_t box[4] = {64, 1, (cuuint32_t)TILE, 1};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
     cuuint32_t elem[4] = {1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t->ptr, dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1077,7 +1114,7 @@ struct TunedWs {
 static TunedWs tuned_plan(const wa_hsa_params *p) {
     TunedWs w{};
     size_t c = 0;
-    const size_t items = (size_t)p->B * p->H * ceil_div(p->Lq, TILE);
+    const size_t items = (size_t)p->B * p->H * ceil_div(p->Lq, p->block_size < TILE ? p->block_size : TILE);
     w.order = c; c = align_up(c + items * sizeof(int32_t), 256);
     w.counter = c; c = align_up(c + 2 * sizeof(int), 256);
     w.w_bf16 = c; c = align_up(c + (size_t)TILE * TILE * 2, 256);
@@ -1141,13 +1178,13 @@ static bool device_is_sm100() {
 
 bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc) {
     using namespace sm100;
-    if (p->D != TILE || p->block_size != TILE || Lc <= 0) return false;
+    if (p->D != TILE || (p->block_size != TILE && p->block_size != HALF) || Lc <= 0) return false;
     if (!view_ok(&p->q) || !view_ok(&p->k) || !view_ok(&p->v) || !view_ok(kc) || !view_ok(vc)) return false;
     if (!p->part_sparse && (p->out.dtype != WA_BF16 || !p->out.ptr || (uintptr_t)p->out.ptr % 16 || p->out.stride_h % 8 ||
                             p->out.stride_l % 8 || p->out.stride_b % 8))
         return false;
     if (p->part_sparse && (((uintptr_t)p->part_sparse | (uintptr_t)p->part_linear) % 16)) return false;
-    if ((long long)p->B * p->H * ceil_div(p->Lq, TILE) > (1 << 24)) return false;
+    if ((long long)p->B * p->H * ceil_div(p->Lq, p->block_size) > (1 << 24)) return false;
     return device_is_sm100() && encode_fn() != nullptr;
 }
 
@@ -1163,12 +1200,13 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     CUtensorMap tq, tk, tv, tkc, tvc, tw, tout;
     int rc;
     if ((rc = make_map_4d(&tq, &p->q, p->B, p->Lq, p->H, "q"))) return rc;
-    if ((rc = make_map_4d(&tk, &p->k, p->B, p->Lkv, p->H, "k"))) return rc;
-    if ((rc = make_map_4d(&tv, &p->v, p->B, p->Lkv, p->H, "v"))) return rc;
+    const int blk = p->block_size == HALF ? HALF : TILE;   // the linear-branch-only launch (other sizes) never loads k / v
+    if ((rc = make_map_4d(&tk, &p->k, p->B, p->Lkv, p->H, "k", blk))) return rc;
+    if ((rc = make_map_4d(&tv, &p->v, p->B, p->Lkv, p->H, "v", blk))) return rc;
     if ((rc = make_map_4d(&tkc, kc, p->B, Lc, p->H, "k_coarse"))) return rc;
     if ((rc = make_map_4d(&tvc, vc, p->B, Lc, p->H, "v_coarse"))) return rc;
     if ((rc = make_map_w(&tw, w_bf16))) return rc;
-    if ((rc = make_map_4d(&tout, p->part_sparse ? &p->q : &p->out, p->B, p->Lq, p->H, "out"))) return rc;   // unused in partial mode
+    if ((rc = make_map_4d(&tout, p->part_sparse ? &p->q : &p->out, p->B, p->Lq, p->H, "out", blk))) return rc;   // unused in partial mode
 
     const int n_items = p->B * p->H * Nq;
     if (!prepared) {
@@ -1179,6 +1217,7 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     Params kp{};
     kp.B = p->B; kp.H = p->H; kp.Lq = p->Lq; kp.Lkv = p->Lkv; kp.Lc = Lc; kp.Nq = Nq; kp.Nkv = Nkv;
     kp.n_items = n_items;
+    kp.blk = blk;
     kp.index = index; kp.num = num; kp.order = order; kp.work_counter = counter; kp.error_flag = counter + 1;
     kp.out = (__nv_bfloat16 *)p->out.ptr; kp.osb = p->out.stride_b; kp.osl = p->out.stride_l; kp.osh = p->out.stride_h;
     kp.gate_bias = bias; kp.has_gate = p->gate_w != nullptr;
@@ -1190,7 +1229,9 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
 
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
         attr_set = true;
     }
@@ -1199,7 +1240,8 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     if (getenv("WA_SM100_ONE_CTA") && grid > max_grid() / 2) grid = max_grid() / 2;   // tuning aid: one CTA per SM
 #endif
     profile_mark(true, stream);
-    hsa_fwd_sm100_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
+    if (blk == TILE) hsa_fwd_sm100_kernel<TILE><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
+    else hsa_fwd_sm100_kernel<HALF><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     profile_mark(false, stream);
     return check_launch("wa_hsa_forward(tcgen05)");
 }
