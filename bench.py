@@ -237,7 +237,7 @@ def workload_config(name, n_gpus, mode=None):
 
 
 # ------------------------------------------------------------------------------------------------
-# HKV retrieval (BASELINE config 3): per-head page scoring, top-16, gather from the HBM-hot pool
+# HKV retrieval (benchmark config 3): per-head page scoring, top-16, gather from the HBM-hot pool
 # ------------------------------------------------------------------------------------------------
 def bench_hkv(dev, steps=5, layers=30, pages_total=480, pages_hot=64, topk=16):
     """Score 480 page centroids per (layer, head), take the top-16 per head, gather those pages.
@@ -350,7 +350,7 @@ def main():
     ap.add_argument("--force-generic", action="store_true")
     ap.add_argument("--no-hkv", action="store_true")
     ap.add_argument("--hkv-only", action="store_true", help="run only the HKV retrieval measurement (one GPU)")
-    ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the HKV measurement (30 = BASELINE config 3)")
+    ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the HKV measurement (30 = benchmark config 3)")
     ap.add_argument("--shard", default="auto", choices=["auto", "heads", "kv"], help="sharding for --gpus > 1")
     ap.add_argument("--gather-heads", action="store_true",
                     help="head split: also all-gather the outputs (off: they stay head-sharded for a head-parallel consumer)")

@@ -39,7 +39,8 @@ def _np(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("WORLDATTENTION_REFERENCE"), required="WORLDATTENTION_REFERENCE" not in os.environ,
+                    help="checkout of alibaba-damo-academy/WorldAttention (or set WORLDATTENTION_REFERENCE)")
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     args = ap.parse_args()
     _stub_reference(args.reference)

@@ -265,7 +265,7 @@ def test_forward_generic_path_against_oracle(wa, dtype, bs, topk):
 
 
 def test_config1_shape_fp32(wa):
-    """BASELINE config 1: q = 1 frame (1560 tokens), KV = 3 frames, 12 heads x 128, block 64, top-8, seed 0."""
+    """Benchmark config 1: q = 1 frame (1560 tokens), KV = 3 frames, 12 heads x 128, block 64, top-8, seed 0."""
     heads, d, q_len, kv_len, bs, seg = 12, 128, 1560, 4680, 64, 1560
     q, k, v = _seeded_case(0, q_len, kv_len, heads, d, "fp32")
     ek = _block_average_proj(math.ceil(seg / bs), seg, bs)

@@ -1,7 +1,7 @@
 """The tcgen05 fused kernel (bf16, head_dim 128, 128-token blocks) against the oracle and the SIMT kernels.
 
 Routing ids/counts are produced by the same routing kernels on both paths and must be identical;
-outputs meet max-abs 2e-2 / mean-rel 1e-2 against the oracle (the tolerance BASELINE states) and
+outputs meet max-abs 2e-2 / mean-rel 1e-2 against the oracle (the tolerance the benchmark definition states) and
 are much closer to the library's own generic path.
 """
 import math
@@ -106,7 +106,7 @@ def test_large_logits_exercise_the_running_max_rescale(wa):
 
 
 def test_config2_shape_head_adaptive_topk(wa):
-    """BASELINE config 2 at full size: the property checked is agreement with the SIMT path of this library."""
+    """Benchmark config 2 at full size: the property checked is agreement with the SIMT path of this library."""
     heads, q_len, kv_len, seg = 12, 4680, 32760, 1560
     g = torch.Generator().manual_seed(1)
     topk = torch.tensor([4, 8, 16, 32])[torch.randint(0, 4, (heads,), generator=g)].to(torch.int32)
