@@ -35,6 +35,8 @@ FRAME_TOKENS = 1560
 WORKLOADS = {
     # name: (q frames, kv frames, block, top-k policy)
     "c2": dict(q_frames=3, kv_frames=21, block=128, topk="adaptive", seed=1, scale=1.0 / math.sqrt(HEAD_DIM)),
+    # config 2 with the reference class's default 64-token blocks and twice the block counts (the same selected tokens)
+    "c2-64": dict(q_frames=3, kv_frames=21, block=64, topk="adaptive-x2", seed=1, scale=1.0 / math.sqrt(HEAD_DIM)),
     "c5": dict(q_frames=3, kv_frames=480, block=64, topk=32, seed=4, scale=1.0),
     # the long-horizon cache with 128-token blocks (the shape the tcgen05 kernel covers); top-16 blocks = the same
     # 2048 selected tokens per query row as top-32 at 64-token blocks
@@ -50,9 +52,10 @@ NCU_TRAFFIC_BYTES = 168.0e6
 # workload construction (host side, seeded)
 # ------------------------------------------------------------------------------------------------
 def draw_topk(spec, heads=HEADS):
-    if spec["topk"] == "adaptive":
+    if spec["topk"] in ("adaptive", "adaptive-x2"):
         g = torch.Generator().manual_seed(spec["seed"])
-        return torch.tensor([4, 8, 16, 32])[torch.randint(0, 4, (heads,), generator=g)].to(torch.int32)
+        k = torch.tensor([4, 8, 16, 32])[torch.randint(0, 4, (heads,), generator=g)].to(torch.int32)
+        return k * 2 if spec["topk"] == "adaptive-x2" else k
     return torch.full((heads,), int(spec["topk"]), dtype=torch.int32)
 
 
