@@ -193,12 +193,12 @@ def test_head_slices_of_a_resident_cache_equal_the_full_call(wa):
         assert torch.equal(part, full[:, :, hs])
 
 
-def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3):
+def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3, bsz=1):
     bs = 64
     rng = np.random.default_rng(seed)
-    q = _draw(rng, (1, q_len, heads, D), scale)
-    k = _draw(rng, (1, kv_len, heads, D), scale)
-    v = _draw(rng, (1, kv_len, heads, D), 1.0)
+    q = _draw(rng, (bsz, q_len, heads, D), scale)
+    k = _draw(rng, (bsz, kv_len, heads, D), scale)
+    v = _draw(rng, (bsz, kv_len, heads, D), 1.0)
     ek = _proj(math.ceil(seg / bs), seg, bs, rng)
     gw = (rng.standard_normal((D, D)) * 0.05).astype(np.float32)
     gb = (rng.standard_normal((D,)) * 0.3).astype(np.float32)
@@ -225,6 +225,7 @@ def test_64_token_blocks_run_on_the_tcgen05_kernel(wa):
     """Routing block size 64 (the reference class's default): a work item is a 64-row query block and a key tile holds
     two selected blocks.  Odd and even counts, an empty head, ragged query and key tails."""
     _run_case_64(wa, seed=21, heads=3, q_len=500, kv_len=2100, seg=700, topk=[5, 12, 0])
+    _run_case_64(wa, seed=24, heads=2, q_len=150, kv_len=1400, seg=700, topk=[7, 2], bsz=2)
 
 
 def test_64_token_blocks_with_the_ragged_last_key_block_anywhere_in_the_list(wa):
