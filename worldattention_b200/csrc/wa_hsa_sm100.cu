@@ -3,17 +3,19 @@
 //
 // Replaces the reference's Triton `_fwd_kernel` (wan/modules/hsa/block_sparse_triton.py:67-139)
 // plus `_linear_branch` and the gate/addcmul epilogue (wan/modules/hsa/attention.py:113-118,
-// 246-259) for bf16, head_dim 128, 128-token blocks.
+// 246-259) for bf16, head_dim 128, 128- or 64-token routing blocks.
 //
-// Work item = (batch, head, 128-row query block).  Per item the CTA runs a chain of 128x128 tiles:
+// Work item = (batch, head, query block).  Per item the CTA runs a chain of 128x128 tiles:
 //   sparse:  for each selected key block   S = Q K^T -> online softmax -> O += P V
 //   linear:  for each 128 compressed slots  S = Q Kc^T -> online softmax -> O += P Vc
 //   gate:    S = Q Wg^T ; out = O_sparse/l_s + sigmoid(S + b) * O_linear/l_l
 // Data path: TMA (cp.async.bulk.tensor, 128-byte swizzle, one consumer CTA per copy) -> shared memory ->
 // tcgen05.mma with the S and O accumulators in tensor memory; P goes back to tensor memory as
-// bf16 and is the A operand of the PV product.  Warp 0 issues TMA, warp 1 issues MMA, warps 2-5
-// (one thread per query row) do softmax and the epilogue.  Two CTAs share an SM (256 tensor-memory
-// columns and ~97 KB shared memory each) so one CTA's softmax overlaps the other's MMAs.
+// bf16 and is the A operand of the PV product.  One persistent CTA of 12 warps per SM owns all 512
+// tensor-memory columns (three S buffers + O) and ~227 KB of shared memory (Q x2, K x3, V x2 tiles):
+// warps 0-7 do the softmax and the epilogue (a query row is shared by four lanes of one warp, a tile's
+// columns by two warps), warp 8 issues TMA loads, warp 9 the QK products, warp 11 the PV products and
+// warp 10 the TMA store of the finished tile.  Items are taken heaviest first from a global counter.
 //
 // Every mbarrier wait is bounded (about two seconds); on expiry the kernel raises a flag in
 // global memory, all roles leave their loops, tensor memory is released and the kernel returns.
