@@ -140,6 +140,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
     return ok != 0;
 }
+// Same with a caller-chosen sleep limit (for a thread that watches two barriers).
+__device__ __forceinline__ bool mbar_try_wait_ns(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 // Non-blocking test of a barrier phase.
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -484,10 +494,57 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 tma_load_4d(qdst, &tm_q, &bar->q_full[qs], 0, h, qb * BLK, b);
                 tma_load_4d(qdst + HALF_BYTES, &tm_q, &bar->q_full[qs], 64, h, qb * BLK, b);
 
+                // K tiles and V tiles advance on cursors of their own: the V ring is shallower and its stages come back
+                // later (after the PV product), and a K load that queued behind a V wait would reach the QK warp late.
+                int tv = 0;   // next V tile of this item
+                auto load_v = [&]() {   // V tile tv into the next stage of its ring (the stage is free)
+                    const uint32_t vs = vcount % V_STAGES;
+                    ++vcount;
+                    uint8_t *vdst = v_s + vs * TILE_BYTES;
+                    mbar_expect_tx(&bar->v_full[vs], TILE_BYTES);
+                    if (tv < n_st) {
+                        if (BLK == TILE) {
+                            const int id = max(0, min(ids[tv], p.Nkv - 1));
+                            tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * TILE, b);
+                            tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * TILE, b);
+                        } else {
+                            const int id = max(0, min(ids[2 * tv], p.Nkv - 1));
+                            const int id2 = 2 * tv + 1 < n_sel ? max(0, min(ids[2 * tv + 1], p.Nkv - 1)) : id;
+                            tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * HALF, b);
+                            tma_load_4d(vdst + HALF_BYTES / 2, &tm_v, &bar->v_full[vs], 0, h, id2 * HALF, b);
+                            tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * HALF, b);
+                            tma_load_4d(vdst + HALF_BYTES + HALF_BYTES / 2, &tm_v, &bar->v_full[vs], 64, h, id2 * HALF, b);
+                        }
+                    } else {
+                        const int c = (tv - n_st) * TILE;
+                        tma_load_4d(vdst, &tm_vc, &bar->v_full[vs], 0, h, c, b);
+                        tma_load_4d(vdst + HALF_BYTES, &tm_vc, &bar->v_full[vs], 64, h, c, b);
+                    }
+                    ++tv;
+                };
+                auto v_free = [&]() { return mbar_test(&bar->v_empty[vcount % V_STAGES], ((vcount / V_STAGES) & 1u) ^ 1u); };
+
                 for (int t = 0; t <= n_kv && ok; ++t) {
                     const uint32_t ks = kcount % KV_STAGES, kpar = ((kcount / KV_STAGES) & 1u) ^ 1u;
-                    ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, p.error_flag, 1);
-                    if (!ok) break;
+                    // wait for the K stage; V tiles whose K tile is out already go out as their stages come back
+                    if (!mbar_test(&bar->k_empty[ks], kpar)) {
+                        const long long w0 = clock64();
+                        while (ok) {
+                            if (tv < t && v_free()) load_v();
+                            if (tv >= t) {   // nothing else to feed
+                                ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, p.error_flag, 1);
+                                break;
+                            }
+                            if (mbar_try_wait_ns(&bar->k_empty[ks], kpar, 200u)) break;
+                            if (*abort_flag) ok = false;
+                            else if (clock64() - w0 > WAIT_CYCLES) {
+                                *abort_flag = 1;
+                                atomicExch(p.error_flag, 1);
+                                ok = false;
+                            }
+                        }
+                        if (!ok) break;
+                    }
                     uint8_t *kdst = k_s + ks * TILE_BYTES;
                     // real tokens of the tile: low byte = of its first 64 keys, next byte = of its last 64
                     int id = 0, id2 = 0, valid = 0;
@@ -527,29 +584,12 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tma_load_2d(kdst, &tm_w, &bar->k_full[ks], 0, 0);
                         tma_load_2d(kdst + HALF_BYTES, &tm_w, &bar->k_full[ks], 64, 0);
                     }
-                    if (t < n_kv) {
-                        const uint32_t vs = vcount % V_STAGES, vpar = ((vcount / V_STAGES) & 1u) ^ 1u;
-                        ok = mbar_wait(&bar->v_empty[vs], vpar, abort_flag, p.error_flag, 2);
-                        if (!ok) break;
-                        ++vcount;
-                        uint8_t *vdst = v_s + vs * TILE_BYTES;
-                        mbar_expect_tx(&bar->v_full[vs], TILE_BYTES);
-                        if (t < n_st) {
-                            if (BLK == TILE) {
-                                tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * TILE, b);
-                                tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * TILE, b);
-                            } else {
-                                tma_load_4d(vdst, &tm_v, &bar->v_full[vs], 0, h, id * HALF, b);
-                                tma_load_4d(vdst + HALF_BYTES / 2, &tm_v, &bar->v_full[vs], 0, h, id2 * HALF, b);
-                                tma_load_4d(vdst + HALF_BYTES, &tm_v, &bar->v_full[vs], 64, h, id * HALF, b);
-                                tma_load_4d(vdst + HALF_BYTES + HALF_BYTES / 2, &tm_v, &bar->v_full[vs], 64, h, id2 * HALF, b);
-                            }
-                        } else {
-                            const int c = (t - n_st) * TILE;
-                            tma_load_4d(vdst, &tm_vc, &bar->v_full[vs], 0, h, c, b);
-                            tma_load_4d(vdst + HALF_BYTES, &tm_vc, &bar->v_full[vs], 64, h, c, b);
-                        }
-                    }
+                    while (tv <= t && tv < n_kv && v_free()) load_v();
+                }
+                // the item's remaining V tiles, in order
+                while (ok && tv < n_kv) {
+                    ok = mbar_wait(&bar->v_empty[vcount % V_STAGES], ((vcount / V_STAGES) & 1u) ^ 1u, abort_flag, p.error_flag, 2);
+                    if (ok) load_v();
                 }
                 ++jcount;
             }
