@@ -610,6 +610,10 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
         auto issue_qk = [&](uint64_t qd, bool is_gate) -> bool {
             const uint32_t buf = kcount % S_BUFS;
+            // the K tile first: it is there long before the S buffer comes back, so that nothing but the fence and the
+            // products themselves stand between that and the scores
+            const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
             if (occ_gate & (1u << buf)) {
                 // the epilogue has read the gate scores of tile kcount - S_BUFS out of this buffer
                 if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], ((kcount - S_BUFS) / S_BUFS) & 1u, abort_flag, p.error_flag, 13)))
@@ -622,8 +626,6 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             occ_gate &= ~(1u << buf);
             occ_pv &= ~(1u << buf);
-            const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
-            if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
             ++kcount;
             WA_TRACE(1);
             tc_fence_after();
@@ -635,8 +637,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     const uint64_t off = (uint64_t)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
                     mma_ss(d, qd + off, kd + off, IDESC_QK, kk > 0);
                 }
+                tc_commit(&bar->s_full[buf]);   // the softmax waits for this one
                 tc_commit(&bar->k_empty[ks]);
-                tc_commit(&bar->s_full[buf]);
             }
             __syncwarp();
             if (is_gate) occ_gate |= 1u << buf;
@@ -679,13 +681,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int t = 0; t < n_kv && ok; ++t, ++g) {
                 const uint32_t buf = g % S_BUFS;
                 const bool first = (t == 0) || (t == n_sel);
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (g / S_BUFS) & 1u, abort_flag, p.error_flag, 5));
-                if (!ok) break;
-                WA_TRACE(5);
+                // the V tile first (it lands long before the probabilities do)
                 const uint32_t vs = vcount % V_STAGES, vpar = (vcount / V_STAGES) & 1u;
                 ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, p.error_flag, 6));
                 if (!ok) break;
                 ++vcount;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (g / S_BUFS) & 1u, abort_flag, p.error_flag, 5));
+                if (!ok) break;
+                WA_TRACE(5);
                 if (first) {
                     // the accumulator of the previous branch (or item) must have been read out
                     ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7));
@@ -699,8 +702,8 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     for (int kk = 0; kk < 8; ++kk)
                         mma_ts(tmem_o, tmem_s + buf * TILE + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
                                !(first && kk == 0));
+                    tc_commit(&bar->s_free[buf]);   // first: the next score product waits for it
                     tc_commit(&bar->v_empty[vs]);   // frees the V stage; the rescale path reads it as "this product has landed"
-                    tc_commit(&bar->s_free[buf]);
                     if (t == n_sel - 1 || t == n_kv - 1) tc_commit(&bar->o_done);
                 }
                 __syncwarp();
