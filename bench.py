@@ -45,7 +45,7 @@ WORKLOADS = {
 L2_FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one hsa_fwd_sm100_kernel launch on workload c2
 # (ncu capture summarised in profiles/hsa_fwd_sm100_config2.md)
-NCU_TRAFFIC_BYTES = 168.0e6
+NCU_TRAFFIC_BYTES = 165.6e6
 
 
 # ------------------------------------------------------------------------------------------------
