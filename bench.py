@@ -351,6 +351,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "pair", "solo"],
+                    help="form of the tcgen05 kernel: two CTAs per SM (pair, the default) or one (solo)")
     ap.add_argument("--no-hkv", action="store_true")
     ap.add_argument("--hkv-only", action="store_true", help="run only the HKV retrieval measurement (one GPU)")
     ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the HKV measurement (30 = benchmark config 3)")
@@ -442,7 +444,7 @@ def main():
                 return wa.hsa.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat,
                                             v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=block,
                                             proj_segment_len=FRAME_TOKENS, topk_per_head=hsa.topk_per_head,
-                                            force_generic=args.force_generic)
+                                            force_generic=args.force_generic, kernel=args.kernel)
             if mode == "heads":
                 return sharded.hsa_attention_head_split(hsa, q, k, v, k_coarse=kc, v_coarse=vc,
                                                         topk_local=hsa.topk_per_head, head_plan=plan,
@@ -462,7 +464,7 @@ def main():
             _, (index, num, _, used_tuned) = wa.hsa.hsa_attention(
                 q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat,
                 gate_lin=hsa.gate_lin, block_size=block, proj_segment_len=FRAME_TOKENS,
-                topk_per_head=hsa.topk_per_head, return_routing=True, force_generic=args.force_generic)
+                topk_per_head=hsa.topk_per_head, return_routing=True, force_generic=args.force_generic, kernel=args.kernel)
         sparse_f, linear_f, gate_f = algorithmic_flops(num.cpu().numpy(), index.cpu().numpy(), q_len, kv_len, block,
                                                        kc.shape[1])
     else:
@@ -617,7 +619,7 @@ def main():
                 out = wa.hsa.hsa_attention(d["q"], d["k"], d["v"], k_coarse=d["kc"], v_coarse=d["vc"],
                                            k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
                                            block_size=block, proj_segment_len=FRAME_TOKENS, topk_per_head=d["topk"],
-                                           force_generic=args.force_generic)
+                                           force_generic=args.force_generic, kernel=args.kernel)
                 d["out"] = out
         # outputs leave after the last group's rows have arrived: on this platform a device-to-host copy that runs
         # against a host-to-device copy slows both down several times
@@ -684,7 +686,8 @@ def main():
             "frac": (achieved / peak_tf) if achieved else None,
             "traffic": NCU_TRAFFIC_BYTES if (used_tuned and world == 1 and args.workload == "c2") else None,
             "peak_source": peak_src,
-            "kernel": "hsa_fwd_sm100 (tcgen05: sparse + linear + gate)" if used_tuned else "generic_attention_kernel (SIMT sparse branch)",
+            "kernel": (f"hsa_fwd_sm100 (tcgen05: sparse + linear + gate; {'one CTA' if args.kernel == 'solo' else 'two CTAs'} per SM)"
+                       if used_tuned else "generic_attention_kernel (SIMT sparse branch)"),
             "kernel_ms": kernel_ms,
             "flops": {"sparse": sparse_f, "linear": linear_f, "gate": gate_f, "counted": flops},
             "sparse_only_frac": (sparse_f / (kernel_ms * 1e-3) / 1e12 / peak_tf) if kernel_ms else None,

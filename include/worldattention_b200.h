@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define WA_ABI_VERSION 1
+#define WA_ABI_VERSION 2
 
 /* element types */
 #define WA_F32 0
@@ -39,6 +39,8 @@ extern "C" {
 /* flags for wa_hsa_forward */
 #define WA_HSA_FORCE_GENERIC 1  /* skip the tcgen05 kernel even when the shape qualifies  */
 #define WA_HSA_REQUIRE_TUNED 2  /* fail with WA_ERR_UNSUPPORTED instead of using the generic kernels */
+#define WA_HSA_KERNEL_SOLO 4    /* tcgen05 kernel as one CTA per SM (three score buffers, two issuing warps)
+                                   instead of the default two CTAs per SM; results agree to rounding   */
 
 /* A strided view of a `[B, L, H, D]` tensor whose last axis is contiguous.  Strides count
  * elements.  `[B, H, N, D]` tensors are described by swapping stride_l / stride_h. */
@@ -51,6 +53,8 @@ typedef struct wa_tensor4 {
 
 int wa_abi_version(void);
 const char *wa_last_error(void);
+/* sizeof(wa_hsa_params) as the library was compiled: a binding checks its own mirror of the struct against it. */
+size_t wa_hsa_params_size(void);
 
 /* Measurement aids (no reference counterpart).  wa_launch_count: kernels this library has
  * launched in this process.  wa_profile_enable(1) makes wa_hsa_forward bracket its attention
@@ -191,6 +195,11 @@ typedef struct wa_hsa_params {
      * the workspace and every block is pooled.  Ignored when index_in is set. */
     float *k_pooled;
     int32_t k_pooled_valid, reserved2;
+    /* Failure mirror (optional, may be NULL): an int32 the device can write and the host can read without a
+     * copy -- page-locked host memory.  When a bounded wait inside the tcgen05 kernel runs out, the site code
+     * that wa_hsa_status would return is also stored here, so a caller can poll it at its own synchronisation
+     * points instead of paying a device-to-host copy per call.  The library never clears it. */
+    int32_t *status_mirror;
 } wa_hsa_params;
 
 /* Bytes of workspace wa_hsa_forward needs for these sizes (pointers in `p` are ignored). */

@@ -123,12 +123,17 @@ def test_head_split_plans():
 
 
 def test_kv_shard_plans_cut_at_block_boundaries():
-    for kv_len, bs, world, page in ((748_800, 64, 8, 1560), (32_760, 128, 8, 1560), (1000, 64, 4, 0), (100, 64, 8, 0)):
+    for kv_len, bs, world, page in ((748_800, 64, 8, 1560), (32_760, 128, 8, 1560), (1000, 64, 4, 0), (100, 64, 8, 0),
+                                    (120, 64, 8, 0), (120, 64, 8, 50), (160, 64, 8, 100), (4681, 128, 3, 1560)):
         shards = sharded.plan_kv_shards(kv_len, bs, world, page)
         assert len(shards) == world and shards[0][0] == 0 and shards[-1][1] == kv_len
         for (a, b), (c, d) in zip(shards, shards[1:]):
-            assert b == c and a <= b and b % bs == 0
+            # a cut is a block boundary, or the end of the cache when the ragged last block has been given away already
+            assert b == c and a <= b <= kv_len and (b % bs == 0 or b == kv_len)
+        assert sum(b - a for a, b in shards) == kv_len                     # a partition of [0, kv_len): no token twice
         assert sum(math.ceil((b - a) / bs) for a, b in shards) == math.ceil(kv_len / bs)
+    # the ragged case that used to claim tokens past the end: 120 tokens, 64-token blocks, 8 ranks
+    assert sharded.plan_kv_shards(120, 64, 8)[-2:] == [(64, 120), (120, 120)]
 
 
 def test_local_selection_partitions_the_global_selection():
@@ -150,3 +155,45 @@ def test_local_selection_partitions_the_global_selection():
         for i in range(3):
             want[0, h, i, index[0, h, i, : int(num[0, h, i])].long()] = 1
     assert torch.equal(seen, want)
+
+
+def test_install_plan_matches_the_oracle_plan():
+    """The array-form install plan of `HKVCache.apply` against the oracle's restatement of the reference loops:
+    unknown chunks/pages and chunks no tier holds are skipped, the page that crosses the capacity is cut, frames
+    count back from the current start frame."""
+    import numpy as np
+    from oracle import hkv_oracle as K
+    rng = np.random.default_rng(5)
+    frame_len, page_frames = 6, 2
+    bank = wa.hkv.HKVCache(frame_seq_length=frame_len, page_size_frames=page_frames)
+    valid = [40, 31, 24, 12]
+    for c, n in enumerate(valid):
+        bank.chunks.append({"chunk_id": c, "valid_tokens": n, "page_spans": K.page_spans(n, frame_len * page_frames),
+                            "start_frame": 3 + 7 * c, "page_index": None, "heads": 1})
+
+    class Tier:                      # chunk 2 has been dropped by every tier; nothing is on disk
+        def get(self, chunk_id):
+            return None if chunk_id == 2 else {"k": [], "v": []}
+
+        def page_reader(self, chunk_id):
+            return None
+    bank.tier = Tier()
+    for trial in range(60):
+        pairs = [(int(rng.integers(-1, 5)), int(rng.integers(-1, 5))) for _ in range(int(rng.integers(0, 7)))]
+        capacity = int(rng.integers(0, 70))
+        current = int(rng.integers(20, 40))
+        entries = [(c, *bank.chunks[c]["page_spans"][p]) for c, p in pairs
+                   if 0 <= c < len(valid) and c != 2 and 0 <= p < len(bank.chunks[c]["page_spans"])]
+        plan, blobs = bank._install_plan(pairs, capacity=capacity, current_start_frame=current)
+        if not entries:
+            assert plan is None and blobs == {}
+            continue
+        installed = K.plan_install(entries, capacity)
+        moves = K.plan_rerope(installed, [ch["start_frame"] for ch in bank.chunks], frame_len, current)
+        rows = [r for r in plan if int(r["count"]) > 0 or installed]
+        assert int(plan["count"].sum()) == sum(e - s for _, s, e in installed)
+        if not installed:
+            continue
+        assert [(int(r["chunk"]), int(r["src"]), int(r["src"] + r["count"])) for r in rows] == installed
+        assert [(int(r["frame_from"]), int(r["frame_to"])) for r in rows] == moves
+        assert [int(r["dst"]) for r in rows] == list(np.cumsum([0] + [e - s for _, s, e in installed])[:-1])

@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("WORLDATTENTION_B200_LIB") or os.path.join(_HERE, "lib
 
 WA_F32, WA_BF16 = 0, 1
 WA_ERR_ARG, WA_ERR_UNSUPPORTED, WA_ERR_WORKSPACE, WA_ERR_ALIGN, WA_ERR_DEVICE = -1, -2, -3, -4, -5
-WA_HSA_FORCE_GENERIC, WA_HSA_REQUIRE_TUNED = 1, 2
+WA_HSA_FORCE_GENERIC, WA_HSA_REQUIRE_TUNED, WA_HSA_KERNEL_SOLO = 1, 2, 4
 
 
 class Tensor4(C.Structure):
@@ -39,6 +39,7 @@ class HsaParams(C.Structure):
         ("index_in", C.c_void_p), ("num_in", C.c_void_p), ("part_sparse", C.c_void_p), ("part_linear", C.c_void_p),
         ("lse_sparse", C.c_void_p), ("lse_linear", C.c_void_p),
         ("k_pooled", C.c_void_p), ("k_pooled_valid", C.c_int32), ("reserved2", C.c_int32),
+        ("status_mirror", C.c_void_p),
     ]
 
 
@@ -54,6 +55,7 @@ _vp, _i, _f, _d, _i64 = C.c_void_p, C.c_int, C.c_float, C.c_double, C.c_int64
 SIGNATURES = {
     "wa_abi_version": [],
     "wa_last_error": [],
+    "wa_hsa_params_size": [],
     "wa_launch_count": [],
     "wa_profile_enable": [_i],
     "wa_profile_attention_ms": [C.POINTER(C.c_float)],
@@ -79,7 +81,7 @@ SIGNATURES = {
                              _i, _i, _i, _i, _vp, _vp, _vp],
     "wa_hkv_gather_pages": [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
 }
-_RESTYPES = {"wa_last_error": C.c_char_p, "wa_hsa_workspace_bytes": C.c_size_t,
+_RESTYPES = {"wa_last_error": C.c_char_p, "wa_hsa_workspace_bytes": C.c_size_t, "wa_hsa_params_size": C.c_size_t,
              "wa_launch_count": C.c_ulonglong}
 
 _lib: Optional[C.CDLL] = None
@@ -99,8 +101,8 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = _RESTYPES.get(name, C.c_int)
-        if handle.wa_abi_version() != 1:
-            raise RuntimeError("libwa_b200.so ABI version mismatch; rebuild the library")
+        if handle.wa_abi_version() != 2 or handle.wa_hsa_params_size() != C.sizeof(HsaParams):
+            raise RuntimeError("libwa_b200.so ABI mismatch (version or wa_hsa_params layout); rebuild the library")
         _lib = handle
     return _lib
 
@@ -140,6 +142,37 @@ def require_cuda(*tensors: torch.Tensor) -> torch.device:
         elif t.device != dev:
             raise ValueError(f"tensors live on different devices: {dev} and {t.device}")
     return dev
+
+
+_status_words: dict = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The page-locked int32 that the tcgen05 kernel writes its failure code to on `device` (one per device)."""
+    key = torch.device(device).index or 0
+    word = _status_words.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_words[key] = word
+    return word
+
+
+def raise_if_failed(device: torch.device) -> None:
+    """Raise if an earlier tcgen05 launch on `device` gave up at a bounded wait (its output is invalid).
+
+    Reads host memory only: no copy, no synchronisation.  A failure of a launch that is still in flight shows
+    at the next call or at the caller's next synchronisation point followed by this check.
+    """
+    word = _status_words.get(torch.device(device).index or 0)
+    if word is not None and int(word[0]) != 0:
+        code = int(word[0])
+        word.zero_()
+        raise RuntimeError(f"an earlier tcgen05 HSA launch on {device} gave up at wait site {code}; its output is invalid")
+
+
+def device_guard(device: torch.device):
+    """Make `device` the current CUDA device for the calls inside (function set-up and launches act on the current one)."""
+    return torch.cuda.device(device)
 
 
 def stream_ptr(device: torch.device) -> int:

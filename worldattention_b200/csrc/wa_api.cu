@@ -38,6 +38,7 @@ void profile_mark(bool begin, cudaStream_t stream) {
 using namespace wa;
 
 extern "C" int wa_abi_version(void) { return WA_ABI_VERSION; }
+extern "C" size_t wa_hsa_params_size(void) { return sizeof(wa_hsa_params); }
 extern "C" unsigned long long wa_launch_count(void) { return launch_counter(); }
 extern "C" int wa_profile_enable(int on) {
     g_profile = on != 0;

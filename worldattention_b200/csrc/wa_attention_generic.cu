@@ -170,12 +170,12 @@ int launch_generic_attention(GenericAttnParams &p, int B, int n_q_blocks, cudaSt
     const long long gx = (long long)n_q_blocks * p.tiles_per_block;
     WA_REQUIRE(gx < (1ll << 31) && p.H <= 65535 && B <= 65535, WA_ERR_UNSUPPORTED, "%s: grid too large", what);
     const size_t smem = ((size_t)GA_QT * p.D + (size_t)GA_TK * (p.D + 1) + (size_t)GA_TK * p.D) * sizeof(float);
-    static bool attr_set = false;
-    if (smem > 48 * 1024 && !attr_set) {
+    static PerDeviceOnce attr_set;
+    if (smem > 48 * 1024 && !attr_set.done()) {
         cudaError_t e = cudaFuncSetAttribute(generic_attention_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
         if (e != cudaSuccess) return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
-        attr_set = true;
+        attr_set.mark();
     }
     dim3 grid((unsigned)gx, p.H, B);
     generic_attention_kernel<<<grid, GA_THREADS, smem, stream>>>(p);
@@ -360,12 +360,12 @@ extern "C" int wa_gate_combine(const wa_tensor4 *q, const wa_tensor4 *sparse, co
     WA_REQUIRE(blocks < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: too many tokens", what);
     if (gate_w && D <= 128) {
         const size_t smem2 = ((size_t)D * (D + 1) + D + (size_t)GS_WARPS * D) * sizeof(float);
-        static bool attr_set = false;
-        if (smem2 > 48 * 1024 && !attr_set) {
+        static PerDeviceOnce attr_set;
+        if (smem2 > 48 * 1024 && !attr_set.done()) {
             cudaError_t e = cudaFuncSetAttribute(gate_combine_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)(((size_t)128 * 129 + 128 + GS_WARPS * 128) * sizeof(float)));
             if (e != cudaSuccess) return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
-            attr_set = true;
+            attr_set.mark();
         }
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -31,6 +32,25 @@ inline int check_launch(const char *what) {
     if (e != cudaSuccess) return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
     return 0;
 }
+
+// A "done once" mark per CUDA device.  Function attributes (the dynamic shared-memory opt-in) and
+// capability answers belong to a device, not to the process: a second GPU used by the same process
+// needs its own set-up.  Devices beyond the 64 tracked ones simply repeat the set-up on every call.
+struct PerDeviceOnce {
+    std::atomic<unsigned long long> bits{0};
+    static int current() {
+        int dev = -1;
+        return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+    }
+    bool done() const {
+        const int dev = current();
+        return dev >= 0 && dev < 64 && ((bits.load(std::memory_order_acquire) >> dev) & 1ull);
+    }
+    void mark() {
+        const int dev = current();
+        if (dev >= 0 && dev < 64) bits.fetch_or(1ull << dev, std::memory_order_release);
+    }
+};
 
 #define WA_REQUIRE(cond, code, ...)                    \
     do {                                               \

@@ -19,29 +19,23 @@
 //
 // Every mbarrier wait is bounded (about two seconds); on expiry the kernel raises a flag in
 // global memory, all roles leave their loops, tensor memory is released and the kernel returns.
-#include <cuda.h>
-
 #include <cstdlib>
 
 #include "wa_internal.cuh"
+#include "wa_sm100_ptx.cuh"
 
 namespace wa {
 namespace sm100 {
 
-constexpr int TILE = 128;            // query rows, key tokens and head_dim of one tile
-constexpr int HALF = 64;             // key tokens per softmax / MMA pipeline step
 constexpr int THREADS = 384;         // warps 0..7 softmax (two threads per query row), warp 8 TMA, warp 9 QK products, warp 10 output store, warp 11 PV products
 constexpr int REGS_SOFTMAX = 224;    // register budget per thread after the roles split (two warpgroups of softmax warps)
 constexpr int REGS_OTHER = 56;       // ... and of the warpgroup that holds the four single-purpose warps; 256*224 + 128*56 = 384*168
-constexpr int HALF_BYTES = TILE * 64 * 2;   // one TMA box: 128 rows x 64 bf16 (128 B per row)
-constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
 constexpr int TMEM_COLS = 512;       // three S buffers: columns [0,128), [128,256), [256,384); O: [384,512)
 constexpr int S_BUFS = 3;            // score products run up to two tiles ahead of the softmax
 constexpr int Q_STAGES = 2;          // the staged output of item j leaves from one Q buffer while item j+1 loads the other
 constexpr int KV_STAGES = 3;         // shared-memory ring depth for K tiles
 constexpr int V_STAGES = 2;          // shared-memory ring depth for V tiles
 constexpr int SMEM_BYTES = (Q_STAGES + KV_STAGES + V_STAGES) * TILE_BYTES + 3072 /*barriers, bias*/;
-constexpr long long WAIT_CYCLES = 4000000000ll;
 
 // Optional event trace for kernel tuning (compile with -DWA_SM100_TRACE): CTA 0 appends
 // (event id, clock) pairs from one thread per role to a global buffer.
@@ -92,287 +86,6 @@ __device__ __forceinline__ unsigned wa_smid() {
 #define WA_TRACE_FLUSH do { } while (0)
 #endif
 
-struct Params {
-    int B, H, Lq, Lkv, Lc, Nq, Nkv;
-    int blk;       // routing block size: 128, or 64 (a work item is then a 64-row query block in a 128-row tile whose
-                   // upper rows are computed and dropped, and a key tile holds two selected 64-token blocks)
-    int n_items;
-    const int32_t *index;   // [B,H,Nq,Nkv]
-    const int32_t *num;     // [B,H,Nq]
-    const int32_t *order;   // [n_items] work order (heaviest first)
-    int *work_counter;
-    int *error_flag;
-    __nv_bfloat16 *out;
-    long long osb, osl, osh;
-    const float *gate_bias;   // [128] or null
-    int has_gate;             // 0: gate = sigmoid(q)
-    const __nv_bfloat16 *q;   // for the no-gate path
-    long long qsb, qsl, qsh;
-    float scale_log2;         // D^-1/2 * log2(e)
-    // partial-output mode (KV-sharded multi-GPU): normalised per-branch outputs + natural-log LSE
-    float *part_sparse, *part_linear;   // [B, Lq, H, 128] float32 or null
-    float *lse_sparse, *lse_linear;     // [B, H, Lq]
-};
-
-// ---- PTX wrappers --------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// One arrival for the whole warp: every lane has finished (and fenced) its part before lane 0 signals.
-__device__ __forceinline__ void warp_arrive(uint64_t *bar) {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"   // %3: the thread may sleep this many ns
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
-    return ok != 0;
-}
-// Same with a caller-chosen sleep limit (for a thread that watches two barriers).
-__device__ __forceinline__ bool mbar_try_wait_ns(uint64_t *bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
-    return ok != 0;
-}
-// Non-blocking test of a barrier phase.
-__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false after the abort flag is raised or the time budget is spent.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *error_flag,
-                                          int code) {
-    if (mbar_test(bar, parity)) return true;   // the common case: the phase is over already
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
-            *abort_flag = 1;
-            atomicExch(error_flag, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2,
-                                            int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, const void *src, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-
-#define TMEM_LD32(taddr, r)                                                                                          \
-    asm volatile(                                                                                                    \
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                    \
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                    \
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                    \
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),            \
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),      \
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),    \
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])     \
-        : "r"(taddr) : "memory")
-
-#define TMEM_LD16(taddr, r)                                                                                          \
-    asm volatile(                                                                                                    \
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "                                                                    \
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                             \
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),            \
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])       \
-        : "r"(taddr) : "memory")
-
-#define TMEM_ST16(taddr, r)                                                                                          \
-    asm volatile(                                                                                                    \
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                              \
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                                   \
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),        \
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory")
-
-#define TMEM_ST32(taddr, r)                                                                                          \
-    asm volatile(                                                                                                    \
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                                              \
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "                                   \
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"                           \
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),        \
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),              \
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),            \
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory")
-
-// Quad-row shapes: a 16-row group of lanes is read so that thread t holds rows t/4 and t/4+8 and, per 8-column step j,
-// the column pair 8j + 2(t%4), +1 of each (registers 4j..4j+3: row A pair, row B pair) -- a row lives in one quad.
-// The 16x128b store is the matching shape for 32-bit words: registers 2j, 2j+1 = word 4j + t%4 of row A, row B.
-#define TMEM_LDQ64(taddr, r) \
-    asm volatile("tcgen05.ld.sync.aligned.16x256b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];" \
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]) \
-        : "r"(taddr) : "memory")
-#define TMEM_LDQ16(taddr, r) \
-    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];" \
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) \
-        : "r"(taddr) : "memory")
-#define TMEM_STQ16(taddr, r) \
-    asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" \
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory")
-#define TMEM_STP32(taddr, r) \
-    asm volatile("tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" \
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory")
-
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ float tanh_approx(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
-
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle.  `lbo`, `sbo` in bytes.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;   // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;   // 128-byte swizzle
-    return d;
-}
-
-// kind::f16 instruction descriptor: bf16 x bf16 -> f32, M = N = 128; `b_mn_major` for the V operand.
-__host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major, int n) {
-    return (1u << 4)                 // D format f32
-           | (1u << 7)               // A format bf16
-           | (1u << 10)              // B format bf16
-           | ((b_mn_major ? 1u : 0u) << 16)
-           | ((uint32_t)(n >> 3) << 17)
-           | ((uint32_t)(TILE >> 4) << 24);
-}
-
-// Softmax arithmetic.  It runs on pairs of columns with the packed float32x2 instructions of this architecture (one
-// issue slot for two results).  2^x on the FMA pipe: split x into round(x) + f, f in [-0.5, 0.5], evaluate a
-// cubic for 2^f and add round(x) to the exponent field; relative error < 2^-10, below the bf16 rounding of P.
-// The special-function unit (16 results per clock per SM) is the narrowest pipe of the softmax, so every
-// POLY_EVERY-th pair of columns takes the polynomial instead.
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-    x.x = fmaxf(x.x, -125.0f);
-    x.y = fmaxf(x.y, -125.0f);
-    const float2 magic = make_float2(12582912.0f, 12582912.0f);   // 1.5 * 2^23: the integer part of x lands in the low mantissa bits
-    const float2 t = __fadd2_rn(x, magic);
-    const float2 f = __fadd2_rn(x, __fadd2_rn(magic, make_float2(-t.x, -t.y)));   // x - (t - magic)
-    float2 q = __ffma2_rn(f, make_float2(0.0555041f, 0.0555041f), make_float2(0.2402265f, 0.2402265f));
-    q = __ffma2_rn(q, f, make_float2(0.6931472f, 0.6931472f));
-    q = __ffma2_rn(q, f, make_float2(1.0f, 1.0f));
-    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
-                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
-}
-#ifndef WA_POLY_EVERY
-#define WA_POLY_EVERY 4
-#endif
-constexpr int POLY_EVERY = WA_POLY_EVERY;
-
-
-// One 8-column step of a quad-row tile: this thread's column pair of row A (x0, x1) and of row B (x2, x3)
-// -> probabilities, packed to one bf16 pair per row; row sums accumulate in accA / accB (packed float32x2).
-template <bool POLY, bool MASKED>
-__device__ __forceinline__ void exp_step(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, float2 sc, float2 nmA, float2 nmB,
-                                         float2 &accA, float2 &accB, uint32_t &pkA, uint32_t &pkB, int col, int valid) {
-    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(x0), __uint_as_float(x1)), sc, nmA);
-    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(x2), __uint_as_float(x3)), sc, nmB);
-    float2 pa, pb;
-    if (POLY) {
-        pa = ex2_poly2(xa);
-        pb = ex2_poly2(xb);
-    } else {
-        pa = make_float2(ex2(xa.x), ex2(xa.y));
-        pb = make_float2(ex2(xb.x), ex2(xb.y));
-    }
-    if (MASKED) {
-        if (col >= valid) pa.x = pb.x = 0.f;
-        if (col + 1 >= valid) pa.y = pb.y = 0.f;
-    }
-    accA = __fadd2_rn(accA, pa);
-    accB = __fadd2_rn(accB, pb);
-    __nv_bfloat162 ha = __floats2bfloat162_rn(pa.x, pa.y), hb = __floats2bfloat162_rn(pb.x, pb.y);
-    pkA = *reinterpret_cast<uint32_t *>(&ha);
-    pkB = *reinterpret_cast<uint32_t *>(&hb);
-}
-
-__device__ __forceinline__ float quad_max(float x) {
-    x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
-    return fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
-}
-__device__ __forceinline__ float quad_sum(float x) {
-    x += __shfl_xor_sync(0xffffffffu, x, 1);
-    return x + __shfl_xor_sync(0xffffffffu, x, 2);
-}
-
-struct ItemDesc {
-    int item;    // (b*H + h)*Nq + qb, or -1: no more work
-    int n_sel;   // selected key blocks of this item
-};
-
 struct Barriers {
     uint64_t item_full[2], item_empty[2];
     uint64_t q_full[Q_STAGES], q_empty[Q_STAGES], out_ready[Q_STAGES];
@@ -408,10 +121,11 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &bar->abort_flag;
+    const FailSink sink{p.error_flag, p.status_mirror};
 
     if (threadIdx.x == 0) {
         bar->abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;   // misaligned shared memory: give up before any TMA
-        if (bar->abort_flag) atomicExch(p.error_flag, 99);
+        if (bar->abort_flag) report_failure(sink, 99);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar->item_full[i], 1);
             mbar_init(&bar->item_empty[i], 2 + 8 + 1);   // both MMA leaders + every softmax warp + store warp
@@ -467,7 +181,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             int at = blockIdx.x;
             while (ok) {
                 const uint32_t slot = jcount & 1u;
-                ok = mbar_wait(&bar->item_empty[slot], ((jcount >> 1) & 1u) ^ 1u, abort_flag, p.error_flag, 11);
+                ok = mbar_wait(&bar->item_empty[slot], ((jcount >> 1) & 1u) ^ 1u, abort_flag, sink, 11);
                 if (!ok) break;
                 int item = -1, n_sel = 0;
                 if (at < p.n_items) {
@@ -487,7 +201,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 WA_STATS_ITEM(n_kv + 1);
 
                 const uint32_t qs = jcount % Q_STAGES;
-                ok = mbar_wait(&bar->q_empty[qs], ((jcount / Q_STAGES) & 1u) ^ 1u, abort_flag, p.error_flag, 12);
+                ok = mbar_wait(&bar->q_empty[qs], ((jcount / Q_STAGES) & 1u) ^ 1u, abort_flag, sink, 12);
                 if (!ok) break;
                 uint8_t *qdst = q_s + qs * TILE_BYTES;
                 mbar_expect_tx(&bar->q_full[qs], TILE_BYTES);
@@ -532,14 +246,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         while (ok) {
                             if (tv < t && v_free()) load_v();
                             if (tv >= t) {   // nothing else to feed
-                                ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, p.error_flag, 1);
+                                ok = mbar_wait(&bar->k_empty[ks], kpar, abort_flag, sink, 1);
                                 break;
                             }
                             if (mbar_try_wait_ns(&bar->k_empty[ks], kpar, 200u)) break;
                             if (*abort_flag) ok = false;
                             else if (clock64() - w0 > WAIT_CYCLES) {
                                 *abort_flag = 1;
-                                atomicExch(p.error_flag, 1);
+                                report_failure(sink, 1);
                                 ok = false;
                             }
                         }
@@ -588,7 +302,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
                 // the item's remaining V tiles, in order
                 while (ok && tv < n_kv) {
-                    ok = mbar_wait(&bar->v_empty[vcount % V_STAGES], ((vcount / V_STAGES) & 1u) ^ 1u, abort_flag, p.error_flag, 2);
+                    ok = mbar_wait(&bar->v_empty[vcount % V_STAGES], ((vcount / V_STAGES) & 1u) ^ 1u, abort_flag, sink, 2);
                     if (ok) load_v();
                 }
                 ++jcount;
@@ -613,14 +327,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             // the K tile first: it is there long before the S buffer comes back, so that nothing but the fence and the
             // products themselves stand between that and the scores
             const uint32_t ks = kcount % KV_STAGES, kpar = (kcount / KV_STAGES) & 1u;
-            if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, p.error_flag, 4))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bar->k_full[ks], kpar, abort_flag, sink, 4))) return false;
             if (occ_gate & (1u << buf)) {
                 // the epilogue has read the gate scores of tile kcount - S_BUFS out of this buffer
-                if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], ((kcount - S_BUFS) / S_BUFS) & 1u, abort_flag, p.error_flag, 13)))
+                if (!__all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], ((kcount - S_BUFS) / S_BUFS) & 1u, abort_flag, sink, 13)))
                     return false;
             } else if (occ_pv & (1u << buf)) {
                 // the PV product that read P from this buffer has landed
-                if (!__all_sync(0xffffffffu, mbar_wait(&bar->s_free[buf], (ph_sf >> buf) & 1u, abort_flag, p.error_flag, 19)))
+                if (!__all_sync(0xffffffffu, mbar_wait(&bar->s_free[buf], (ph_sf >> buf) & 1u, abort_flag, sink, 19)))
                     return false;
                 ph_sf ^= 1u << buf;
             }
@@ -649,7 +363,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
         while (ok) {
             const uint32_t slot = jcount & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 14));
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, sink, 14));
             if (!ok) break;
             const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
             __syncwarp();
@@ -657,7 +371,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (item < 0) break;
             const int n_kv = n_sel + lin_tiles;   // K-type tiles 0 .. n_kv - 1 feed a PV product, tile n_kv is the gate
             const uint32_t qs = jcount % Q_STAGES;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full[qs], (jcount / Q_STAGES) & 1u, abort_flag, p.error_flag, 3));
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->q_full[qs], (jcount / Q_STAGES) & 1u, abort_flag, sink, 3));
             if (!ok) break;
             const uint64_t qd = smem_desc(smem_u32(q_s + qs * TILE_BYTES), 16, 1024);
             for (int t = 0; t <= n_kv && ok; ++t) ok = issue_qk(qd, t == n_kv);
@@ -671,7 +385,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         bool ok = true;
         while (ok) {
             const uint32_t slot = jcount & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 20));
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, sink, 20));
             if (!ok) break;
             const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
             __syncwarp();
@@ -683,15 +397,15 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const bool first = (t == 0) || (t == n_sel);
                 // the V tile first (it lands long before the probabilities do)
                 const uint32_t vs = vcount % V_STAGES, vpar = (vcount / V_STAGES) & 1u;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, p.error_flag, 6));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_full[vs], vpar, abort_flag, sink, 6));
                 if (!ok) break;
                 ++vcount;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (g / S_BUFS) & 1u, abort_flag, p.error_flag, 5));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->p_full[buf], (g / S_BUFS) & 1u, abort_flag, sink, 5));
                 if (!ok) break;
                 WA_TRACE(5);
                 if (first) {
                     // the accumulator of the previous branch (or item) must have been read out
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, p.error_flag, 7));
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_free, ph_of, abort_flag, sink, 7));
                     if (!ok) break;
                     ph_of ^= 1u;
                 }
@@ -719,14 +433,14 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             bool ok = true;
             while (ok) {
                 const uint32_t slot = jcount & 1u;
-                ok = mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 16);
+                ok = mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, sink, 16);
                 if (!ok) break;
                 const int item = bar->items[slot].item;
                 mbar_arrive(&bar->item_empty[slot]);
                 if (item < 0) break;
                 const int qb = item % p.Nq, h = (item / p.Nq) % p.H, b = item / (p.Nq * p.H);
                 const uint32_t qs = jcount % Q_STAGES;
-                ok = mbar_wait(&bar->out_ready[qs], (jcount / Q_STAGES) & 1u, abort_flag, p.error_flag, 17);
+                ok = mbar_wait(&bar->out_ready[qs], (jcount / Q_STAGES) & 1u, abort_flag, sink, 17);
                 if (!ok) break;
                 if (!p.part_linear) {
                     // rows beyond q_len are clipped by the tensor map
@@ -763,7 +477,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
         while (ok) {
             const uint32_t slot = jcount & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, p.error_flag, 15));
+            ok = __all_sync(0xffffffffu, mbar_wait(&bar->item_full[slot], (jcount >> 1) & 1u, abort_flag, sink, 15));
             if (!ok) break;
             const int item = bar->items[slot].item, n_sel = bar->items[slot].n_sel;
             warp_arrive(&bar->item_empty[slot]);
@@ -788,7 +502,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 for (int t = t0; t < t1 && ok; ++t) {
                     const int buf = (sg + t) % S_BUFS;
                     const uint32_t s_addr = tmem_s + buf * TILE + lane_addr;
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], ((sg + t) / S_BUFS) & 1u, abort_flag, p.error_flag, 8));
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[buf], ((sg + t) / S_BUFS) & 1u, abort_flag, sink, 8));
                     if (!ok) break;
                     WA_TRACE(2);
                     tc_fence_after();
@@ -834,7 +548,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     if (__any_sync(0xffffffffu, (growA || growB) && t > t0)) {
                         // every PV requested so far must have landed before the accumulator is touched
                         ok = __all_sync(0xffffffffu, mbar_wait(&bar->v_empty[(pv_count - 1u) % V_STAGES],
-                                                               ((pv_count - 1u) / V_STAGES) & 1u, abort_flag, p.error_flag, 9));
+                                                               ((pv_count - 1u) / V_STAGES) & 1u, abort_flag, sink, 9));
                         if (!ok) break;
                         tc_fence_after();
                         const float fA = (growA && t > t0) ? ex2(mA - mA_new) : 1.0f, fB = (growB && t > t0) ? ex2(mB - mB_new) : 1.0f;
@@ -898,7 +612,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         // The sparse branch's accumulator: its last PV product had this whole tile to land.  Normalise,
                         // round to bf16 (the reference stores this branch in bf16) and park it in registers until the
                         // combine; then the linear branch's first PV product may overwrite it.
-                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
+                        ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, sink, 9));
                         if (!ok) break;
                         ph_od ^= 1u;
                         tc_fence_after();
@@ -973,7 +687,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             };
             if (ok) {
                 WA_TRACE(18);
-                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], ((sg + n_kv) / S_BUFS) & 1u, abort_flag, p.error_flag, 10));
+                ok = __all_sync(0xffffffffu, mbar_wait(&bar->s_full[gbuf], ((sg + n_kv) / S_BUFS) & 1u, abort_flag, sink, 10));
             }
             if (ok) {
                 tc_fence_after();
@@ -1019,7 +733,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 tc_fence_before();
                 warp_arrive(&bar->p_full[gbuf]);
                 if (lin_tiles > 0) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, p.error_flag, 9));
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bar->o_done, ph_od, abort_flag, sink, 9));
                     ph_od ^= 1u;
                     tc_fence_after();
                     WA_TRACE(12);
@@ -1210,15 +924,14 @@ SchedJob hsa_sm100_sched_job(const wa_hsa_params *p, void *workspace) {
 }
 
 static bool device_is_sm100() {
-    static int cached = -1;
-    if (cached < 0) {
-        int dev = 0, major = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
-            return false;
-        cached = major == 10 ? 1 : 0;
-    }
-    return cached == 1;
+    static PerDeviceOnce known_sm100;   // the answer belongs to the current device, not to the process
+    if (known_sm100.done()) return true;
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+        return false;
+    if (major == 10) known_sm100.mark();
+    return major == 10;
 }
 
 bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc) {
@@ -1264,6 +977,7 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.n_items = n_items;
     kp.blk = blk;
     kp.index = index; kp.num = num; kp.order = order; kp.work_counter = counter; kp.error_flag = counter + 1;
+    kp.status_mirror = p->status_mirror;
     kp.out = (__nv_bfloat16 *)p->out.ptr; kp.osb = p->out.stride_b; kp.osl = p->out.stride_l; kp.osh = p->out.stride_h;
     kp.gate_bias = bias; kp.has_gate = p->gate_w != nullptr;
     kp.q = (const __nv_bfloat16 *)p->q.ptr; kp.qsb = p->q.stride_b; kp.qsl = p->q.stride_l; kp.qsh = p->q.stride_h;
@@ -1272,20 +986,29 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.lse_sparse = p->lse_sparse; kp.lse_linear = p->lse_linear;
 
 
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
-        attr_set = true;
+    // Two forms of the kernel: two CTAs per SM, each with one work item in flight (the default), or one CTA per SM
+    // with three score buffers and two issuing warps.
+    const bool pair = !(p->flags & WA_HSA_KERNEL_SOLO);
+    if (pair) {
+        if ((rc = pair_kernel_prepare())) return rc;
+    } else {
+        static PerDeviceOnce attr_set;
+        if (!attr_set.done()) {
+            cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
+            attr_set.mark();
+        }
     }
-    int grid = n_items < max_grid() ? n_items : max_grid();
+    const int slots = max_grid() * (pair ? 2 : 1);
+    int grid = n_items < slots ? n_items : slots;
 #ifdef WA_SM100_TRACE
     if (getenv("WA_SM100_ONE_CTA") && grid > max_grid() / 2) grid = max_grid() / 2;   // tuning aid: one CTA per SM
 #endif
     profile_mark(true, stream);
-    if (blk == TILE) hsa_fwd_sm100_kernel<TILE><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
+    if (pair) pair_kernel_launch(blk, grid, stream, tq, tk, tv, tkc, tvc, tw, tout, kp);
+    else if (blk == TILE) hsa_fwd_sm100_kernel<TILE><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     else hsa_fwd_sm100_kernel<HALF><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     profile_mark(false, stream);
     return check_launch("wa_hsa_forward(tcgen05)");

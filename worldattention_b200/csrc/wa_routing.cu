@@ -39,10 +39,10 @@ pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks,
         const int lanes_per_row = D >> 3;
         const int rows = POOL_THREADS / lanes_per_row;
         const int lane = threadIdx.x % lanes_per_row, row = threadIdx.x / lanes_per_row;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // float64: exact for a block of bf16 values, so order-free
         if (row < rows) {
             const __nv_bfloat16 *p = (const __nv_bfloat16 *)x.ptr + base + lane * 8;
-            // eight row loads in flight per thread; rows past the end contribute zeros (same sum order as a plain loop)
+            // eight row loads in flight per thread; rows past the end contribute zeros
             for (int t = row; t < n_real; t += 8 * rows) {
                 uint4 raw[8];
 #pragma unroll
@@ -57,24 +57,24 @@ pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks,
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         float2 f = __bfloat1622float2(h2[i]);
-                        acc[2 * i] += f.x;
-                        acc[2 * i + 1] += f.y;
+                        acc[2 * i] += (double)f.x;
+                        acc[2 * i + 1] += (double)f.y;
                     }
                 }
             }
         }
-        float *sm = reinterpret_cast<float *>(pool_smem);  // [rows][D]
+        double *sm = pool_smem;  // [rows][D]
         if (row < rows) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) sm[row * D + lane * 8 + i] = acc[i];
         }
         __syncthreads();
         for (int d = threadIdx.x; d < D; d += POOL_THREADS) {
-            float s = 0.f;
-            for (int r = 0; r < rows; ++r) s += sm[r * D + d];  // fixed order
+            double s = 0.0;
+            for (int r = 0; r < rows; ++r) s += sm[r * D + d];
             float out;
-            if (aligned) out = bf16_round_f((float)((double)s / (double)block_size));
-            else out = __fdiv_rn(bf16_round_f(s), (float)n_real);
+            if (aligned) out = bf16_round_f((float)(s / (double)block_size));
+            else out = __fdiv_rn(bf16_round_f((float)s), (float)n_real);
             dst[d] = out;
         }
     } else {
@@ -111,66 +111,105 @@ pool_blocks_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks,
 }
 
 // ------------------------------------------------------------------------------------------------
-// Pooling, streaming form for bf16 rows of 8..256 channels (a power of two): one WARP per (batch,
-// block, head), no block-level synchronisation, eight 16-byte row loads in flight per lane.  The
-// D/8 lanes that cover one token row form a group; the 32/(D/8) groups take token rows round-robin
-// and their partial sums are added in group order at the end.
+// Pooling, streaming form for bf16 rows of 8..256 channels (a power of two): SPLIT warps per (batch,
+// block, head), no block-level synchronisation on the load path.  The D/8 lanes that cover one token
+// row form a group; the groups of the item's warps take token rows round-robin.  Every lane keeps
+// UNROLL 16-byte row loads in flight and issues the next batch before it consumes the current one.
+// Sums are float64: a sum of a few hundred bf16 values is exact there, so the result does not depend
+// on the order of the additions (the routing decision downstream is discrete).
 // ------------------------------------------------------------------------------------------------
-template <int UNROLL>
-__global__ void __launch_bounds__(POOL_THREADS)
+#ifndef WA_POOL_SPLIT
+#define WA_POOL_SPLIT 2
+#endif
+#ifndef WA_POOL_UNROLL
+#define WA_POOL_UNROLL 4
+#endif
+
+#ifndef WA_POOL_MIN_CTAS
+#define WA_POOL_MIN_CTAS 3
+#endif
+
+template <int UNROLL, int SPLIT>
+__global__ void __launch_bounds__(POOL_THREADS, WA_POOL_MIN_CTAS)
 pool_warp_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, int aligned, float *__restrict__ pooled,
                  View4 x2, int L2, int num_blocks2, int aligned2, float *__restrict__ pooled2, int out_blocks2, int B,
                  int *__restrict__ zero, int n_zero) {
+    constexpr int ITEMS_PER_CTA = POOL_THREADS / 32 / SPLIT;
+    __shared__ double partial[ITEMS_PER_CTA][SPLIT > 1 ? SPLIT - 1 : 1][256];   // [item][warp - 1][channel]
     if (n_zero && blockIdx.x == 0)   // counters of the kernel that follows on the stream
         for (int i = threadIdx.x; i < n_zero; i += POOL_THREADS) zero[i] = 0;
-    const int lane = threadIdx.x & 31;
-    long long item = (long long)blockIdx.x * (POOL_THREADS / 32) + (threadIdx.x >> 5);   // ((b, block), head), head fastest
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slot = warp / SPLIT, part = warp % SPLIT;   // item of this CTA, this warp's share of its rows
+    long long item = (long long)blockIdx.x * ITEMS_PER_CTA + slot;   // ((b, block), head), head fastest
     const long long items1 = (long long)B * num_blocks * H;
     int out_blocks = num_blocks;   // rows per (batch, head) of the output buffer
+    bool live = true;
     if (item >= items1) {   // second tensor (keys) pooled by the same launch
         item -= items1;
-        if (item >= (long long)B * num_blocks2 * H) return;
+        live = item < (long long)B * num_blocks2 * H;
         x = x2; L = L2; num_blocks = num_blocks2; aligned = aligned2; pooled = pooled2; out_blocks = out_blocks2;
     }
+    if (!live) item = 0;   // keeps the CTA's barrier below unconditional; nothing is stored
     const int h = (int)(item % H);
     const int nb = (int)((item / H) % num_blocks);
     const int b = (int)(item / ((long long)H * num_blocks));
     const int t0 = nb * block_size;
-    const int n_real = min(block_size, L - t0);
+    const int n_real = live ? min(block_size, L - t0) : 0;
     const int lanes_per_row = D >> 3, groups = 32 / lanes_per_row;
     const int col = (lane % lanes_per_row) * 8, group = lane / lanes_per_row;
+    const int stride = groups * SPLIT;               // token rows between two loads of one lane
     const __nv_bfloat16 *p = (const __nv_bfloat16 *)x.ptr + (long long)b * x.sb + (long long)h * x.sh +
                              (long long)t0 * x.sl + col;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int t = group; t < n_real; t += UNROLL * groups) {
-        uint4 raw[UNROLL];
+    double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 cur[UNROLL], nxt[UNROLL];
+    auto fetch = [&](uint4 (&dst)[UNROLL], int t) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int tt = t + u * groups;
-            raw[u] = tt < n_real ? __ldg(reinterpret_cast<const uint4 *>(p + (long long)tt * x.sl)) : make_uint4(0u, 0u, 0u, 0u);
+            const int tt = t + u * stride;
+            dst[u] = tt < n_real ? __ldg(reinterpret_cast<const uint4 *>(p + (long long)tt * x.sl)) : make_uint4(0u, 0u, 0u, 0u);
         }
+    };
+    const int first = part * groups + group;
+    fetch(cur, first);
+    for (int t = first; t < n_real; t += UNROLL * stride) {
+        fetch(nxt, t + UNROLL * stride);   // rows past the end load nothing
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&cur[u]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 f = __bfloat1622float2(h2[i]);
-                acc[2 * i] += f.x;
-                acc[2 * i + 1] += f.y;
+                acc[2 * i] += (double)f.x;
+                acc[2 * i + 1] += (double)f.y;
             }
         }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) cur[u] = nxt[u];
     }
-    // group g adds the partial of group g + step: (0 + 1), ((0 + 1) + (2 + 3)), ... a fixed tree
+    // the groups of a warp, then the warps of the item
     for (int step = lanes_per_row; step < 32; step <<= 1) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], step);
     }
-    if (group == 0) {
+    if (SPLIT > 1) {
+        if (part > 0 && group == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) partial[slot][part - 1][col + i] = acc[i];
+        }
+        __syncthreads();
+        if (part == 0 && group == 0) {
+#pragma unroll
+            for (int w = 0; w < SPLIT - 1; ++w)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += partial[slot][w][col + i];
+        }
+    }
+    if (live && part == 0 && group == 0) {
         float out[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            out[i] = aligned ? bf16_round_f((float)((double)acc[i] / (double)block_size))
-                             : __fdiv_rn(bf16_round_f(acc[i]), (float)n_real);
+            out[i] = aligned ? bf16_round_f((float)(acc[i] / (double)block_size))
+                             : __fdiv_rn(bf16_round_f((float)acc[i]), (float)n_real);
         float4 *dst = reinterpret_cast<float4 *>(pooled + (((long long)b * H + h) * out_blocks + nb) * (long long)D + col);
         dst[0] = make_float4(out[0], out[1], out[2], out[3]);
         dst[1] = make_float4(out[4], out[5], out[6], out[7]);
@@ -709,15 +748,15 @@ int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int
     const int lanes = D / 8;
     if (vec && D % 8 == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0 && ((uintptr_t)px % 16 == 0) &&
         (!y || (uintptr_t)py % 16 == 0)) {
+        constexpr int items_per_cta = POOL_THREADS / 32 / WA_POOL_SPLIT;
         const long long items = (long long)B * H * (nbx + nby);
-        const long long ctas = (items + POOL_THREADS / 32 - 1) / (POOL_THREADS / 32);
+        const long long ctas = (items + items_per_cta - 1) / items_per_cta;
         WA_REQUIRE(ctas < (1ll << 31), WA_ERR_UNSUPPORTED, "wa_pool_blocks: too many blocks");
-        pool_warp_kernel<8><<<(unsigned)ctas, POOL_THREADS, 0, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0, px, vy,
-                                                                      Ly, nby, y_aligned, py, nby_all, B, zero,
-                                                                      n_zero);
+        pool_warp_kernel<WA_POOL_UNROLL, WA_POOL_SPLIT><<<(unsigned)ctas, POOL_THREADS, 0, stream>>>(
+            vx, Lx, H, D, block_size, nbx, Lx % block_size == 0, px, vy, Ly, nby, y_aligned, py, nby_all, B, zero, n_zero);
     } else if (vec) {
         const int rows = POOL_THREADS / (D / 8);
-        const size_t smem = (size_t)rows * D * sizeof(float);
+        const size_t smem = (size_t)rows * D * sizeof(double);
         WA_REQUIRE(smem <= 48 * 1024, WA_ERR_UNSUPPORTED, "wa_pool_blocks: D=%d too large", D);
         pool_blocks_kernel<true><<<grid, POOL_THREADS, smem, stream>>>(vx, Lx, H, D, block_size, nbx, Lx % block_size == 0,
                                                                        px, vy, Ly, nby, y_aligned, py, nby_all, zero, n_zero);

@@ -158,140 +158,144 @@ class HKVCache:
 
         Returns the number of tokens installed; 0 (cache untouched) when nothing resolves.
         """
-        entries, blobs = self._resolve_pages(selected_pairs)
-        if not entries:
-            return 0
-
         k0 = kv_cache[0]["k"]
+        plan, blobs = self._install_plan(selected_pairs, capacity=int(k0.shape[1]),
+                                         current_start_frame=int(current_start_frame))
+        if plan is None:
+            return 0
         dev = _lib.require_cuda(k0)
-        bsz, capacity, heads, head_dim = k0.shape
-        dtype = k0.dtype
+        tokens = int(plan["count"].sum())
 
-        budget = capacity
-        installed: List[Tuple[int, int, int]] = []
-        for chunk_id, start, end in entries:
-            if budget <= 0:
-                break
-            take = min(end - start, budget)
-            installed.append((chunk_id, start, start + take))
-            budget -= take
-        total_tokens = sum(end - start for _, start, end in installed)
-
-        frame_moves = self._plan_rerope(installed, current_start_frame) if self.rerope else None
-
-        has_coarse = "k_coarse" in kv_cache[0] and "v_coarse" in kv_cache[0]
-        if has_coarse and hsa_modules is None:
+        compressed = all(name in kv_cache[0] for name in ("k_coarse", "v_coarse"))
+        if compressed and hsa_modules is None:
             raise ValueError(
                 "the online cache carries a compressed tier, so hsa_modules must be supplied so it "
                 "can be rebuilt for the installed pages"
             )
 
-        if total_tokens > 0:
-            self._install(kv_cache, installed, blobs, frame_moves, temporal_freqs, dev, dtype)
+        if tokens > 0:
+            self._install(kv_cache, plan, blobs, temporal_freqs, dev, k0.dtype)
 
-        for block_idx, block in enumerate(kv_cache):
-            block["k"][:, total_tokens:].zero_()
-            block["v"][:, total_tokens:].zero_()
-            if has_coarse:
-                coarse_end = 0
-                if total_tokens > 0:
-                    coarse_end = self._write_coarse(block, hsa_modules[block_idx], total_tokens)
-                block["k_coarse"][:, coarse_end:].zero_()
-                block["v_coarse"][:, coarse_end:].zero_()
-            block["global_end_index"].fill_(current_start_frame * self.frame_seq_length)
-            block["local_end_index"].fill_(total_tokens)
-        return total_tokens
+        end_token = current_start_frame * self.frame_seq_length
+        for layer, block in enumerate(kv_cache):
+            # only the tail beyond the installed span needs clearing: the copy kernel wrote everything before it
+            for name in ("k", "v"):
+                block[name][:, tokens:].zero_()
+            if compressed:
+                filled = self._write_coarse(block, hsa_modules[layer], tokens) if tokens > 0 else 0
+                for name in ("k_coarse", "v_coarse"):
+                    block[name][:, filled:].zero_()
+            block["global_end_index"].fill_(end_token)
+            block["local_end_index"].fill_(tokens)
+        return tokens
 
-    def _install(self, kv_cache, installed, blobs, frame_moves, temporal_freqs, dev, dtype) -> None:
-        """One page-copy launch for every (layer, page, K|V, batch item)."""
+    _PLAN_DTYPE = np.dtype([("chunk", "<i8"), ("src", "<i8"), ("count", "<i8"), ("dst", "<i8"),
+                            ("frame_from", "<i8"), ("frame_to", "<i8")])
+
+    def _install_plan(self, selected_pairs, *, capacity: int, current_start_frame: int):
+        """The install as a table, one row per page that resolves and (at least partly) fits.
+
+        Columns: owning chunk, first source token and token count inside the chunk, first destination token in
+        the cache, and the frame the page was written at / is replayed at.  Pairs that name an unknown chunk or
+        page, or a chunk no tier holds any more, are left out (cache.py:256-271); pages fill the cache front to
+        back and the one that crosses the capacity is cut (cache.py:203-211); the installed span ends at
+        `current_start_frame`, so a page's new frame is that minus the frames still to come (cache.py:273-287).
+        Returns `(None, {})` when no row remains.
+        """
+        blobs: dict = {}
+        rows = []
+        for chunk_id, page_id in selected_pairs:
+            meta = self.chunks[chunk_id] if 0 <= chunk_id < len(self.chunks) else None
+            if meta is None or not 0 <= page_id < len(meta["page_spans"]):
+                continue
+            if chunk_id not in blobs:
+                # a spilled chunk is read page by page from its file; anything else comes as a whole blob
+                held = self.tier.page_reader(chunk_id) or self.tier.get(chunk_id)
+                if held is None:
+                    continue
+                blobs[chunk_id] = held
+            first, last = meta["page_spans"][page_id]
+            rows.append((chunk_id, first, last - first))
+        if not rows:
+            return None, {}
+        plan = np.zeros(len(rows), dtype=self._PLAN_DTYPE)
+        plan["chunk"], plan["src"], plan["count"] = (np.asarray(col, dtype=np.int64) for col in zip(*rows))
+        before = np.cumsum(plan["count"]) - plan["count"]               # tokens installed ahead of each page
+        plan["count"] = np.clip(capacity - before, 0, plan["count"])    # the page that crosses the capacity is cut
+        plan = plan[: int(np.searchsorted(before, capacity, side="left"))] if capacity > 0 else plan[:0]
+        if plan.size == 0:
+            plan = np.zeros(1, dtype=self._PLAN_DTYPE)   # everything resolved but nothing fits: an empty install
+            plan["chunk"] = rows[0][0]
+        plan["dst"] = np.cumsum(plan["count"]) - plan["count"]
+        frame_len = self.frame_seq_length
+        chunk_frame = np.asarray([self.chunks[int(c)]["start_frame"] for c in plan["chunk"]], dtype=np.int64)
+        plan["frame_from"] = chunk_frame + plan["src"] // frame_len
+        plan["frame_to"] = current_start_frame - int(plan["count"].sum()) // frame_len + plan["dst"] // frame_len
+        return plan, blobs
+
+    def _install(self, kv_cache, plan, blobs, temporal_freqs, dev, dtype) -> None:
+        """One page-copy launch for every (layer, page, K|V, batch item) of the plan."""
         k0 = kv_cache[0]["k"]
-        bsz, capacity, heads, head_dim = k0.shape
+        bsz, _, heads, head_dim = k0.shape
         row_elems = heads * head_dim
         esize = k0.element_size()
         nt = temporal_complex_dims(head_dim)
         rot = None
-        if frame_moves is not None:
-            rot = rotation_table(temporal_freqs, [m[1] for m in frame_moves], [m[0] for m in frame_moves], nt)
+        if self.rerope:
+            rot = rotation_table(temporal_freqs, plan["frame_to"].tolist(), plan["frame_from"].tolist(), nt)
 
         main = torch.cuda.current_stream(dev)
         side = self.tier.side_stream(dev)
         staged = []          # keeps promoted pages alive until the copy kernel has consumed them
         promoted = False
         records = []
-        longest = 1
         for layer, block in enumerate(kv_cache):
             for name, rotate in (("k", True), ("v", False)):
                 dst = block[name]
                 if dst.stride(3) != 1 or dst.stride(2) != head_dim or dst.stride(1) != row_elems:
                     raise ValueError("online cache tensors must be contiguous [B, capacity, H, D]")
-                offset = 0
-                for i, (chunk_id, start, end) in enumerate(installed):
-                    src = blobs[chunk_id][name][layer]
-                    n = end - start
-                    page = src[:, start:end]
+                for i, row in enumerate(plan):
+                    n = int(row["count"])
+                    if n == 0:
+                        continue
+                    held, first = blobs[int(row["chunk"])], int(row["src"])
+                    page = held(name, layer, first, first + n) if callable(held) else held[name][layer][:, first: first + n]
                     if not page.is_cuda:
-                        # cold page: page-locked async copy on the side stream
+                        # cold page: page-locked async copy on the side stream; whatever conversion it needs runs
+                        # there too, behind the copy, so that nothing reads the landing buffer early
                         with torch.cuda.stream(side):
-                            hot = torch.empty(page.shape, dtype=page.dtype, device=dev)
-                            hot.copy_(page, non_blocking=True)
+                            landed = torch.empty(page.shape, dtype=page.dtype, device=dev)
+                            landed.copy_(page, non_blocking=True)
+                            page = self._as_cache_rows(landed, dtype, head_dim)
                         promoted = True
-                        page = hot
-                    if page.dtype != dtype:
-                        page = page.to(dtype)
-                    if page.stride(3) != 1 or page.stride(2) != head_dim:
-                        page = page.contiguous()
+                    else:
+                        page = self._as_cache_rows(page, dtype, head_dim)
                     staged.append(page)
                     for b in range(bsz):
                         records.append(_lib.PageCopy(
                             page.data_ptr() + b * page.stride(0) * esize,
-                            dst.data_ptr() + (b * dst.stride(0) + offset * row_elems) * esize,
+                            dst.data_ptr() + (b * dst.stride(0) + int(row["dst"]) * row_elems) * esize,
                             page.stride(1), row_elems, n,
                             i if (rotate and rot is not None) else -1))
-                    longest = max(longest, n)
-                    offset += n
         if promoted:
             main.wait_stream(side)
         arr = (_lib.PageCopy * len(records))(*records)
         dev_records = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev)
         rot_dev = torch.from_numpy(np.ascontiguousarray(rot)).to(dev) if rot is not None else None
         _lib.check(_lib.lib().wa_hkv_gather_pages(
-            dev_records.data_ptr(), len(records), longest, row_elems, head_dim, _lib.dtype_code(dtype),
+            dev_records.data_ptr(), len(records), int(plan["count"].max()), row_elems, head_dim, _lib.dtype_code(dtype),
             _lib.ptr(rot_dev), nt, main.cuda_stream))
         for page in staged:
-            if page.is_cuda:
-                page.record_stream(main)
+            page.record_stream(main)
 
-    def _resolve_pages(self, selected_pairs):
-        """Turn `(chunk, page)` pairs into token spans, skipping anything unresolvable (cache.py:256-271)."""
-        entries, blobs = [], {}
-        for chunk_id, page_id in selected_pairs:
-            if not (0 <= chunk_id < len(self.chunks)):
-                continue
-            spans = self.chunks[chunk_id]["page_spans"]
-            if not (0 <= page_id < len(spans)):
-                continue
-            if chunk_id not in blobs:
-                blob = self.tier.get(chunk_id)
-                if blob is None:
-                    continue
-                blobs[chunk_id] = blob
-            start, end = spans[page_id]
-            entries.append((chunk_id, start, end))
-        return entries, blobs
-
-    def _plan_rerope(self, installed, current_start_frame):
-        """Frame each installed page moves from and to (cache.py:273-287).
-
-        Installed pages occupy consecutive frames ending at `current_start_frame`.
-        """
-        moves = []
-        base = current_start_frame - sum(e - s for _, s, e in installed) // self.frame_seq_length
-        offset = 0
-        for chunk_id, start, end in installed:
-            orig_frame = self.chunks[chunk_id]["start_frame"] + start // self.frame_seq_length
-            moves.append((orig_frame, base + offset // self.frame_seq_length))
-            offset += end - start
-        return moves
+    @staticmethod
+    def _as_cache_rows(page: torch.Tensor, dtype: torch.dtype, head_dim: int) -> torch.Tensor:
+        """`page` in the cache's dtype with head rows contiguous (a no-op for pages stored the way the cache is)."""
+        if page.dtype != dtype:
+            page = page.to(dtype)
+        if page.stride(3) != 1 or page.stride(2) != head_dim:
+            page = page.contiguous()
+        return page
 
     @staticmethod
     def _write_coarse(block: dict, hsa, total_tokens: int) -> int:

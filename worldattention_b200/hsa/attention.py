@@ -163,13 +163,17 @@ def hsa_attention(
     check_status: bool = False,
     k_pooled_cache: torch.Tensor | None = None,
     k_pooled_valid: int = 0,
+    kernel: str = "auto",
 ):
     """Run HSA over `[B, L, H, D]` queries, keys and values (attention.py:153-259).
 
     Beyond the reference signature: `topk_per_head` (int32 `[H]`) selects a fixed number of blocks
     per head instead of the cumulative-mass count; `force_generic` skips the tcgen05 kernel;
     `return_routing` also returns `(index, num, thresholds, used_tuned)`; `check_status` waits for
-    the launch and raises if a bounded wait inside the tcgen05 kernel ran out.
+    the launch and raises if a bounded wait inside the tcgen05 kernel ran out (without it, such a
+    failure raises at the next call on the device, or when the caller runs `_lib.raise_if_failed`
+    after its own synchronisation); `kernel="solo"` picks the one-CTA-per-SM form of the tcgen05
+    kernel instead of the default two-CTAs-per-SM form.
 
     `k_pooled_cache` (float32 `[B, H, ceil(Lkv / block_size), D]`, contiguous) is state the caller
     keeps next to a growing key cache: its first `k_pooled_valid` rows already hold the block means of
@@ -186,12 +190,16 @@ def hsa_attention(
     if q_len <= 0 or kv_len <= 0:
         raise ValueError("q_len and kv_len must be positive")
     dev = _lib.require_cuda(q, k, v, k_coarse, v_coarse)
+    _lib.raise_if_failed(dev)
+    if kernel not in ("auto", "pair", "solo"):
+        raise ValueError(f"kernel must be 'auto', 'pair' or 'solo', got {kernel!r}")
 
     p = _lib.HsaParams()
     p.B, p.H, p.D, p.Lq, p.Lkv = bsz, heads, head_dim, q_len, kv_len
     p.block_size = int(block_size)
     p.tau_min, p.tau_max = float(tau_min), float(tau_max)
-    p.flags = _lib.WA_HSA_FORCE_GENERIC if force_generic else 0
+    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_SOLO if kernel == "solo" else 0)
+    p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     keep = [q, k, v]
     p.q, p.k, p.v = _lib.t4_blhd(q), _lib.t4_blhd(k), _lib.t4_blhd(v)
@@ -267,11 +275,13 @@ def hsa_attention(
     ws = _workspace(dev, need)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     used = ctypes.c_int(0)
-    _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
+    with _lib.device_guard(dev):
+        _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
     if check_status and used.value:
         status = ctypes.c_int(0)
         _lib.check(lib.wa_hsa_status(ctypes.byref(p), ctypes.byref(status), _lib.stream_ptr(dev)))
         if status.value:
+            _lib.status_word(dev).zero_()
             raise RuntimeError(f"tcgen05 HSA kernel gave up at wait site {status.value}; its output is invalid")
 
     if distill.distill_enabled() and torch.is_grad_enabled():

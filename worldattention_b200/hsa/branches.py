@@ -74,7 +74,8 @@ def merge_partials(outs: torch.Tensor, lses: torch.Tensor):
     return out, lse
 
 
-def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, force_generic: bool = False):
+def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, force_generic: bool = False,
+                 kernel: str = "auto"):
     """Both branches over one key shard, in one `wa_hsa_forward` call with the routing supplied.
 
     `index` / `num` are the routing restricted to this shard (`sharded.local_selection`).  Returns
@@ -85,11 +86,13 @@ def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, fo
     import ctypes
     from .attention import _unit_last, _workspace
     dev = _lib.require_cuda(q, k, v, k_coarse, v_coarse, index, num)
+    _lib.raise_if_failed(dev)
     bsz, q_len, heads, head_dim = q.shape
     p = _lib.HsaParams()
     p.B, p.H, p.D, p.Lq, p.Lkv, p.Lc = bsz, heads, head_dim, q_len, k.shape[1], k_coarse.shape[1]
     p.block_size = int(block_size)
-    p.flags = _lib.WA_HSA_FORCE_GENERIC if force_generic else 0
+    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_SOLO if kernel == "solo" else 0)
+    p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     k_coarse, v_coarse = _unit_last(k_coarse.to(v_coarse.dtype)), _unit_last(v_coarse)
     p.q, p.k, p.v = _lib.t4_blhd(q), _lib.t4_blhd(k), _lib.t4_blhd(v)
@@ -109,5 +112,6 @@ def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, fo
     ws = _workspace(dev, lib.wa_hsa_workspace_bytes(ctypes.byref(p)))
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     used = ctypes.c_int(0)
-    _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
+    with _lib.device_guard(dev):
+        _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
     return sparse, lse_s, linear, lse_l, bool(used.value)

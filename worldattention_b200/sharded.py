@@ -72,10 +72,14 @@ def plan_kv_shards(kv_len: int, block_size: int, world: int, page_tokens: int = 
         target = kv_len * r / world
         if page_tokens > 0:
             target = round(target / page_tokens) * page_tokens
-        blk = min(max(int(round(target / block_size)), cuts[-1] // block_size), n_blocks)
-        cuts.append(blk * block_size)
+        blk = min(max(int(round(target / block_size)), -(-cuts[-1] // block_size)), n_blocks)
+        cuts.append(min(blk * block_size, kv_len))   # the last block may be ragged: never cut past the end
     cuts.append(kv_len)
-    return [(cuts[r], max(cuts[r], cuts[r + 1])) for r in range(world)]
+    shards = [(cuts[r], cuts[r + 1]) for r in range(world)]
+    assert shards[0][0] == 0 and shards[-1][1] == kv_len and all(lo <= hi for lo, hi in shards)
+    assert all(shards[r][1] == shards[r + 1][0] for r in range(world - 1))
+    assert all(lo % block_size == 0 or lo == kv_len for lo, _ in shards)
+    return shards
 
 
 def local_selection(index: torch.Tensor, num: torch.Tensor, block_lo: int, block_hi: int):
