@@ -39,8 +39,9 @@ extern "C" {
 /* flags for wa_hsa_forward */
 #define WA_HSA_FORCE_GENERIC 1  /* skip the tcgen05 kernel even when the shape qualifies  */
 #define WA_HSA_REQUIRE_TUNED 2  /* fail with WA_ERR_UNSUPPORTED instead of using the generic kernels */
-#define WA_HSA_KERNEL_SOLO 4    /* tcgen05 kernel as one CTA per SM (three score buffers, two issuing warps)
-                                   instead of the default two CTAs per SM; results agree to rounding   */
+#define WA_HSA_KERNEL_PAIR 4    /* tcgen05 kernel as two CTAs per SM, one work item in flight each, instead of the
+                                   default one CTA per SM (three score buffers, two issuing warps); results
+                                   agree to rounding; measured slower on every benchmark shape            */
 
 /* A strided view of a `[B, L, H, D]` tensor whose last axis is contiguous.  Strides count
  * elements.  `[B, H, N, D]` tensors are described by swapping stride_l / stride_h. */
@@ -264,6 +265,13 @@ int wa_hkv_build_records(const int32_t *top_ids, int layers, int heads, int topk
                          long long src_layer_stride, long long src_token_stride, void *dst_base,
                          long long dst_layer_stride, long long dst_token_stride, int page_tokens, int head_dim,
                          int elem_size, int rotate, wa_page_copy *records, int32_t *missing, void *stream);
+
+/* Promotion of cold pages (the `.to(device)` of cache.py:229-231 for chunks that live in host memory): one
+ * asynchronous host-to-device copy per record of the HOST array `host_records` (src = page-locked host memory,
+ * dst = device memory, `rot` ignored), queued on `stream` -- the caller's side stream.  A record whose token rows
+ * are `row_elems` apart on both sides moves as one block, any other as a two-dimensional copy.  No kernel is
+ * launched and nothing waits: record an event on `stream` afterwards and let the install stream wait for it. */
+int wa_hkv_promote_pages(const wa_page_copy *host_records, int n, int row_elems, int elem_size, void *stream);
 
 /* `copies` is a device array of `n` records; `rotations` device float `[R, nt, 2]`. */
 int wa_hkv_gather_pages(const wa_page_copy *copies, int n, int max_tokens, int row_elems,

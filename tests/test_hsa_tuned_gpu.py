@@ -24,9 +24,9 @@ def wa():
     return pkg
 
 
-@pytest.fixture(params=["pair", "solo"])
+@pytest.fixture(params=["solo", "pair"])
 def kernel(request):
-    """Both forms of the tcgen05 kernel: two CTAs per SM (the default) and one CTA per SM."""
+    """Both forms of the tcgen05 kernel: one CTA per SM (the default) and two CTAs per SM."""
     return request.param
 
 

@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("WORLDATTENTION_B200_LIB") or os.path.join(_HERE, "lib
 
 WA_F32, WA_BF16 = 0, 1
 WA_ERR_ARG, WA_ERR_UNSUPPORTED, WA_ERR_WORKSPACE, WA_ERR_ALIGN, WA_ERR_DEVICE = -1, -2, -3, -4, -5
-WA_HSA_FORCE_GENERIC, WA_HSA_REQUIRE_TUNED, WA_HSA_KERNEL_SOLO = 1, 2, 4
+WA_HSA_FORCE_GENERIC, WA_HSA_REQUIRE_TUNED, WA_HSA_KERNEL_PAIR = 1, 2, 4
 
 
 class Tensor4(C.Structure):
@@ -79,6 +79,7 @@ SIGNATURES = {
     "wa_hkv_score_topk_layers": [_vp, _vp, _i, _i, _i, _i, C.c_longlong, _f, _i, _vp, _vp, _vp, _vp],
     "wa_hkv_build_records": [_vp, _i, _i, _i, _vp, _i, C.c_longlong, C.c_longlong, _vp, C.c_longlong, C.c_longlong,
                              _i, _i, _i, _i, _vp, _vp, _vp],
+    "wa_hkv_promote_pages": [_vp, _i, _i, _i, _vp],
     "wa_hkv_gather_pages": [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
 }
 _RESTYPES = {"wa_last_error": C.c_char_p, "wa_hsa_workspace_bytes": C.c_size_t, "wa_hsa_params_size": C.c_size_t,
@@ -152,7 +153,7 @@ def status_word(device: torch.device) -> torch.Tensor:
     key = torch.device(device).index or 0
     word = _status_words.get(key)
     if word is None:
-        word = torch.zeros(1, dtype=torch.int32).pin_memory()
+        word = torch.zeros(1, dtype=torch.int32, device="cpu").pin_memory()
         _status_words[key] = word
     return word
 

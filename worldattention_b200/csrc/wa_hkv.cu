@@ -408,3 +408,29 @@ extern "C" int wa_hkv_gather_pages(const wa_page_copy *copies, int n, int max_to
             copies, row_elems, head_dim, reinterpret_cast<const float2 *>(rotations), n_temporal);
     return check_launch(what);
 }
+
+// Cold-tier promotion: host-to-device copies of pages that live in page-locked host memory, queued on
+// `stream` (the caller's side stream) one cudaMemcpyAsync per page -- two-dimensional when the token rows
+// of source and destination are not equally spaced.  Nothing is launched and nothing waits here; the
+// caller records an event behind the copies and makes the stream of the install kernel wait for it.
+extern "C" int wa_hkv_promote_pages(const wa_page_copy *host_records, int n, int row_elems, int elem_size, void *stream) {
+    const char *what = "wa_hkv_promote_pages";
+    WA_REQUIRE(host_records || n == 0, WA_ERR_ARG, "%s: null record array", what);
+    WA_REQUIRE(n >= 0 && row_elems > 0 && (elem_size == 2 || elem_size == 4), WA_ERR_ARG, "%s: bad sizes", what);
+    const size_t row_bytes = (size_t)row_elems * elem_size;
+    for (int i = 0; i < n; ++i) {
+        const wa_page_copy &r = host_records[i];
+        if (r.n_tokens <= 0) continue;
+        WA_REQUIRE(r.src && r.dst, WA_ERR_ARG, "%s: record %d has a null address", what, i);
+        WA_REQUIRE(r.src_stride >= row_elems && r.dst_stride >= row_elems, WA_ERR_ARG,
+                   "%s: record %d: token rows overlap (stride below the row length)", what, i);
+        cudaError_t e;
+        if (r.src_stride == row_elems && r.dst_stride == row_elems)
+            e = cudaMemcpyAsync(r.dst, r.src, row_bytes * r.n_tokens, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+        else
+            e = cudaMemcpy2DAsync(r.dst, (size_t)r.dst_stride * elem_size, r.src, (size_t)r.src_stride * elem_size, row_bytes,
+                                  r.n_tokens, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+        if (e != cudaSuccess) return fail((int)e, "%s: copy %d of %d: %s", what, i, n, cudaGetErrorString(e));
+    }
+    return 0;
+}

@@ -986,9 +986,9 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.lse_sparse = p->lse_sparse; kp.lse_linear = p->lse_linear;
 
 
-    // Two forms of the kernel: two CTAs per SM, each with one work item in flight (the default), or one CTA per SM
-    // with three score buffers and two issuing warps.
-    const bool pair = !(p->flags & WA_HSA_KERNEL_SOLO);
+    // Two forms of the kernel: one CTA per SM with three score buffers and two issuing warps (the default), or two
+    // CTAs per SM, each with one work item in flight.
+    const bool pair = (p->flags & WA_HSA_KERNEL_PAIR) != 0;
     if (pair) {
         if ((rc = pair_kernel_prepare())) return rc;
     } else {

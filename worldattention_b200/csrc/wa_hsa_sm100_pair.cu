@@ -644,8 +644,20 @@ int pair_kernel_prepare() {
         cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_pair_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(hsa_fwd_sm100_pair_kernel<HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        // two CTAs need the largest shared-memory carve-out of the SM; ask for it rather than leave it to a heuristic
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(hsa_fwd_sm100_pair_kernel<TILE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(hsa_fwd_sm100_pair_kernel<HALF>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
         attr_set.mark();
+#ifdef WA_DEBUG_OCCUPANCY   // tuning aid: how many CTAs of this kernel the driver places on an SM
+        int n = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, hsa_fwd_sm100_pair_kernel<TILE>, THREADS, SMEM_BYTES);
+        fprintf(stderr, "hsa_fwd_sm100_pair_kernel: %d CTAs per SM\n", n);
+#endif
     }
     return 0;
 }

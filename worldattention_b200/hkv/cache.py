@@ -246,11 +246,11 @@ class HKVCache:
 
         main = torch.cuda.current_stream(dev)
         side = self.tier.side_stream(dev)
-        staged = []          # keeps promoted pages alive until the copy kernel has consumed them
-        promoted = False
-        records = []
+        # pass 1: where every page comes from
+        sources = []         # (layer, name, plan row index, tensor or host page, staging offset in elements or None)
+        staged_elems = 0
         for layer, block in enumerate(kv_cache):
-            for name, rotate in (("k", True), ("v", False)):
+            for name in ("k", "v"):
                 dst = block[name]
                 if dst.stride(3) != 1 or dst.stride(2) != head_dim or dst.stride(1) != row_elems:
                     raise ValueError("online cache tensors must be contiguous [B, capacity, H, D]")
@@ -260,23 +260,53 @@ class HKVCache:
                         continue
                     held, first = blobs[int(row["chunk"])], int(row["src"])
                     page = held(name, layer, first, first + n) if callable(held) else held[name][layer][:, first: first + n]
-                    if not page.is_cuda:
-                        # cold page: page-locked async copy on the side stream; whatever conversion it needs runs
-                        # there too, behind the copy, so that nothing reads the landing buffer early
-                        with torch.cuda.stream(side):
-                            landed = torch.empty(page.shape, dtype=page.dtype, device=dev)
-                            landed.copy_(page, non_blocking=True)
-                            page = self._as_cache_rows(landed, dtype, head_dim)
-                        promoted = True
-                    else:
-                        page = self._as_cache_rows(page, dtype, head_dim)
-                    staged.append(page)
-                    for b in range(bsz):
-                        records.append(_lib.PageCopy(
-                            page.data_ptr() + b * page.stride(0) * esize,
-                            dst.data_ptr() + (b * dst.stride(0) + int(row["dst"]) * row_elems) * esize,
-                            page.stride(1), row_elems, n,
-                            i if (rotate and rot is not None) else -1))
+                    slot = None
+                    if not page.is_cuda and page.dtype == dtype and page.stride(3) == 1 and page.stride(2) == head_dim \
+                            and page.stride(1) == row_elems:
+                        slot = staged_elems                      # cold page in the cache's own layout: one block copy per item
+                        staged_elems += bsz * n * row_elems
+                    sources.append((layer, name, i, page, slot))
+
+        # pass 2: cold pages cross on the side stream into ONE staging buffer; whatever conversion a page needs runs on
+        # that stream too, behind its copy, so that nothing reads a landing buffer early
+        staging = torch.empty((max(staged_elems, 1),), dtype=dtype, device=dev) if staged_elems else None
+        keep_alive = [staging]
+        promote, records = [], []
+        promoted = False
+        for layer, name, i, page, slot in sources:
+            row = plan[i]
+            n = int(row["count"])
+            dst = kv_cache[layer][name]
+            if slot is not None:
+                src_ptr, src_batch, src_stride = staging.data_ptr() + slot * esize, n * row_elems, row_elems
+                for b in range(bsz):
+                    promote.append(_lib.PageCopy(page.data_ptr() + b * page.stride(0) * esize,
+                                                 src_ptr + b * src_batch * esize, row_elems, row_elems, n, -1))
+                keep_alive.append(page)
+            else:
+                if not page.is_cuda:
+                    with torch.cuda.stream(side):
+                        landed = torch.empty(page.shape, dtype=page.dtype, device=dev)
+                        landed.copy_(page, non_blocking=True)
+                        page = self._as_cache_rows(landed, dtype, head_dim)
+                    promoted = True
+                else:
+                    page = self._as_cache_rows(page, dtype, head_dim)
+                keep_alive.append(page)
+                src_ptr, src_batch, src_stride = page.data_ptr(), page.stride(0), page.stride(1)
+            for b in range(bsz):
+                records.append(_lib.PageCopy(
+                    src_ptr + b * src_batch * esize,
+                    dst.data_ptr() + (b * dst.stride(0) + int(row["dst"]) * row_elems) * esize,
+                    src_stride, row_elems, n,
+                    i if (name == "k" and rot is not None) else -1))
+        if promote:
+            arr = (_lib.PageCopy * len(promote))(*promote)
+            side.wait_stream(main)            # the staging block may be recycled memory that the main stream still uses
+            staging.record_stream(side)
+            with _lib.device_guard(dev):
+                _lib.check(_lib.lib().wa_hkv_promote_pages(arr, len(promote), row_elems, esize, side.cuda_stream))
+            promoted = True
         if promoted:
             main.wait_stream(side)
         arr = (_lib.PageCopy * len(records))(*records)
@@ -285,8 +315,9 @@ class HKVCache:
         _lib.check(_lib.lib().wa_hkv_gather_pages(
             dev_records.data_ptr(), len(records), int(plan["count"].max()), row_elems, head_dim, _lib.dtype_code(dtype),
             _lib.ptr(rot_dev), nt, main.cuda_stream))
-        for page in staged:
-            page.record_stream(main)
+        for t in keep_alive:
+            if t is not None and t.is_cuda:
+                t.record_stream(main)
 
     @staticmethod
     def _as_cache_rows(page: torch.Tensor, dtype: torch.dtype, head_dim: int) -> torch.Tensor:

@@ -172,8 +172,8 @@ def hsa_attention(
     `return_routing` also returns `(index, num, thresholds, used_tuned)`; `check_status` waits for
     the launch and raises if a bounded wait inside the tcgen05 kernel ran out (without it, such a
     failure raises at the next call on the device, or when the caller runs `_lib.raise_if_failed`
-    after its own synchronisation); `kernel="solo"` picks the one-CTA-per-SM form of the tcgen05
-    kernel instead of the default two-CTAs-per-SM form.
+    after its own synchronisation); `kernel="pair"` picks the two-CTAs-per-SM form of the tcgen05
+    kernel instead of the default one-CTA-per-SM form.
 
     `k_pooled_cache` (float32 `[B, H, ceil(Lkv / block_size), D]`, contiguous) is state the caller
     keeps next to a growing key cache: its first `k_pooled_valid` rows already hold the block means of
@@ -198,7 +198,7 @@ def hsa_attention(
     p.B, p.H, p.D, p.Lq, p.Lkv = bsz, heads, head_dim, q_len, kv_len
     p.block_size = int(block_size)
     p.tau_min, p.tau_max = float(tau_min), float(tau_max)
-    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_SOLO if kernel == "solo" else 0)
+    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_PAIR if kernel == "pair" else 0)
     p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     keep = [q, k, v]

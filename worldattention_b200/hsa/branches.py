@@ -91,7 +91,7 @@ def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, fo
     p = _lib.HsaParams()
     p.B, p.H, p.D, p.Lq, p.Lkv, p.Lc = bsz, heads, head_dim, q_len, k.shape[1], k_coarse.shape[1]
     p.block_size = int(block_size)
-    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_SOLO if kernel == "solo" else 0)
+    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_PAIR if kernel == "pair" else 0)
     p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     k_coarse, v_coarse = _unit_last(k_coarse.to(v_coarse.dtype)), _unit_last(v_coarse)
