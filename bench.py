@@ -400,7 +400,7 @@ class Work:
                 return self.sharded.gather_heads(out, self.plan) if gather else out
             out = self.sharded.hsa_attention_kv_sharded(self.hsa, self.q, self.k_loc, self.v_loc, self.kc, self.vc,
                                                         kv_len=self.kv_len, shards=self.shards, topk_per_head=self.topk,
-                                                        kernel=self.kernel)
+                                                        kernel=self.kernel, topk_max=int(self.topk_all.max()))
             self.used_tuned = bool(self.sharded.last_call_info.get("used_tuned"))
             return out
 
@@ -613,6 +613,19 @@ def bench_compress(dev, flush, block=128, steps=20):
         t = float(np.mean(ms)) * 1e-3
         out[label] = {"tokens": n, "slots": int(kc.shape[1]), "ms": t * 1e3, "bytes": moved, "gbs": moved / t / 1e9,
                       "frac_of_hbm": moved / t / 1e9 / peak_gbs, "gflop": flops / 1e9, "tflops": flops / t / 1e12}
+        if frames == 3:
+            # the same three segments through the fused append entry point (rows in place: compress only), whose token split
+            # fills the GPU where one CTA per (column tile, segment) leaves half of it idle
+            import worldattention_b200 as wa
+            hsa = wa.hsa.HSAAttention(HEADS, HEAD_DIM, block_size=block, proj_segment_len=FRAME_TOKENS).to(dev)
+            with torch.no_grad():
+                hsa.k_proj_mat.copy_(proj); hsa.v_proj_mat.copy_(proj)
+            kc2, vc2 = torch.empty_like(kc), torch.empty_like(kc)
+            ms2, _ = timed_steps(lambda: hsa.append_kv(k, v, k, v, kc2, vc2, position=0), steps, 3, flush)
+            t2 = float(np.mean(ms2)) * 1e-3
+            close = float((kc2.float() - kc.float()).abs().max())
+            out["chunk_3_segments_fused_append"] = {"ms": t2 * 1e3, "gbs": moved / t2 / 1e9, "frac_of_hbm": moved / t2 / 1e9 / peak_gbs,
+                                                    "max_abs_vs_compress_kv": close}
         del k, v
     out["hbm_peak_gbs"] = peak_gbs
     return out
@@ -911,8 +924,6 @@ def main():
     import torch.distributed as dist
 
     import worldattention_b200 as wa
-    from worldattention_b200.hsa.attention import _compress_blhd
-
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -1028,19 +1039,18 @@ def main():
         """The chunk's rows go from page-locked host memory to the cache tail; their compressed slots follow."""
         k_cache[:, kv_len - new:].copy_(k_rows, non_blocking=True)
         v_cache[:, kv_len - new:].copy_(v_rows, non_blocking=True)
-        kn, vn = _compress_blhd(k_cache[:, kv_len - new:], v_cache[:, kv_len - new:], segment_len=FRAME_TOKENS,
-                                k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, block_size=block)
-        kc_cache[:, kc_cache.shape[1] - kn.shape[1]:].copy_(kn)
-        vc_cache[:, vc_cache.shape[1] - vn.shape[1]:].copy_(vn)
+        # the rows are in place: one launch compresses the three new segments into the tail of the compressed cache
+        hsa.append_kv(k_cache[:, kv_len - new:], v_cache[:, kv_len - new:], k_cache, v_cache, kc_cache, vc_cache,
+                      position=kv_len - new)
 
     # One GPU: the heads are independent, so the step is pipelined over head groups on separate streams -- group g+1's
     # rows cross PCIe while group g computes and group g-1's output returns (the copies are most of the step).
     E2E_GROUPS = int(os.environ.get("WA_E2E_GROUPS", "3")) if mode == "single" else 1
-    e2e_note = "one stream: copy in, append + compress, layer, copy out"
+    e2e_note = "one stream: copy in, compress the new segments (one fused launch), layer, copy out"
     if E2E_GROUPS > 1:
         hg = HEADS // E2E_GROUPS
         e2e_note = (f"{E2E_GROUPS} head groups of {hg} heads, each with its own resident cache tensors and stream: copy in, "
-                    f"append + compress, layer (`hsa_attention` on the group's heads), copy out; groups overlap")
+                    f"compress the new segments (one fused launch), layer (`hsa_attention` on the group's heads), copy out; groups overlap")
         streams = [torch.cuda.Stream(device=dev) for _ in range(E2E_GROUPS)]
         done = [torch.cuda.Event() for _ in range(E2E_GROUPS)]
         arrived = [torch.cuda.Event() for _ in range(E2E_GROUPS)]
@@ -1068,10 +1078,8 @@ def main():
                 d["k"][:, kv_len - new:].copy_(d["k_h"], non_blocking=True)
                 d["v"][:, kv_len - new:].copy_(d["v_h"], non_blocking=True)
                 arrived[g].record(st)
-                kn, vn = _compress_blhd(d["k"][:, kv_len - new:], d["v"][:, kv_len - new:], segment_len=FRAME_TOKENS,
-                                        k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, block_size=block)
-                d["kc"][:, d["kc"].shape[1] - kn.shape[1]:].copy_(kn)
-                d["vc"][:, d["vc"].shape[1] - vn.shape[1]:].copy_(vn)
+                hsa.append_kv(d["k"][:, kv_len - new:], d["v"][:, kv_len - new:], d["k"], d["v"], d["kc"], d["vc"],
+                              position=kv_len - new)
                 out = wa.hsa.hsa_attention(d["q"], d["k"], d["v"], k_coarse=d["kc"], v_coarse=d["vc"],
                                            k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
                                            block_size=block, proj_segment_len=FRAME_TOKENS, topk_per_head=d["topk"],

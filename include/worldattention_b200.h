@@ -117,6 +117,21 @@ int wa_map_to_index(const uint8_t *mask, int B, int H, int Nq, int Nkv, int32_t 
 int wa_route_local_selection(const int32_t *index, const int32_t *num, long long rows, int Nkv, int block_lo,
                              int block_hi, int32_t *local_index, int32_t *local_num, void *stream);
 
+/* Fixed top-k routing over a key cache that is SHARDED across ranks (no reference counterpart).  Step 1, per rank:
+ * score the Nloc key blocks this rank owns (k_pooled_local `[B, H, Nloc, D]`, global ids block_lo ...) against every
+ * query block and keep the best `kcap` of each row as 64-bit keys that sort ascending into (logit descending, global
+ * block id ascending); absent entries are all-ones.  candidates `[B*H*Nq, kcap]`. */
+int wa_route_local_candidates(const float *q_pooled, const float *k_pooled_local, int B, int H, int Nq, int Nloc, int D,
+                              int block_lo, int kcap, unsigned long long *candidates, void *stream);
+/* Step 2, after the ranks have exchanged their candidates (`[W, B*H*Nq, kcap]`, rank-major): per row the k_h =
+ * min(topk_per_head[h], Nkv_total) best of all candidates; of those, the blocks in [block_lo, block_hi) go to
+ * local_index (rebased to the shard, ascending, rows `index_stride` ints apart) and their number to local_num.
+ * Selection is by logit; it equals wa_route_select's fixed-count choice except where distinct logits round to equal
+ * probabilities at the k-th place. */
+int wa_route_merge_candidates(const unsigned long long *candidates, int W, int B, int H, int Nq, int kcap,
+                              const int32_t *topk_per_head, int Nkv_total, int block_lo, int block_hi, int index_stride,
+                              int32_t *local_index, int32_t *local_num, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Attention branches -- wan/modules/hsa/block_sparse_torch.py, block_sparse_triton.py,
  * attention.py
@@ -143,6 +158,23 @@ int wa_compress_kv(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *o
                    int block_size, const void *k_proj, const void *v_proj, int proj_dtype,
                    int proj_rank, int proj_cols, void *stream);
 
+/* The KV-cache write of one forward (causal_model.py:395-413, where the reference first clones the whole layer cache,
+ * :294-299) fused with the compression of the segments it completes (causal_model.py:317-326 -> compress_kv): the
+ * `n_new` new token rows `[B, n_new, H, D]` are read once, stored at rows [position, position + n_new) of the caches
+ * `[B, capacity, H, D]`, and projected into compressed slots position / segment_len * rank ... of `k_coarse` /
+ * `v_coarse` `[B, slots, H, D]`.  `position` is a multiple of segment_len (as token_range_to_coarse requires).
+ * k_new / v_new may BE those cache rows (the rows were written in place, e.g. by a copy from the host): then nothing
+ * is copied and the call only compresses; any other overlap with the caches is not allowed.  bf16, stride_h == D,
+ * H*D a multiple of 128, rank <= 32 (WA_ERR_UNSUPPORTED otherwise: copy the rows and call wa_compress_kv).
+ * `workspace`: wa_kv_append_workspace_bytes(...) bytes, 256-byte aligned, ZEROED before its first use (every call
+ * leaves it ready for the next); calls that share a workspace must not overlap on the GPU. */
+size_t wa_kv_append_workspace_bytes(int B, int n_new, int H, int D, int segment_len, int block_size, int proj_rank);
+int wa_kv_append_compress(const wa_tensor4 *k_new, const wa_tensor4 *v_new, const wa_tensor4 *k_cache,
+                          const wa_tensor4 *v_cache, const wa_tensor4 *k_coarse, const wa_tensor4 *v_coarse, int B,
+                          int n_new, int position, int H, int D, int segment_len, int block_size, const void *k_proj,
+                          const void *v_proj, int proj_dtype, int proj_rank, int proj_cols, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
 /* _linear_branch (attention.py:113-118): dense softmax attention of q over Lc compressed slots.
  * Output rounded to bf16 when `round_output_bf16`; `lse` as above, may be NULL. */
 int wa_linear_branch(const wa_tensor4 *q, const wa_tensor4 *k_coarse, const wa_tensor4 *v_coarse,
@@ -161,6 +193,13 @@ int wa_gate_combine(const wa_tensor4 *q, const wa_tensor4 *sparse, const wa_tens
  * case). */
 int wa_merge_partials(const float *outs, const float *lses, int G, int64_t rows, int D,
                       float *out, float *lse, void *stream);
+
+/* The same merge for the packed records of the KV-sharded exchange (see wa_hsa_params::part_stride): `recv` holds
+ * G x vectors records of `record` floats, [sparse (D) | linear (D) | lse_sparse lse_linear ...], shard-major.  Writes
+ * the merged sparse branch rounded to bf16 (attention.py:253 casts it so) and the merged linear branch in float32,
+ * both `[vectors, D]`: the inputs of wa_gate_combine. */
+int wa_merge_packed(const float *recv, int G, int64_t vectors, int D, int record, void *sparse_out, float *linear_out,
+                    void *stream);
 
 /* hsa_attention (attention.py:153-259), the whole forward in one call. */
 typedef struct wa_hsa_params {
@@ -201,6 +240,15 @@ typedef struct wa_hsa_params {
      * that wa_hsa_status would return is also stored here, so a caller can poll it at its own synchronisation
      * points instead of paying a device-to-host copy per call.  The library never clears it. */
     int32_t *status_mirror;
+    /* Layout of the partial outputs (0 everywhere: the contiguous defaults described above).  part_stride: floats
+     * between the vectors of consecutive (token, head) pairs in part_sparse / part_linear (a multiple of 4, >= D), the
+     * vector of (b, token, head) starting at ((b * Lq + token) * H + head) * part_stride.  lse_stride_token /
+     * lse_stride_head: the normaliser of (b, head, token) sits at (b * Lq + token) * lse_stride_token + head *
+     * lse_stride_head.  With part_linear = part_sparse + D, lse_sparse = part_sparse + 2 D, lse_linear = lse_sparse + 1,
+     * part_stride = lse_stride_head = 2 D + 4 and lse_stride_token = H * part_stride, a (token, head) becomes ONE
+     * record [sparse | linear | lse_s lse_l pad pad] and the rows of a query range one contiguous block: the unit the
+     * KV-sharded path exchanges.  tcgen05 kernel only. */
+    int64_t part_stride, lse_stride_token, lse_stride_head;
 } wa_hsa_params;
 
 /* Bytes of workspace wa_hsa_forward needs for these sizes (pointers in `p` are ignored). */

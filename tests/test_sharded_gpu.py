@@ -23,3 +23,90 @@ def test_local_selection_kernel_matches_the_tensor_formulation():
         got_idx, got_num = sharded.local_selection(torch.from_numpy(index).to(dev()), torch.from_numpy(num).to(dev()), lo, hi)
         assert torch.equal(got_num.cpu(), want_num)
         assert torch.equal(got_idx.cpu(), want_idx)
+
+
+def _emulated_kv_shard_forward(wa, hsa, q, k, v, kc, vc, topk, world, routing, seg):
+    """The KV-sharded forward with the ranks played one after another on ONE GPU: every collective is replaced by the
+    slicing it amounts to (no process group, no kernel waits for another)."""
+    from worldattention_b200 import sharded
+    from worldattention_b200.hsa import branches
+    from worldattention_b200.hsa.routing import block_attention_map, build_block_routing
+    bs = hsa.block_size
+    _, q_len, heads, d = q.shape
+    kv_len = k.shape[1]
+    shards = sharded.plan_kv_shards(kv_len, bs, world, seg)
+    blocks = [-(-(b - a) // bs) for a, b in shards]
+    q_pooled = sharded._pool_blhd(q, bs)
+    pooled = [sharded._pool_blhd(k[:, a:b].contiguous(), bs) if b > a else q_pooled.new_zeros((1, heads, 0, d)) for a, b in shards]
+    nq = q_pooled.shape[2]
+    if routing == "candidates":
+        kmax = int(topk.max())
+        every = torch.stack([sharded.local_candidates(q_pooled, pooled[r], block_lo=sum(blocks[:r]), topk_max=kmax)
+                             for r in range(world)])
+        sel = [sharded.merge_candidates(every, (1, heads, nq), topk_per_head=topk, blocks_total=sum(blocks),
+                                        block_lo=sum(blocks[:r]), block_hi=sum(blocks[:r + 1])) for r in range(world)]
+    else:
+        decided = build_block_routing(block_attention_map(q_pooled, torch.cat(pooled, dim=2)), hsa.tau_min, hsa.tau_max,
+                                      topk_per_head=topk)
+        sel = [sharded.local_selection(decided.index, decided.num, sum(blocks[:r]), sum(blocks[:r + 1])) for r in range(world)]
+    rp, row_plan = sharded.exchange_rows(q_len, world)
+    rec = branches.record_floats(d)
+    r_ = hsa.proj_rank
+    sent = []
+    for r, (a, b) in enumerate(shards):
+        records = torch.full((1, rp * world, heads, rec), float("nan"), device=q.device)
+        records[:, q_len:] = 0
+        s_lo = -(-a // seg)
+        s_hi = -(-b // seg) if r < world - 1 else -(-kv_len // seg)
+        sharded.partial_records(q, k[:, a:b].contiguous(), v[:, a:b].contiguous(), kc[:, s_lo * r_: s_hi * r_].contiguous(),
+                                vc[:, s_lo * r_: s_hi * r_].contiguous(), sel[r][0], sel[r][1], bs, records)
+        assert torch.isfinite(records[:, :, :, :2 * d]).all()
+        sent.append(records[0])
+    out = torch.empty_like(q)
+    for j, (first, count) in enumerate(row_plan):      # what rank j receives: slice j of every rank's records
+        recv = torch.stack([s[j * rp:(j + 1) * rp] for s in sent])                       # [W, rp, H, rec]
+        sparse, linear = branches.merge_packed(recv.view(world, rp * heads, rec), d)
+        if count:
+            out[:, first:first + count] = branches.gate_combine(
+                q[:, first:first + count], sparse.view(1, rp, heads, d)[:, :count], linear.view(1, rp, heads, d)[:, :count],
+                hsa.gate_lin, round_bf16=True)
+    return out, sel
+
+
+@pytest.mark.parametrize("routing,world", [("gather", 3), ("candidates", 3), ("candidates", 8)])
+def test_kv_shard_pipeline_emulated_on_one_gpu(routing, world):
+    """Packed partial records, their merge and the candidate routing against the single-GPU forward."""
+    import worldattention_b200 as wa
+    heads, d, q_len, kv_len, seg, bs = 4, 128, 333, 12480, 1560, 128      # 8 segments: every shard of 3 or 8 owns at least one
+    g = torch.Generator().manual_seed(2)
+    q = (torch.randn(1, q_len, heads, d, generator=g) * 0.6).to(dev(), torch.bfloat16)
+    k = (torch.randn(1, kv_len, heads, d, generator=g) * 0.6).to(dev(), torch.bfloat16)
+    v = torch.randn(1, kv_len, heads, d, generator=g).to(dev(), torch.bfloat16)
+    hsa = wa.hsa.HSAAttention(heads, d, block_size=bs, proj_segment_len=seg).to(dev())
+    wa.hsa_stage.init_hsa_parameters(hsa)
+    with torch.no_grad():
+        hsa.gate_lin.weight.normal_(0, 0.05)
+        kc, vc = hsa.compress_kv_cache(k, v)
+    topk = torch.tensor([3, 17, 1, 8], dtype=torch.int32, device=dev())
+    want, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat,
+                                                       v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=bs,
+                                                       proj_segment_len=seg, topk_per_head=topk, return_routing=True)
+    assert used
+    got, sel = _emulated_kv_shard_forward(wa, hsa, q, k, v, kc, vc, topk, world, routing, seg)
+    # the union of the shards' selections is the single-GPU selection (logits here are far apart: no equal probabilities)
+    nkv = index.shape[-1]
+    from worldattention_b200 import sharded
+    shards = sharded.plan_kv_shards(kv_len, bs, world, seg)
+    blocks = [-(-(b - a) // bs) for a, b in shards]
+    chosen = torch.zeros((1, heads, index.shape[2], nkv), dtype=torch.bool, device=dev())
+    for r in range(world):
+        idx, n = sel[r]
+        slots = torch.arange(idx.shape[-1], device=dev())[None, None, None, :] < n[..., None]
+        ids = (idx.long() + sum(blocks[:r])).clamp(0, nkv - 1)
+        chosen.scatter_(-1, ids, slots | chosen.gather(-1, ids))
+    want_sel = torch.zeros_like(chosen)
+    slots = torch.arange(nkv, device=dev())[None, None, None, :] < num[..., None]
+    want_sel.scatter_(-1, index.long(), slots)
+    assert torch.equal(chosen, want_sel)
+    diff = (got.float() - want.float()).abs()
+    assert float(diff.max()) < 2e-2 and float(diff.mean() / want.float().abs().mean()) < 1e-2

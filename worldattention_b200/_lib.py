@@ -40,6 +40,7 @@ class HsaParams(C.Structure):
         ("lse_sparse", C.c_void_p), ("lse_linear", C.c_void_p),
         ("k_pooled", C.c_void_p), ("k_pooled_valid", C.c_int32), ("reserved2", C.c_int32),
         ("status_mirror", C.c_void_p),
+        ("part_stride", C.c_int64), ("lse_stride_token", C.c_int64), ("lse_stride_head", C.c_int64),
     ]
 
 
@@ -65,12 +66,18 @@ SIGNATURES = {
     "wa_route_select_static": [_vp, _i, _i, _i, _i, _d, _d, _vp, _vp, _vp, _vp, _vp, _vp],
     "wa_map_to_index": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "wa_route_local_selection": [_vp, _vp, C.c_longlong, _i, _i, _i, _vp, _vp, _vp],
+    "wa_route_local_candidates": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "wa_route_merge_candidates": [_vp, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "wa_block_sparse_forward": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _i,
                                 _vp, _vp],
     "wa_compress_kv": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp],
+    "wa_kv_append_workspace_bytes": [_i, _i, _i, _i, _i, _i, _i],
+    "wa_kv_append_compress": [_T4P, _T4P, _T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp,
+                              C.c_size_t, _vp],
     "wa_linear_branch": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "wa_gate_combine": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp],
     "wa_merge_partials": [_vp, _vp, _i, _i64, _i, _vp, _vp, _vp],
+    "wa_merge_packed": [_vp, _i, _i64, _i, _i, _vp, _vp, _vp],
     "wa_hsa_workspace_bytes": [C.POINTER(HsaParams)],
     "wa_hsa_forward": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
     "wa_hsa_status": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
@@ -82,7 +89,7 @@ SIGNATURES = {
     "wa_hkv_promote_pages": [_vp, _i, _i, _i, _vp],
     "wa_hkv_gather_pages": [_vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
 }
-_RESTYPES = {"wa_last_error": C.c_char_p, "wa_hsa_workspace_bytes": C.c_size_t, "wa_hsa_params_size": C.c_size_t,
+_RESTYPES = {"wa_last_error": C.c_char_p, "wa_hsa_workspace_bytes": C.c_size_t, "wa_hsa_params_size": C.c_size_t, "wa_kv_append_workspace_bytes": C.c_size_t,
              "wa_launch_count": C.c_ulonglong}
 
 _lib: Optional[C.CDLL] = None

@@ -289,6 +289,42 @@ __global__ void merge_partials_kernel(const float *__restrict__ outs, const floa
     if (lse && lane == 0) lse[row] = total > 0.f ? m_safe + logf(total) : -INFINITY;
 }
 
+// Merge of packed shard partials.  A record is [sparse (D) | linear (D) | lse_sparse, lse_linear, pad, pad] floats; `recv`
+// holds G x vectors of them (shard-major).  One warp per (token, head) vector: per branch out = sum_g e^(lse_g - LSE) O_g,
+// the sparse branch rounded to bf16 (the reference stores it so), the linear one kept in float32.
+__global__ void __launch_bounds__(256)
+merge_packed_kernel(const float *__restrict__ recv, int G, long long vectors, int D, int record,
+                    __nv_bfloat16 *__restrict__ sparse_out, float *__restrict__ linear_out) {
+    const long long vec = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (vec >= vectors) return;
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int branch = 0; branch < 2; ++branch) {
+        float m = -INFINITY;
+        for (int g = 0; g < G; ++g) m = fmaxf(m, __ldg(recv + ((long long)g * vectors + vec) * record + 2 * D + branch));
+        const float m_safe = m == -INFINITY ? 0.f : m;
+        float total = 0.f;
+        for (int g = 0; g < G; ++g) total += expf(__ldg(recv + ((long long)g * vectors + vec) * record + 2 * D + branch) - m_safe);
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
+        for (int d = lane * 4; d < D; d += 128) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int g = 0; g < G; ++g) {
+                const float *rec = recv + ((long long)g * vectors + vec) * record;
+                const float w = expf(__ldg(rec + 2 * D + branch) - m_safe) * inv;
+                const float4 o = __ldg(reinterpret_cast<const float4 *>(rec + branch * D + d));
+                acc.x = fmaf(w, o.x, acc.x); acc.y = fmaf(w, o.y, acc.y); acc.z = fmaf(w, o.z, acc.z); acc.w = fmaf(w, o.w, acc.w);
+            }
+            if (branch == 0) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+                uint2 packed = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+                *reinterpret_cast<uint2 *>(sparse_out + vec * D + d) = packed;
+            } else {
+                *reinterpret_cast<float4 *>(linear_out + vec * D + d) = acc;
+            }
+        }
+    }
+}
+
 static int check_view(const wa_tensor4 *t, const char *what, const char *name) {
     WA_REQUIRE(t && t->ptr, WA_ERR_ARG, "%s: %s is null", what, name);
     WA_REQUIRE(valid_dtype(t->dtype), WA_ERR_ARG, "%s: %s has bad dtype %d", what, name, t->dtype);
@@ -395,4 +431,21 @@ extern "C" int wa_merge_partials(const float *outs, const float *lses, int G, in
     merge_partials_kernel<<<(unsigned)blocks, warps * 32, 0, (cudaStream_t)stream>>>(outs, lses, G, rows, D, out,
                                                                                      lse);
     return check_launch("wa_merge_partials");
+}
+
+extern "C" int wa_merge_packed(const float *recv, int G, int64_t vectors, int D, int record, void *sparse_out, float *linear_out,
+                               void *stream) {
+    const char *what = "wa_merge_packed";
+    WA_REQUIRE(recv && sparse_out && linear_out, WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(G > 0 && vectors > 0 && D > 0, WA_ERR_ARG, "%s: sizes must be positive", what);
+    WA_REQUIRE(D % 4 == 0 && record % 4 == 0 && record >= 2 * D + 2, WA_ERR_ARG,
+               "%s: D and the record length must be multiples of 4 and a record must hold two vectors and two normalisers", what);
+    WA_REQUIRE(((uintptr_t)recv | (uintptr_t)linear_out) % 16 == 0 && (uintptr_t)sparse_out % 8 == 0, WA_ERR_ALIGN,
+               "%s: buffers must be 16-byte aligned", what);
+    const int warps = 8;
+    const long long blocks = (vectors + warps - 1) / warps;
+    WA_REQUIRE(blocks < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: too many vectors", what);
+    merge_packed_kernel<<<(unsigned)blocks, warps * 32, 0, (cudaStream_t)stream>>>(recv, G, vectors, D, record,
+                                                                                   (__nv_bfloat16 *)sparse_out, linear_out);
+    return check_launch(what);
 }

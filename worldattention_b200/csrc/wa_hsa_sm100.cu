@@ -489,9 +489,9 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const int tokenA = qb * BLK + rowA, tokenB = tokenA + 8;
             const bool okA = rowA < BLK && tokenA < p.Lq, okB = rowB < BLK && tokenB < p.Lq;
             // float32 offsets of this thread's first column pair in the partial outputs, and of the rows' normalisers
-            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * TILE + 2 * c2;
-            const long long partB = partA + 8ll * p.H * TILE;
-            const long long lseA = ((long long)b * p.H + h) * p.Lq + tokenA, lseB = lseA + 8;
+            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
+            const long long partB = partA + 8ll * p.H * p.part_stride;
+            const long long lseA = (long long)b * p.lse_sb + (long long)h * p.lse_sh + (long long)tokenA * p.lse_st, lseB = lseA + 8 * p.lse_st;
             const int gbuf = (sg + n_kv) % S_BUFS;
             float inv_linA = 0.f, inv_linB = 0.f, inv_spA = 0.f, inv_spB = 0.f;
             uint32_t park[32];   // the sparse branch's result: word 2j = row A, 2j + 1 = row B, bf16 pair of step j
@@ -941,7 +941,9 @@ bool hsa_sm100_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, c
     if (!p->part_sparse && (p->out.dtype != WA_BF16 || !p->out.ptr || (uintptr_t)p->out.ptr % 16 || p->out.stride_h % 8 ||
                             p->out.stride_l % 8 || p->out.stride_b % 8))
         return false;
-    if (p->part_sparse && (((uintptr_t)p->part_sparse | (uintptr_t)p->part_linear) % 16)) return false;
+    if (p->part_sparse && (((uintptr_t)p->part_sparse | (uintptr_t)p->part_linear) % 16 || p->part_stride % 4 || p->part_stride < 0 ||
+                           (p->part_stride > 0 && p->part_stride < TILE)))
+        return false;
     if ((long long)p->B * p->H * ceil_div(p->Lq, p->block_size) > (1 << 24)) return false;
     return device_is_sm100() && encode_fn() != nullptr;
 }
@@ -984,6 +986,14 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.scale_log2 = (float)(pow((double)TILE, -0.5) * 1.4426950408889634);
     kp.part_sparse = p->part_sparse; kp.part_linear = p->part_linear;
     kp.lse_sparse = p->lse_sparse; kp.lse_linear = p->lse_linear;
+    // default layouts: contiguous [B, Lq, H, 128] vectors and [B, H, Lq] normalisers; the packed exchange layout of the
+    // KV-sharded path puts both branches of a (token, head) into one record
+    kp.part_stride = p->part_stride > 0 ? p->part_stride : TILE;
+    if (p->lse_stride_token > 0) {
+        kp.lse_st = p->lse_stride_token; kp.lse_sh = p->lse_stride_head; kp.lse_sb = (long long)p->Lq * p->lse_stride_token;
+    } else {
+        kp.lse_st = 1; kp.lse_sh = p->Lq; kp.lse_sb = (long long)p->H * p->Lq;
+    }
 
 
     // Two forms of the kernel: one CTA per SM with three score buffers and two issuing warps (the default), or two

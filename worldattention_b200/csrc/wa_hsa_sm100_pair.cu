@@ -452,8 +452,8 @@ hsa_fwd_sm100_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                             const uint32_t o_addr = tmem_o + ((uint32_t)(warp * 32 + s * 16) << 16);
                             const int rowA = warp * 32 + s * 16 + g, tokenA = qb * BLK + rowA;
                             const bool okA = rowA < BLK && tokenA < p.Lq, okB = rowA + 8 < BLK && tokenA + 8 < p.Lq;
-                            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * TILE + 2 * c2;
-                            const long long partB = partA + 8ll * p.H * TILE;
+                            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
+                            const long long partB = partA + 8ll * p.H * p.part_stride;
 #pragma unroll
                             for (int c = 0; c < 4; ++c) {   // 32 columns at a time
                                 uint32_t ro[16];
@@ -500,11 +500,11 @@ hsa_fwd_sm100_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                     float *lse = phase == 0 ? p.lse_sparse : p.lse_linear;
                     if (lse && c2 == 0) {
                         const int rowA = warp * 32 + s * 16 + g, tokenA = qb * BLK + rowA;
-                        const long long lseA = ((long long)b * p.H + h) * p.Lq + tokenA;
+                        const long long lseA = (long long)b * p.lse_sb + (long long)h * p.lse_sh + (long long)tokenA * p.lse_st;
                         if (rowA < BLK && tokenA < p.Lq)
                             lse[lseA] = lA > 0.f ? (st[s].mA + log2f(lA)) * 0.6931471805599453f : -INFINITY;
                         if (rowA + 8 < BLK && tokenA + 8 < p.Lq)
-                            lse[lseA + 8] = lB > 0.f ? (st[s].mB + log2f(lB)) * 0.6931471805599453f : -INFINITY;
+                            lse[lseA + 8 * p.lse_st] = lB > 0.f ? (st[s].mB + log2f(lB)) * 0.6931471805599453f : -INFINITY;
                     }
                 }
                 if (phase == 0 && n_sel == 0) {   // no selected block: the sparse term is zero and there is no accumulator to read
@@ -512,8 +512,8 @@ hsa_fwd_sm100_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
                         for (int s = 0; s < 2; ++s) {
                             const int rowA = warp * 32 + s * 16 + g, tokenA = qb * BLK + rowA;
-                            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * TILE + 2 * c2;
-                            const long long partB = partA + 8ll * p.H * TILE;
+                            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
+                            const long long partB = partA + 8ll * p.H * p.part_stride;
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 if (rowA < BLK && tokenA < p.Lq) *reinterpret_cast<float2 *>(p.part_sparse + partA + 8 * j) = make_float2(0.f, 0.f);
@@ -542,8 +542,8 @@ hsa_fwd_sm100_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                     const uint32_t lane_addr = (uint32_t)(warp * 32 + s * 16) << 16;
                     const int rowA = warp * 32 + s * 16 + g, rowB = rowA + 8, tokenA = qb * BLK + rowA;
                     const bool okA = rowA < BLK && tokenA < p.Lq, okB = rowB < BLK && tokenA + 8 < p.Lq;
-                    const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * TILE + 2 * c2;
-                    const long long partB = partA + 8ll * p.H * TILE;
+                    const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
+                    const long long partB = partA + 8ll * p.H * p.part_stride;
                     uint32_t gpk[32];
                     if (!p.part_linear) {
 #pragma unroll

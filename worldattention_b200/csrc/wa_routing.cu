@@ -235,10 +235,10 @@ __device__ long long g_route_trace[4096 * 8];
 #define ROUTE_STAMP(i)
 #endif
 
-// One row: out[j] = softmax_j(q . k_j * scale) with float64 dots and sums, each rounded once to float32.
-// `out` may be shared or global memory; `red` holds >= 32 doubles.  Called by every thread of the CTA.
-__device__ __forceinline__ void row_block_attention(const float *__restrict__ q, const float *__restrict__ k, int Nkv, int D,
-                                                    float scale, float *out, double *red, float *bcast) {
+// One row of logits: out[j] = fl32(q . k_j) * scale, the dot accumulated in float64 and rounded once.  `out` may be
+// shared or global memory.  Called by every thread of the CTA; no barrier at the end.
+__device__ __forceinline__ void row_logits(const float *__restrict__ q, const float *__restrict__ k, int Nkv, int D, float scale,
+                                           float *out) {
     const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
     const bool vec = (D & 3) == 0;
     for (int j0 = warp * 8; j0 < Nkv; j0 += nwarps * 8) {   // eight independent dot products in flight
@@ -287,6 +287,14 @@ __device__ __forceinline__ void row_block_attention(const float *__restrict__ q,
         const int u = (lane >> 2) & 7;
         if ((lane & 3) == 0 && j0 + u < Nkv) out[j0 + u] = __fmul_rn((float)t, scale);
     }
+}
+
+// One row: out[j] = softmax_j(q . k_j * scale) with float64 dots and sums, each rounded once to float32.
+// `out` may be shared or global memory; `red` holds >= 32 doubles.  Called by every thread of the CTA.
+__device__ __forceinline__ void row_block_attention(const float *__restrict__ q, const float *__restrict__ k, int Nkv, int D,
+                                                    float scale, float *out, double *red, float *bcast) {
+    const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
+    row_logits(q, k, Nkv, D, scale, out);
     __syncthreads();
     ROUTE_STAMP(1);
 
@@ -641,6 +649,90 @@ namespace wa {
 #endif
 
 // ------------------------------------------------------------------------------------------------
+// Fixed top-k routing over a SHARDED key cache (no reference counterpart: the reference is single-device).
+// Every rank scores only the key blocks it owns and keeps its best `kcap` per row as sortable 64-bit keys
+// (descending logit, then ascending global block id); the ranks exchange those keys; each rank then merges
+// the W * kcap candidates of a row, takes the head's k best and keeps the ones it owns.  Work and traffic per
+// rank fall with the number of ranks, where gathering every pooled key and repeating the whole routing on
+// every rank does not.  Selection is by LOGIT: softmax is monotone, so this is the single-device choice
+// except where distinct logits round to one probability at the k-th place (there the single-device rule
+// orders by block id, this one by logit).
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void sort_keys_smem(unsigned long long *keys, int n_pow2) {   // ascending bitonic sort, whole CTA
+    const int T = blockDim.x;
+    for (int k = 2; k <= n_pow2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < n_pow2; i += T) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long a = keys[i], b = keys[ixj];
+                    const bool up = (i & k) == 0;
+                    if ((a > b) == up) {
+                        keys[i] = b;
+                        keys[ixj] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+route_local_candidates_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int Nq, int Nloc, int n_pow2, int D,
+                              float scale, int block_lo, int kcap, unsigned long long *__restrict__ cand) {
+    extern __shared__ __align__(16) unsigned char cand_smem[];
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(cand_smem);   // n_pow2
+    float *logits = reinterpret_cast<float *>(keys + n_pow2);                       // Nloc
+    const long long row = blockIdx.x;   // (b * H + h) * Nq + i
+    const long long bh = row / Nq;
+    row_logits(qp + row * D, kp + bh * (long long)Nloc * D, Nloc, D, scale, logits);
+    __syncthreads();
+    for (int j = threadIdx.x; j < n_pow2; j += blockDim.x)
+        keys[j] = j < Nloc ? (((unsigned long long)descending_key(logits[j]) << 32) | (unsigned)(block_lo + j))
+                           : 0xFFFFFFFFFFFFFFFFull;
+    __syncthreads();
+    sort_keys_smem(keys, n_pow2);
+    for (int j = threadIdx.x; j < kcap; j += blockDim.x) cand[row * kcap + j] = j < n_pow2 ? keys[j] : 0xFFFFFFFFFFFFFFFFull;
+}
+
+__global__ void __launch_bounds__(256)
+route_merge_candidates_kernel(const unsigned long long *__restrict__ cand, int W, long long rows, int Nq, int H, int kcap,
+                              int n_pow2, const int32_t *__restrict__ topk, int Nkv_total, int block_lo, int block_hi,
+                              int index_stride, int32_t *__restrict__ local_index, int32_t *__restrict__ local_num) {
+    extern __shared__ __align__(16) unsigned char merge_smem[];
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(merge_smem);   // n_pow2 >= W * kcap
+    __shared__ int count;
+    const long long row = blockIdx.x;
+    const int h = (int)((row / Nq) % H);
+    const int n = W * kcap;
+    for (int j = threadIdx.x; j < n_pow2; j += blockDim.x)
+        keys[j] = j < n ? cand[((long long)(j / kcap) * rows + row) * kcap + (j % kcap)] : 0xFFFFFFFFFFFFFFFFull;
+    if (threadIdx.x == 0) count = 0;
+    __syncthreads();
+    sort_keys_smem(keys, n_pow2);
+    const int k = max(0, min(min(topk[h], Nkv_total), n));
+    // the head's k best; the ones this rank owns, in ascending block order (candidates of one rank arrive id-distinct,
+    // so an id appears once)
+    int32_t *out = local_index + row * index_stride;
+    for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        const unsigned id = (unsigned)(keys[j] & 0xFFFFFFFFull);
+        if (keys[j] != 0xFFFFFFFFFFFFFFFFull && (int)id >= block_lo && (int)id < block_hi) {
+            // rank among the owned ones = number of owned selected ids below this one
+            int below = 0;
+            for (int t = 0; t < k; ++t) {
+                const unsigned other = (unsigned)(keys[t] & 0xFFFFFFFFull);
+                below += keys[t] != 0xFFFFFFFFFFFFFFFFull && (int)other >= block_lo && (int)other < block_hi && other < id;
+            }
+            out[below] = (int)id - block_lo;
+            atomicAdd(&count, 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) local_num[row] = count;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Mask -> ascending index list.  One warp per row, ballot-ordered compaction.
 // ------------------------------------------------------------------------------------------------
 __global__ void map_to_index_kernel(const uint8_t *__restrict__ mask, long long rows, int Nkv,
@@ -931,4 +1023,46 @@ extern "C" int wa_route_select_static(const float *block_attn, int B, int H, int
     // Nothing in the scratch has to start at zero: pass A writes every row's Gini term before pass B reads it.
     return route_select_launch(block_attn, B, H, Nq, Nkv, tau_min, tau_max, fixed_num_per_head, index, num, mask,
                                thresholds, scratch, (cudaStream_t)stream);
+}
+
+extern "C" int wa_route_local_candidates(const float *q_pooled, const float *k_pooled_local, int B, int H, int Nq, int Nloc, int D,
+                                         int block_lo, int kcap, unsigned long long *candidates, void *stream) {
+    const char *what = "wa_route_local_candidates";
+    WA_REQUIRE(q_pooled && candidates && (k_pooled_local || Nloc == 0), WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(B > 0 && H > 0 && Nq > 0 && Nloc >= 0 && D > 0 && kcap > 0 && block_lo >= 0, WA_ERR_ARG, "%s: bad sizes", what);
+    int n_pow2 = 1;
+    while (n_pow2 < Nloc) n_pow2 <<= 1;
+    WA_REQUIRE(n_pow2 <= 16384, WA_ERR_UNSUPPORTED, "%s: at most 16384 key blocks per shard, got %d", what, Nloc);
+    const long long rows = (long long)B * H * Nq;
+    WA_REQUIRE(rows < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: too many rows", what);
+    int threads = n_pow2 / 2;
+    threads = threads < 256 ? 256 : (threads > 1024 ? 1024 : threads);
+    const size_t smem = (size_t)n_pow2 * sizeof(unsigned long long) + (size_t)(Nloc > 0 ? Nloc : 1) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(route_local_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
+    }
+    route_local_candidates_kernel<<<(unsigned)rows, threads, smem, (cudaStream_t)stream>>>(
+        q_pooled, k_pooled_local, Nq, Nloc, n_pow2, D, (float)pow((double)D, -0.5), block_lo, kcap, candidates);
+    return check_launch(what);
+}
+
+extern "C" int wa_route_merge_candidates(const unsigned long long *candidates, int W, int B, int H, int Nq, int kcap,
+                                         const int32_t *topk_per_head, int Nkv_total, int block_lo, int block_hi, int index_stride,
+                                         int32_t *local_index, int32_t *local_num, void *stream) {
+    const char *what = "wa_route_merge_candidates";
+    WA_REQUIRE(candidates && topk_per_head && local_index && local_num, WA_ERR_ARG, "%s: null pointer", what);
+    WA_REQUIRE(W > 0 && B > 0 && H > 0 && Nq > 0 && kcap > 0 && Nkv_total > 0 && block_lo >= 0 && block_hi >= block_lo, WA_ERR_ARG,
+               "%s: bad sizes", what);
+    WA_REQUIRE(index_stride >= kcap || index_stride >= block_hi - block_lo, WA_ERR_ARG,
+               "%s: index rows of %d entries cannot hold the selection", what, index_stride);
+    int n_pow2 = 1;
+    while (n_pow2 < W * kcap) n_pow2 <<= 1;
+    WA_REQUIRE(n_pow2 <= 4096, WA_ERR_UNSUPPORTED, "%s: at most 4096 candidates per row, got %d", what, W * kcap);
+    const long long rows = (long long)B * H * Nq;
+    WA_REQUIRE(rows < (1ll << 31), WA_ERR_UNSUPPORTED, "%s: too many rows", what);
+    route_merge_candidates_kernel<<<(unsigned)rows, 256, (size_t)n_pow2 * sizeof(unsigned long long), (cudaStream_t)stream>>>(
+        candidates, W, rows, Nq, H, kcap, n_pow2, topk_per_head, Nkv_total, block_lo, block_hi, index_stride, local_index,
+        local_num);
+    return check_launch(what);
 }

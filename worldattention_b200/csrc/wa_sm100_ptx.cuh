@@ -301,8 +301,9 @@ struct Params {
     long long qsb, qsl, qsh;
     float scale_log2;         // D^-1/2 * log2(e)
     // partial-output mode (KV-sharded multi-GPU): normalised per-branch outputs + natural-log LSE
-    float *part_sparse, *part_linear;   // [B, Lq, H, 128] float32 or null
-    float *lse_sparse, *lse_linear;     // [B, H, Lq]
+    float *part_sparse, *part_linear;   // float32 or null: vector of (b, token, head) at ((b * Lq + token) * H + head) * part_stride
+    float *lse_sparse, *lse_linear;     // float32: value of (b, head, token) at b * lse_sb + head * lse_sh + token * lse_st
+    long long part_stride, lse_sb, lse_sh, lse_st;
 };
 
 struct ItemDesc {

@@ -20,7 +20,7 @@ from .. import _lib
 from . import distill
 
 __all__ = [
-    "HSAAttention", "hsa_attention", "compress_kv", "resolve_backend", "hsa_parameter_names",
+    "HSAAttention", "hsa_attention", "compress_kv", "append_kv", "resolve_backend", "hsa_parameter_names",
     "require_trained_hsa",
 ]
 
@@ -80,6 +80,56 @@ def _compress_blhd(k, v, *, segment_len, k_proj_mat, v_proj_mat, block_size):
         seg, block_size, pk.data_ptr(), pv.data_ptr(), _lib.dtype_code(pk.dtype), pk.shape[0], pk.shape[1],
         _lib.stream_ptr(dev)))
     return out_k, out_v
+
+
+_append_workspaces: dict = {}
+
+
+def append_kv(k_new, v_new, k_cache, v_cache, k_coarse, v_coarse, *, position: int, segment_len: int, k_proj_mat, v_proj_mat,
+              block_size: int) -> None:
+    """Write `n_new` token rows into the K/V cache at `position` and compress the segments they complete, in ONE kernel.
+
+    Stands in for the cache update of the reference's `CausalWanSelfAttention.forward` (causal_model.py:294-327,
+    395-413: clone the layer cache, write the rows, `compress_kv_cache` of the new segments into the coarse cache).
+    All tensors `[B, *, H, D]` bf16; `position` is a multiple of `segment_len`.  `k_new` / `v_new` may be views of the
+    cache rows themselves (rows already in place): then the call only compresses.  Shapes the fused kernel does not cover
+    go through a copy and `compress_kv`.
+    """
+    dev = _lib.require_cuda(k_new, v_new, k_cache, v_cache, k_coarse, v_coarse)
+    bsz, n_new, heads, head_dim = k_new.shape
+    if position % segment_len:
+        raise ValueError(f"rows are appended at segment boundaries, got position={position}, segment_len={segment_len}")
+    if position + n_new > k_cache.shape[1]:
+        raise ValueError("the rows do not fit the cache")
+    pk = k_proj_mat.detach().to(device=dev).contiguous()
+    pv = v_proj_mat.detach().to(device=dev, dtype=pk.dtype).contiguous()
+    lib = _lib.lib()
+    need = lib.wa_kv_append_workspace_bytes(bsz, n_new, heads, head_dim, segment_len, block_size, pk.shape[0])
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _append_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 16), device=dev, dtype=torch.uint8)      # zeroed once; every call leaves it zeroed
+        _append_workspaces[key] = ws
+    with _lib.device_guard(dev):
+        rc = lib.wa_kv_append_compress(
+            _lib.t4_blhd(k_new), _lib.t4_blhd(v_new), _lib.t4_blhd(k_cache), _lib.t4_blhd(v_cache), _lib.t4_blhd(k_coarse),
+            _lib.t4_blhd(v_coarse), bsz, n_new, int(position), heads, head_dim, int(segment_len), int(block_size), pk.data_ptr(),
+            pv.data_ptr(), _lib.dtype_code(pk.dtype), pk.shape[0], pk.shape[1], ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev))
+    if rc == _lib.WA_ERR_UNSUPPORTED:
+        rows_k, rows_v = k_cache[:, position:position + n_new], v_cache[:, position:position + n_new]
+        if rows_k.data_ptr() != k_new.data_ptr():
+            rows_k.copy_(k_new)
+            rows_v.copy_(v_new)
+        per_segment = min(pk.shape[0], math.ceil(segment_len / block_size))      # slots of a whole segment in the cache
+        for s0 in range(0, n_new, segment_len):                                 # the last segment may be short (fewer slots)
+            s1 = min(n_new, s0 + segment_len)
+            kn, vn = _compress_blhd(rows_k[:, s0:s1], rows_v[:, s0:s1], segment_len=segment_len, k_proj_mat=pk, v_proj_mat=pv,
+                                    block_size=block_size)
+            first = (position + s0) // segment_len * per_segment
+            k_coarse[:, first:first + kn.shape[1]].copy_(kn)
+            v_coarse[:, first:first + vn.shape[1]].copy_(vn)
+        return
+    _lib.check(rc)
 
 
 def compress_kv(k, v, *, segment_len: int, k_proj_mat, v_proj_mat, block_size: int):
@@ -353,6 +403,12 @@ class HSAAttention(nn.Module):
             raise ValueError(f"expected [B, L, H, D] tensors, got ndim={k.ndim}")
         return _compress_blhd(k, v, segment_len=self.proj_segment_len, k_proj_mat=self.k_proj_mat,
                               v_proj_mat=self.v_proj_mat, block_size=self.block_size)
+
+    def append_kv(self, k_new, v_new, k_cache, v_cache, k_coarse, v_coarse, *, position: int) -> None:
+        """Write new token rows into the layer's K/V cache and their compressed slots into the coarse cache, fused
+        (see `append_kv`; the reference does this in three steps, causal_model.py:294-327, 395-413)."""
+        append_kv(k_new, v_new, k_cache, v_cache, k_coarse, v_coarse, position=position, segment_len=self.proj_segment_len,
+                  k_proj_mat=self.k_proj_mat, v_proj_mat=self.v_proj_mat, block_size=self.block_size)
 
     def forward(self, q, k, v, k_coarse=None, v_coarse=None):
         return hsa_attention(

@@ -9,7 +9,8 @@ import torch
 
 from .. import _lib
 
-__all__ = ["sparse_branch", "linear_branch", "gate_combine", "merge_partials", "hsa_partials"]
+__all__ = ["sparse_branch", "linear_branch", "gate_combine", "merge_partials", "hsa_partials", "hsa_partials_packed",
+           "merge_packed", "record_floats"]
 
 
 def sparse_branch(q, k, v, index, num, block_size: int, *, kv_len: int | None = None, lse: bool = True,
@@ -44,11 +45,14 @@ def linear_branch(q, k_coarse, v_coarse, *, lse: bool = True):
     return out, row_lse
 
 
-def gate_combine(q, sparse, linear, gate_lin, *, round_bf16: bool):
-    """`sparse + linear * sigmoid(gate_lin(q))` in q's dtype (reference: attention.py:246-259)."""
+def gate_combine(q, sparse, linear, gate_lin, *, round_bf16: bool, out: torch.Tensor | None = None):
+    """`sparse + linear * sigmoid(gate_lin(q))` in q's dtype (reference: attention.py:246-259); `out` may be supplied."""
     dev = _lib.require_cuda(q, sparse, linear)
     bsz, q_len, heads, head_dim = q.shape
-    out = torch.empty((bsz, q_len, heads, head_dim), device=dev, dtype=q.dtype)
+    if out is None:
+        out = torch.empty((bsz, q_len, heads, head_dim), device=dev, dtype=q.dtype)
+    elif tuple(out.shape) != (bsz, q_len, heads, head_dim) or out.dtype != q.dtype or out.stride(3) != 1:
+        raise ValueError("out must be [B, L, H, D] in q's dtype with a contiguous last axis")
     gw = gb = None
     gdt = 0
     if gate_lin is not None:
@@ -115,3 +119,69 @@ def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, fo
     with _lib.device_guard(dev):
         _lib.check(lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev)))
     return sparse, lse_s, linear, lse_l, bool(used.value)
+
+
+def record_floats(head_dim: int) -> int:
+    """Floats in one packed partial record of a (token, head): [sparse (D) | linear (D) | lse_sparse, lse_linear, 0, 0]."""
+    return 2 * head_dim + 4
+
+
+def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int, records: torch.Tensor, *,
+                        kernel: str = "auto") -> bool:
+    """`hsa_partials` writing straight into packed records (`records`: float32 `[B, rows >= Lq, H, 2 D + 4]`, contiguous).
+
+    Both branch outputs and both normalisers of a (token, head) land in one record, so the rows of a query range are
+    one contiguous block -- the unit the KV-sharded path sends to the rank that merges those rows.  Only the tcgen05
+    kernel writes this layout; returns False (nothing launched) where it does not cover the shape, and the caller packs
+    the output of `hsa_partials` itself.
+    """
+    import ctypes
+    from .attention import _unit_last, _workspace
+    dev = _lib.require_cuda(q, k, v, k_coarse, v_coarse, index, num, records)
+    _lib.raise_if_failed(dev)
+    bsz, q_len, heads, head_dim = q.shape
+    rec = record_floats(head_dim)
+    if records.dtype != torch.float32 or not records.is_contiguous() or records.dim() != 4 or records.shape[0] != bsz \
+            or records.shape[1] < q_len or tuple(records.shape[2:]) != (heads, rec) or (bsz > 1 and records.shape[1] != q_len):
+        raise ValueError(f"records must be contiguous float32 [{bsz}, >= {q_len}, {heads}, {rec}]")
+    p = _lib.HsaParams()
+    p.B, p.H, p.D, p.Lq, p.Lkv, p.Lc = bsz, heads, head_dim, q_len, k.shape[1], k_coarse.shape[1]
+    p.block_size = int(block_size)
+    p.flags = _lib.WA_HSA_REQUIRE_TUNED | (_lib.WA_HSA_KERNEL_PAIR if kernel == "pair" else 0)
+    p.status_mirror = _lib.status_word(dev).data_ptr()
+    q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
+    k_coarse, v_coarse = _unit_last(k_coarse.to(v_coarse.dtype)), _unit_last(v_coarse)
+    p.q, p.k, p.v = _lib.t4_blhd(q), _lib.t4_blhd(k), _lib.t4_blhd(v)
+    p.k_coarse, p.v_coarse = _lib.t4_blhd(k_coarse), _lib.t4_blhd(v_coarse)
+    index = index.to(torch.int32).contiguous()
+    num = num.to(torch.int32).contiguous()
+    if index.shape[-1] != -(-k.shape[1] // block_size):
+        raise ValueError("index rows must span exactly this shard's key blocks")
+    p.index_in, p.num_in = index.data_ptr(), num.data_ptr()
+    base = records.data_ptr()
+    p.part_sparse, p.part_linear = base, base + 4 * head_dim
+    p.lse_sparse, p.lse_linear = base + 8 * head_dim, base + 8 * head_dim + 4
+    p.part_stride, p.lse_stride_token, p.lse_stride_head = rec, heads * rec, rec
+    lib = _lib.lib()
+    ws = _workspace(dev, lib.wa_hsa_workspace_bytes(ctypes.byref(p)))
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    used = ctypes.c_int(0)
+    with _lib.device_guard(dev):
+        rc = lib.wa_hsa_forward(ctypes.byref(p), ctypes.byref(used), _lib.stream_ptr(dev))
+    if rc == _lib.WA_ERR_UNSUPPORTED:
+        return False
+    _lib.check(rc)
+    return True
+
+
+def merge_packed(recv: torch.Tensor, head_dim: int):
+    """Merge packed shard partials `recv` (float32 `[G, vectors, 2 D + 4]`): returns the sparse branch rounded to bf16
+    (as the reference stores it) and the linear branch in float32, both `[vectors, D]`."""
+    dev = _lib.require_cuda(recv)
+    g, vectors, rec = recv.shape
+    recv = recv.float().contiguous()
+    sparse = torch.empty((vectors, head_dim), device=dev, dtype=torch.bfloat16)
+    linear = torch.empty((vectors, head_dim), device=dev, dtype=torch.float32)
+    _lib.check(_lib.lib().wa_merge_packed(recv.data_ptr(), g, vectors, head_dim, rec, sparse.data_ptr(), linear.data_ptr(),
+                                          _lib.stream_ptr(dev)))
+    return sparse, linear

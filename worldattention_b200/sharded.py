@@ -23,8 +23,8 @@ import torch.distributed as dist
 from .hsa import branches
 from .hsa.routing import block_attention_map, block_mean_pool, build_block_routing  # noqa: F401
 
-__all__ = ["plan_head_split", "plan_kv_shards", "local_selection", "gather_heads", "all_gather_cat",
-           "merge_partials", "hsa_attention_head_split", "hsa_attention_kv_sharded"]
+__all__ = ["plan_head_split", "plan_kv_shards", "local_selection", "gather_heads", "all_gather_cat", "exchange_rows",
+           "partial_records", "route_candidates", "local_candidates", "merge_candidates", "merge_partials", "hsa_attention_head_split", "hsa_attention_kv_sharded"]
 
 merge_partials = branches.merge_partials
 
@@ -161,12 +161,125 @@ def hsa_attention_head_split(hsa_module, q_local, k_local, v_local, *, k_coarse=
     return out
 
 
+last_call_info: dict = {}     # what the most recent `hsa_attention_kv_sharded` on this process ran (for reporting)
+
+
+def exchange_rows(q_len: int, world: int) -> Tuple[int, List[Tuple[int, int]]]:
+    """Query rows per rank in the exchange of partials: `(rows_per_rank, [(first, count) per rank])`.
+
+    Rank j merges rows `[j * rp, (j + 1) * rp)`; the last slices may be short or empty when `q_len` is not a multiple
+    of the rank count."""
+    rp = -(-q_len // world)
+    return rp, [(r * rp, max(0, min(q_len, (r + 1) * rp) - r * rp)) for r in range(world)]
+
+
+def local_candidates(q_pooled, k_pooled_local, *, block_lo: int, topk_max: int) -> torch.Tensor:
+    """This rank's best `topk_max` key blocks per row as sortable keys: int64 `[B * H * Nq, topk_max]`."""
+    from . import _lib
+    dev = _lib.require_cuda(q_pooled, k_pooled_local)
+    bsz, heads, nq, head_dim = q_pooled.shape
+    nloc = k_pooled_local.shape[2]
+    cand = torch.empty((bsz * heads * nq, topk_max), dtype=torch.int64, device=dev)
+    _lib.check(_lib.lib().wa_route_local_candidates(
+        q_pooled.contiguous().data_ptr(), k_pooled_local.contiguous().data_ptr() if nloc else None, bsz, heads, nq, nloc,
+        head_dim, block_lo, topk_max, cand.data_ptr(), _lib.stream_ptr(dev)))
+    return cand
+
+
+def merge_candidates(every: torch.Tensor, shape, *, topk_per_head, blocks_total: int, block_lo: int, block_hi: int):
+    """From the candidates of all ranks (`[W, rows, topk_max]` int64) the selection restricted to `[block_lo, block_hi)`:
+    `(local_index int32 [B, H, Nq, max(block_hi - block_lo, 1)], local_num int32 [B, H, Nq])`."""
+    from . import _lib
+    dev = _lib.require_cuda(every)
+    bsz, heads, nq = shape
+    world, _, topk_max = every.shape
+    width = max(block_hi - block_lo, 1)
+    local_index = torch.empty((bsz, heads, nq, width), dtype=torch.int32, device=dev)
+    local_num = torch.empty((bsz, heads, nq), dtype=torch.int32, device=dev)
+    topk = topk_per_head.to(device=dev, dtype=torch.int32).contiguous()
+    _lib.check(_lib.lib().wa_route_merge_candidates(
+        every.contiguous().data_ptr(), world, bsz, heads, nq, topk_max, topk.data_ptr(), blocks_total, block_lo, block_hi, width,
+        local_index.data_ptr(), local_num.data_ptr(), _lib.stream_ptr(dev)))
+    return local_index, local_num
+
+
+def route_candidates(q_pooled, k_pooled_local, *, block_lo: int, blocks_total: int, topk_per_head, topk_max: int, group=None):
+    """Fixed top-k routing without gathering the pooled keys: every rank scores its own key blocks, the ranks exchange
+    their `topk_max` best candidates per row (ONE all-gather of 8 bytes per candidate), and each rank keeps, of the
+    global top-k of a row, the blocks it owns.  Returns `(local_index int32 [B, H, Nq, Nloc], local_num int32 [B, H, Nq])`.
+    """
+    bsz, heads, nq, _ = q_pooled.shape
+    nloc = k_pooled_local.shape[2]
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    cand = local_candidates(q_pooled, k_pooled_local, block_lo=block_lo, topk_max=topk_max)
+    if world > 1:
+        every = torch.empty((world,) + tuple(cand.shape), dtype=torch.int64, device=cand.device)
+        dist.all_gather_into_tensor(every, cand, group=group)
+    else:
+        every = cand.unsqueeze(0)
+    return merge_candidates(every, (bsz, heads, nq), topk_per_head=topk_per_head, blocks_total=blocks_total, block_lo=block_lo,
+                            block_hi=block_lo + nloc)
+
+
+def _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel):
+    """Per-branch partial outputs of one rank through the contiguous interface (any shape; SIMT kernels where the
+    tcgen05 kernel does not apply; empty branches where the rank owns no keys or no compressed slots)."""
+    bsz, q_len, heads, head_dim = q.shape
+    has_kv = k_local is not None and k_local.shape[1] > 0
+    has_coarse = kc_local is not None and kc_local.shape[1] > 0
+    if has_kv and has_coarse:
+        return branches.hsa_partials(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel=kernel)
+    if has_kv:
+        o_s, l_s = branches.sparse_branch(q, k_local, v_local, index_l, num_l, bs, kv_len=k_local.shape[1])
+    else:
+        o_s = q.new_zeros((bsz, q_len, heads, head_dim), dtype=torch.float32)
+        l_s = q.new_full((bsz, heads, q_len), float("-inf"), dtype=torch.float32)
+    if has_coarse:
+        o_l, l_l = branches.linear_branch(q, kc_local, vc_local)
+    else:
+        o_l = torch.zeros_like(o_s)
+        l_l = torch.full_like(l_s, float("-inf"))
+    return o_s, l_s, o_l, l_l, False
+
+
+def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records, *, kernel: str = "auto") -> bool:
+    """One rank's partials as packed records (`records`: float32 `[1, rows >= Lq, H, 2 D + 4]`, see
+    `branches.hsa_partials_packed`): written by the tcgen05 kernel where it applies, packed here otherwise.  Rows from
+    Lq on are zeroed so that whoever merges the last slice sees finite numbers.  Returns whether the tcgen05 kernel ran."""
+    _, q_len, heads, head_dim = q.shape
+    if records.shape[1] > q_len:
+        records[:, q_len:].zero_()
+    has_kv = k_local is not None and k_local.shape[1] > 0
+    has_coarse = kc_local is not None and kc_local.shape[1] > 0
+    if has_kv and has_coarse and branches.hsa_partials_packed(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs,
+                                                              records, kernel=kernel):
+        return True
+    o_s, l_s, o_l, l_l, used = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel)
+    records[:, :q_len, :, :head_dim] = o_s
+    records[:, :q_len, :, head_dim:2 * head_dim] = o_l
+    records[:, :q_len, :, 2 * head_dim] = l_s.transpose(1, 2)
+    records[:, :q_len, :, 2 * head_dim + 1] = l_l.transpose(1, 2)
+    records[:, :q_len, :, 2 * head_dim + 2:] = 0
+    return bool(used)
+
+
 def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local, *, kv_len: int,
-                             shards: List[Tuple[int, int]], topk_per_head=None, group=None):
+                             shards: List[Tuple[int, int]], topk_per_head=None, group=None, kernel: str = "auto",
+                             routing: str = "auto", topk_max: Optional[int] = None):
     """KV-sharded forward.  `q` is replicated; `k_local`/`v_local` hold this rank's token range.
 
     `kc_local`/`vc_local` are the compressed slots of the segments this rank owns.  Returns the
     full `[B, Lq, H, D]` output on every rank.
+
+    Routing: `"gather"` all-gathers the pooled keys and repeats the whole decision on every rank (identical to the
+    single-device decision); `"candidates"` (fixed top-k only) lets every rank score its own blocks and exchanges the
+    best `topk_max` per row instead (see `route_candidates`); `"auto"` takes the second for fixed top-k over caches of
+    4096 key blocks or more, where gathering and re-sorting everything would not shrink with the rank count.
+
+    Exchange (B = 1, more than one rank): the tcgen05 kernel writes both branch outputs and both normalisers of a
+    (token, head) into one packed record; ONE all-to-all hands rank j the records of query rows
+    `[j * rp, (j + 1) * rp)` of every shard; rank j merges them, gate-combines its rows, and one all-gather
+    distributes the finished bf16 rows.  Three collectives per forward.
     """
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -175,36 +288,53 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     lo, hi = shards[rank]
     n_local = hi - lo
 
-    # routing: pooled keys are exchanged, the decision is taken identically everywhere
     nq = math.ceil(q_len / bs)
     q_pooled = _pool_blhd(q, bs)
     k_pooled_local = _pool_blhd(k_local, bs) if n_local > 0 else q_pooled.new_zeros((bsz, heads, 0, head_dim))
     blocks_per_rank = [math.ceil((b - a) / bs) for a, b in shards]
-    k_pooled = all_gather_cat(k_pooled_local, 2, group=group, sizes=blocks_per_rank) if world > 1 else k_pooled_local
-    routing = build_block_routing(block_attention_map(q_pooled, k_pooled), hsa_module.tau_min, hsa_module.tau_max,
-                                  topk_per_head=topk_per_head)
+    blocks_total = sum(blocks_per_rank)
     block_lo = sum(blocks_per_rank[:rank])
-    index_l, num_l = local_selection(routing.index, routing.num, block_lo, block_lo + blocks_per_rank[rank])
-
-    # partials over what this rank owns: one fused call when the shard has keys and compressed slots
-    has_kv = n_local > 0
-    has_coarse = kc_local is not None and kc_local.shape[1] > 0
-    if has_kv and has_coarse:
-        o_s, l_s, o_l, l_l, _ = branches.hsa_partials(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
+    by_candidates = topk_per_head is not None and (routing == "candidates" or (routing == "auto" and blocks_total >= 4096))
+    if routing not in ("auto", "gather", "candidates") or (routing == "candidates" and topk_per_head is None):
+        raise ValueError("routing must be 'auto', 'gather' or (with a fixed top-k) 'candidates'")
+    if by_candidates:
+        if topk_max is None:
+            topk_max = int(topk_per_head.max().item())       # a host read: pass topk_max to avoid it
+        index_l, num_l = route_candidates(q_pooled, k_pooled_local, block_lo=block_lo, blocks_total=blocks_total,
+                                          topk_per_head=topk_per_head, topk_max=max(1, min(int(topk_max), blocks_total)),
+                                          group=group)
     else:
-        if has_kv:
-            o_s, l_s = branches.sparse_branch(q, k_local, v_local, index_l, num_l, bs, kv_len=n_local)
-        else:
-            o_s = q.new_zeros((bsz, q_len, heads, head_dim), dtype=torch.float32)
-            l_s = q.new_full((bsz, heads, q_len), float("-inf"), dtype=torch.float32)
-        if has_coarse:
-            o_l, l_l = branches.linear_branch(q, kc_local, vc_local)
-        else:
-            o_l = torch.zeros_like(o_s)
-            l_l = torch.full_like(l_s, float("-inf"))
+        # pooled keys are exchanged, the decision is taken identically everywhere
+        k_pooled = all_gather_cat(k_pooled_local, 2, group=group, sizes=blocks_per_rank) if world > 1 else k_pooled_local
+        decided = build_block_routing(block_attention_map(q_pooled, k_pooled), hsa_module.tau_min, hsa_module.tau_max,
+                                      topk_per_head=topk_per_head)
+        index_l, num_l = local_selection(decided.index, decided.num, block_lo, block_lo + blocks_per_rank[rank])
 
+    rec = branches.record_floats(head_dim)
+    records = None
+    o_s = l_s = o_l = l_l = None
     if world > 1 and bsz == 1:
-        return _merge_by_query_rows(hsa_module, q, o_s, l_s, o_l, l_l, rank, world, group)
+        rp, row_plan = exchange_rows(q_len, world)
+        records = torch.empty((1, rp * world, heads, rec), dtype=torch.float32, device=q.device)
+        used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records, kernel=kernel)
+    else:
+        o_s, l_s, o_l, l_l, used_tuned = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel)
+    last_call_info.update(used_tuned=bool(used_tuned), routing="candidates" if by_candidates else "gather", ranks=world)
+
+    if records is not None:
+        recv = torch.empty_like(records[0])                                  # [W * rp, H, rec]: slice j of every rank
+        dist.all_to_all_single(recv, records[0], group=group)
+        sparse, linear = branches.merge_packed(recv.view(world, rp * heads, rec), head_dim)
+        first, count = row_plan[rank]
+        out_rows = q.new_zeros((rp, heads, head_dim)) if count < rp else q.new_empty((rp, heads, head_dim))
+        if count > 0:
+            done = branches.gate_combine(q[:, first:first + count], sparse.view(1, rp, heads, head_dim)[:, :count],
+                                         linear.view(1, rp, heads, head_dim)[:, :count], hsa_module.gate_lin,
+                                         round_bf16=q.dtype == torch.bfloat16, out=out_rows[:count].unsqueeze(0))
+            assert done.data_ptr() == out_rows.data_ptr()
+        full = q.new_empty((world * rp, heads, head_dim))
+        dist.all_gather_into_tensor(full, out_rows, group=group)
+        return full[:q_len].unsqueeze(0)
 
     # single rank or batched input: merge everything everywhere (rows ordered [B, H, Lq] to match the normalisers)
     def rows(o):
@@ -222,43 +352,6 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     sparse = sparse.to(torch.bfloat16).contiguous()       # the reference stores the sparse branch in bf16
     return branches.gate_combine(q, sparse, linear.contiguous(), hsa_module.gate_lin,
                                  round_bf16=q.dtype == torch.bfloat16)
-
-
-def _merge_by_query_rows(hsa_module, q, o_s, l_s, o_l, l_l, rank: int, world: int, group):
-    """Exchange of the shard partials by query rows (B = 1).
-
-    Rank j receives rows `[j*rp, (j+1)*rp)` of every rank's partial outputs and normalisers (an all-to-all: each
-    rank sends and receives (world-1)/world of one partial set instead of gathering all of them), merges and
-    gate-combines its rows, and the finished bf16 rows are all-gathered.  `o_*`: float32 `[1, Lq, H, D]`,
-    `l_*`: float32 `[1, H, Lq]`.
-    """
-    _, q_len, heads, head_dim = q.shape
-    rp = -(-q_len // world)
-    pad = rp * world - q_len
-
-    def exchange(x):   # [Lq, ...] -> [world, rp, ...]: slice j of every rank
-        if pad:
-            x = torch.cat([x, x.new_zeros((pad,) + tuple(x.shape[1:]))])
-        x = x.contiguous()
-        recv = torch.empty_like(x)
-        dist.all_to_all_single(recv, x, group=group)
-        return recv.view(world, rp, *x.shape[1:])
-
-    os_, ol_ = exchange(o_s[0]), exchange(o_l[0])                  # [W, rp, H, D]
-    ls_, ll_ = exchange(l_s[0].t()), exchange(l_l[0].t())          # [W, rp, H]
-    sp, _ = merge_partials(os_.view(world, rp * heads, head_dim), ls_.reshape(world, rp * heads))
-    li, _ = merge_partials(ol_.view(world, rp * heads, head_dim), ll_.reshape(world, rp * heads))
-    lo = rank * rp
-    n = max(0, min(q_len, lo + rp) - lo)
-    out_rows = q.new_zeros((1, rp, heads, head_dim))
-    if n > 0:
-        sparse = sp.view(1, rp, heads, head_dim)[:, :n].to(torch.bfloat16).contiguous()   # the reference stores this branch in bf16
-        linear = li.view(1, rp, heads, head_dim)[:, :n].contiguous()
-        out_rows[:, :n] = branches.gate_combine(q[:, lo:lo + n], sparse, linear, hsa_module.gate_lin,
-                                                round_bf16=q.dtype == torch.bfloat16)
-    full = q.new_empty((world * rp, heads, head_dim))
-    dist.all_gather_into_tensor(full, out_rows[0].contiguous(), group=group)
-    return full[:q_len].unsqueeze(0)
 
 
 def _pool_blhd(x: torch.Tensor, block_size: int) -> torch.Tensor:
