@@ -516,8 +516,8 @@ def triton_incumbent_child():
     if ref is None:
         print(json.dumps({"unavailable": "reference sources are not staged (oracle/stage_reference.py)"}))
         return
-    hsa_ref, _ = ref
     from wan.modules.hsa.block_sparse_triton import block_sparse_attention
+    from wan.modules.hsa.routing import variable_block_sizes
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     lib = wa._lib.lib()
@@ -533,7 +533,7 @@ def triton_incumbent_child():
         out[:, :, : x.shape[1]] = x.transpose(1, 2)
         return out
     q_t, k_t, v_t = padded(work.q, q_pad), padded(work.k, kv_pad), padded(work.v, kv_pad)
-    sizes = hsa_ref.variable_block_sizes(kv_len, kv_pad, block, dev)
+    sizes = variable_block_sizes(kv_len, kv_pad, block, dev)
 
     def triton_kernel():
         return block_sparse_attention(q_t, k_t, v_t, block_sizes=sizes, q2k_index=index, q2k_num=num)

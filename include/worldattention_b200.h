@@ -263,6 +263,19 @@ int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *stream);
 int wa_hsa_status(const wa_hsa_params *p, int *status, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * q/k preparation of the DiT self-attention -- wan/modules/model.py, wan/modules/causal_model.py
+ * ------------------------------------------------------------------------------------------- */
+
+/* WanRMSNorm (model.py:70-86) over the H*D values of a token, then causal_rope_apply (causal_model.py:34-62), in one
+ * pass.  x / out: `[B, L, H, D]` views of one dtype (float32 or bf16); the L tokens are a (frames, grid_h, grid_w)
+ * grid whose first frame is `start_frame`.  norm_weight `[H*D]` (NULL: no normalisation).  freqs: the reference's
+ * complex128 table as `[freq_rows, D/2, 2]` doubles (NULL: no rotation); of a head's D/2 pairs the first
+ * D/2 - 2 (D/2 / 3) turn with the frame, the next (D/2) / 3 with the row, the last (D/2) / 3 with the column. */
+int wa_qk_norm_rope(const wa_tensor4 *x, const wa_tensor4 *out, int B, int L, int H, int D, const void *norm_weight,
+                    int weight_dtype, float eps, const double *freqs, int freq_rows, int start_frame, int grid_h,
+                    int grid_w, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * HKV retrieval -- pipeline/hkv/retrieval.py, rope.py, cache.py
  * ------------------------------------------------------------------------------------------- */
 

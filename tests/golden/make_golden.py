@@ -247,6 +247,43 @@ def main() -> None:
             rec[f"out_l{layer}_ends"] = np.array([int(blk["global_end_index"]), int(blk["local_end_index"])])
         out[name] = rec
 
+    # ---- q/k RMSNorm + causal RoPE (wan/modules/model.py:29-36, 70-86; wan/modules/causal_model.py:34-62) -------------
+    # The modules that hold these functions import the whole model zoo, so the three definitions are taken out of the
+    # reference's source text and executed on their own: the code that runs is still the reference's.
+    import ast
+    import torch.nn as nn
+
+    def reference_definitions(path, names):
+        text = open(path).read()
+        chunks = [ast.get_source_segment(text, node) for node in ast.parse(text).body
+                  if isinstance(node, (ast.FunctionDef, ast.ClassDef)) and node.name in names]
+        scope = {"torch": torch, "nn": nn, "math": __import__("math")}
+        exec("\n\n".join(chunks), scope)
+        return [scope[n] for n in names]
+
+    rope_params, WanRMSNorm = reference_definitions(os.path.join(args.reference, "wan", "modules", "model.py"),
+                                                    ["rope_params", "WanRMSNorm"])
+    (causal_rope_apply,) = reference_definitions(os.path.join(args.reference, "wan", "modules", "causal_model.py"),
+                                                 ["causal_rope_apply"])
+    torch.manual_seed(77)
+    heads, head_dim, grid, start_frame = 2, 128, (2, 3, 4), 5
+    dim, tokens = heads * head_dim, grid[0] * grid[1] * grid[2]
+    freqs = torch.cat([rope_params(1024, head_dim - 4 * (head_dim // 6)), rope_params(1024, 2 * (head_dim // 6)),
+                       rope_params(1024, 2 * (head_dim // 6))], dim=1)
+    rec = dict(freqs=_np(freqs[:16]), grid=np.array(grid), start_frame=np.array(start_frame), eps=np.array(1e-6))
+    weight = 1.0 + 0.1 * torch.randn(dim)
+    x = torch.randn(1, tokens, dim)
+    for tag, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        norm = WanRMSNorm(dim, eps=1e-6).to(dtype)
+        norm.weight.copy_(weight.to(dtype))
+        xin = x.to(dtype)
+        normed = norm(xin)
+        roped = causal_rope_apply(normed.view(1, tokens, heads, head_dim), torch.tensor([grid]), freqs, start_frame=start_frame)
+        rope_only = causal_rope_apply(xin.view(1, tokens, heads, head_dim), torch.tensor([grid]), freqs, start_frame=start_frame)
+        rec.update({f"x_{tag}": _np(xin), f"weight_{tag}": _np(norm.weight), f"normed_{tag}": _np(normed),
+                    f"roped_{tag}": _np(roped), f"rope_only_{tag}": _np(rope_only)})
+    out["qk_norm_rope"] = rec
+
     for name, arrays in out.items():
         path = os.path.join(args.out, f"{name}.npz")
         np.savez_compressed(path, **arrays)

@@ -152,3 +152,21 @@ def test_hkv_install_matches_reference(golden):
             np.testing.assert_allclose(vc.transpose(0, 2, 1, 3), g[f"out_l{layer}_vc"][:, :slots],
                                        rtol=2 ** -6 if dtype == "bf16" else 1e-5, atol=1e-5)
             assert np.count_nonzero(g[f"out_l{layer}_kc"][:, slots:]) == 0
+
+
+def test_qk_norm_and_causal_rope_match_reference(golden):
+    from oracle import rope_oracle as R
+    g = golden("qk_norm_rope")
+    grid, start = tuple(int(v) for v in g["grid"]), int(g["start_frame"])
+    for tag, tol in (("fp32", 2e-6), ("bf16", 0.0)):
+        normed = R.rms_norm(g[f"x_{tag}"], g[f"weight_{tag}"], float(g["eps"]), tag)
+        if tag == "bf16":      # torch's float32 mean has its own summation order: a value may land one bf16 step away
+            assert np.mean(normed != g[f"normed_{tag}"]) < 2e-3
+            np.testing.assert_allclose(normed, g[f"normed_{tag}"], rtol=2 ** -7, atol=0)
+        else:
+            np.testing.assert_allclose(normed, g[f"normed_{tag}"], rtol=tol, atol=tol)
+        heads = 2
+        rope_only = R.causal_rope_apply(g[f"x_{tag}"].reshape(1, -1, heads, 128), grid, g["freqs"], start, tag)
+        np.testing.assert_allclose(rope_only, g[f"rope_only_{tag}"], rtol=0, atol=tol)       # float64 product: exact after the store
+        roped = R.causal_rope_apply(g[f"normed_{tag}"].reshape(1, -1, heads, 128), grid, g["freqs"], start, tag)
+        np.testing.assert_allclose(roped, g[f"roped_{tag}"], rtol=0, atol=tol)

@@ -98,15 +98,16 @@ def test_kv_shard_pipeline_emulated_on_one_gpu(routing, world):
     from worldattention_b200 import sharded
     shards = sharded.plan_kv_shards(kv_len, bs, world, seg)
     blocks = [-(-(b - a) // bs) for a, b in shards]
-    chosen = torch.zeros((1, heads, index.shape[2], nkv), dtype=torch.bool, device=dev())
+    chosen = torch.zeros((1, heads, index.shape[2], nkv + 1), dtype=torch.bool, device=dev())
     for r in range(world):
         idx, n = sel[r]
         slots = torch.arange(idx.shape[-1], device=dev())[None, None, None, :] < n[..., None]
-        ids = (idx.long() + sum(blocks[:r])).clamp(0, nkv - 1)
-        chosen.scatter_(-1, ids, slots | chosen.gather(-1, ids))
+        # entries past the count are not part of the selection (and may be anything): park them in the spare column
+        ids = torch.where(slots, (idx.long() + sum(blocks[:r])).clamp(0, nkv - 1), torch.full_like(idx.long(), nkv))
+        chosen.scatter_(-1, ids, torch.ones_like(slots))
     want_sel = torch.zeros_like(chosen)
     slots = torch.arange(nkv, device=dev())[None, None, None, :] < num[..., None]
-    want_sel.scatter_(-1, index.long(), slots)
-    assert torch.equal(chosen, want_sel)
+    want_sel.scatter_(-1, torch.where(slots, index.long(), torch.full_like(index.long(), nkv)), torch.ones_like(slots))
+    assert torch.equal(chosen[..., :nkv], want_sel[..., :nkv])
     diff = (got.float() - want.float()).abs()
     assert float(diff.max()) < 2e-2 and float(diff.mean() / want.float().abs().mean()) < 1e-2

@@ -654,9 +654,20 @@ int pair_kernel_prepare() {
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
         attr_set.mark();
 #ifdef WA_DEBUG_OCCUPANCY   // tuning aid: how many CTAs of this kernel the driver places on an SM
-        int n = -1;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, hsa_fwd_sm100_pair_kernel<TILE>, THREADS, SMEM_BYTES);
-        fprintf(stderr, "hsa_fwd_sm100_pair_kernel: %d CTAs per SM\n", n);
+        cudaFuncAttributes fa{};
+        cudaFuncGetAttributes(&fa, hsa_fwd_sm100_pair_kernel<TILE>);
+        int dev = 0, smem_sm = 0, smem_res = 0, regs_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+        cudaDeviceGetAttribute(&smem_res, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+        cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev);
+        fprintf(stderr, "pair kernel: regs %d, static smem %zu, max dyn %d, carveout %d; device: smem/SM %d, reserved/block %d, regs/SM %d\n",
+                fa.numRegs, fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, fa.preferredShmemCarveout, smem_sm, smem_res, regs_sm);
+        for (int bytes : {SMEM_BYTES, 110 * 1024, 100 * 1024, 96 * 1024, 64 * 1024, 32 * 1024}) {
+            int n = -1;
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, hsa_fwd_sm100_pair_kernel<TILE>, THREADS, bytes);
+            fprintf(stderr, "  dynamic smem %d -> %d CTAs per SM\n", bytes, n);
+        }
 #endif
     }
     return 0;
