@@ -318,14 +318,14 @@ def workload_config(name, n_gpus, mode=None):
 # a workload on this rank: tensors, the (possibly sharded) forward, the single-GPU forward for checks
 # ------------------------------------------------------------------------------------------------
 class Work:
-    def __init__(self, name, dev, world, rank, *, shard="auto", kernel="auto", force_generic=False, gather_heads=False,
+    def __init__(self, name, dev, world, rank, *, shard="auto", force_generic=False, gather_heads=False,
                  on_device=False):
         import worldattention_b200 as wa
         from worldattention_b200 import sharded
         from worldattention_b200.hsa.attention import _compress_blhd
         self.wa, self.sharded = wa, sharded
         self.name, self.dev, self.world, self.rank = name, dev, world, rank
-        self.kernel, self.force_generic, self.gather = kernel, force_generic, gather_heads
+        self.force_generic, self.gather = force_generic, gather_heads
         spec = self.spec = WORKLOADS[name]
         self.block = block = spec["block"]
         self.topk_all = draw_topk(spec)
@@ -388,7 +388,7 @@ class Work:
         hsa = self.hsa
         return self.wa.hsa.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat,
                                          gate_lin=hsa.gate_lin, block_size=self.block, proj_segment_len=FRAME_TOKENS,
-                                         topk_per_head=topk, force_generic=self.force_generic, kernel=self.kernel, **extra)
+                                         topk_per_head=topk, force_generic=self.force_generic, **extra)
 
     def forward(self, gather=None):
         gather = self.gather if gather is None else gather
@@ -400,7 +400,7 @@ class Work:
                 return self.sharded.gather_heads(out, self.plan) if gather else out
             out = self.sharded.hsa_attention_kv_sharded(self.hsa, self.q, self.k_loc, self.v_loc, self.kc, self.vc,
                                                         kv_len=self.kv_len, shards=self.shards, topk_per_head=self.topk,
-                                                        kernel=self.kernel, topk_max=int(self.topk_all.max()))
+                                                        topk_max=int(self.topk_all.max()))
             self.used_tuned = bool(self.sharded.last_call_info.get("used_tuned"))
             return out
 
@@ -479,10 +479,10 @@ def max_over_ranks(x: float, dev, world) -> float:
     return float(t.item())
 
 
-def side_workload(name, dev, world, rank, lib, flush, *, steps, kernel, shard="auto", on_device=False, check=True):
+def side_workload(name, dev, world, rank, lib, flush, *, steps, shard="auto", on_device=False, check=True):
     """A second workload measured the same way as the headline (fewer steps): ms/chunk, kernel time, fractions."""
     import torch.distributed as dist
-    work = Work(name, dev, world, rank, shard=shard, kernel=kernel, on_device=on_device)
+    work = Work(name, dev, world, rank, shard=shard, on_device=on_device)
     sparse_f, linear_f, gate_f = work.flops()
     barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if world > 1 else None
     lib.wa_profile_enable(1)
@@ -894,8 +894,6 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "pair", "solo"],
-                    help="form of the tcgen05 kernel: one CTA per SM (solo, the default) or two (pair)")
     ap.add_argument("--no-hkv", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip block64 / long_horizon / compress / triton_incumbent")
     ap.add_argument("--hkv-only", action="store_true", help="run only the HKV retrieval measurements (one GPU)")
@@ -938,7 +936,7 @@ def main():
     spec = WORKLOADS[args.workload]
     block = spec["block"]
 
-    work = Work(args.workload, dev, world, rank, shard=args.shard, kernel=args.kernel, force_generic=args.force_generic,
+    work = Work(args.workload, dev, world, rank, shard=args.shard, force_generic=args.force_generic,
                 gather_heads=args.gather_heads)
     mode, hsa = work.mode, work.hsa
     q, k, v, kc, vc = work.q, work.k, work.v, work.kc, work.vc
@@ -996,7 +994,7 @@ def main():
             with torch.no_grad():
                 return wa.hsa.hsa_attention(qa, ka, va, k_coarse=kca, v_coarse=vca, k_proj_mat=hsa.k_proj_mat,
                                             v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=block,
-                                            proj_segment_len=FRAME_TOKENS, topk_per_head=topk_a, kernel=args.kernel)
+                                            proj_segment_len=FRAME_TOKENS, topk_per_head=topk_a)
         barrier()
         alt_ms, _ = timed_steps(forward_alt, min(args.steps, 30), 3, flush_l2)
         head_split_alt = {"sharding": "head-split, uneven (longest-processing-time on the per-head top-k), no collective",
@@ -1018,7 +1016,7 @@ def main():
                 return wa.hsa.hsa_attention(q, k, v, k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat,
                                             v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin, block_size=block,
                                             proj_segment_len=FRAME_TOKENS, topk_per_head=work.topk,
-                                            k_pooled_cache=k_pool, k_pooled_valid=valid_blocks, kernel=args.kernel)
+                                            k_pooled_cache=k_pool, k_pooled_valid=valid_blocks)
         same = bool(torch.equal(forward_cached(0), forward()))   # fills the buffer; the result does not change
         pc_ms, _ = timed_steps(lambda: forward_cached(valid), min(args.steps, 50), 3, flush_l2)
         same = same and bool(torch.equal(forward_cached(valid), forward()))
@@ -1083,7 +1081,7 @@ def main():
                 out = wa.hsa.hsa_attention(d["q"], d["k"], d["v"], k_coarse=d["kc"], v_coarse=d["vc"],
                                            k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
                                            block_size=block, proj_segment_len=FRAME_TOKENS, topk_per_head=d["topk"],
-                                           force_generic=args.force_generic, kernel=args.kernel)
+                                           force_generic=args.force_generic)
                 d["out"] = out
         # outputs leave after the last group's rows have arrived: on this platform a device-to-host copy that runs
         # against a host-to-device copy slows both down several times
@@ -1124,10 +1122,10 @@ def main():
         del work, q, k, v, kc, vc, forward
         torch.cuda.empty_cache()
         if args.workload != "c5":
-            extras["long_horizon"] = side_workload("c5", dev, world, rank, lib, flush_l2, steps=10, kernel=args.kernel,
+            extras["long_horizon"] = side_workload("c5", dev, world, rank, lib, flush_l2, steps=10,
                                                    shard=args.shard, on_device=True)
         if world == 1 and args.workload != "c2-64":
-            extras["block64"] = side_workload("c2-64", dev, 1, 0, lib, flush_l2, steps=30, kernel=args.kernel)
+            extras["block64"] = side_workload("c2-64", dev, 1, 0, lib, flush_l2, steps=30)
 
     if rank != 0:
         if world > 1:
@@ -1148,8 +1146,7 @@ def main():
             "frac": (achieved / peak_tf) if achieved else None,
             "traffic": NCU_TRAFFIC_BYTES if (used_tuned and world == 1 and args.workload == "c2") else None,
             "peak_source": peak_src,
-            "kernel": (f"hsa_fwd_sm100 (tcgen05: sparse + linear + gate; {'two CTAs' if args.kernel == 'pair' else 'one CTA'} per SM"
-                       f"{'; partial-output mode, rank 0' if mode == 'kv' else ''})"
+            "kernel": (f"hsa_fwd_sm100 (tcgen05: sparse + linear + gate{'; partial-output mode, rank 0' if mode == 'kv' else ''})"
                        if used_tuned else "generic_attention_kernel (SIMT sparse branch)"),
             "kernel_ms": kernel_ms,
             "flops": {"sparse": sparse_f, "linear": linear_f, "gate": gate_f, "counted": flops},

@@ -39,9 +39,6 @@ extern "C" {
 /* flags for wa_hsa_forward */
 #define WA_HSA_FORCE_GENERIC 1  /* skip the tcgen05 kernel even when the shape qualifies  */
 #define WA_HSA_REQUIRE_TUNED 2  /* fail with WA_ERR_UNSUPPORTED instead of using the generic kernels */
-#define WA_HSA_KERNEL_PAIR 4    /* tcgen05 kernel as two CTAs per SM, one work item in flight each, instead of the
-                                   default one CTA per SM (three score buffers, two issuing warps); results
-                                   agree to rounding; measured slower on every benchmark shape            */
 
 /* A strided view of a `[B, L, H, D]` tensor whose last axis is contiguous.  Strides count
  * elements.  `[B, H, N, D]` tensors are described by swapping stride_l / stride_h. */
@@ -167,13 +164,19 @@ int wa_compress_kv(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *o
  * is copied and the call only compresses; any other overlap with the caches is not allowed.  bf16, stride_h == D,
  * H*D a multiple of 128, rank <= 32 (WA_ERR_UNSUPPORTED otherwise: copy the rows and call wa_compress_kv).
  * `workspace`: wa_kv_append_workspace_bytes(...) bytes, 256-byte aligned, ZEROED before its first use (every call
- * leaves it ready for the next); calls that share a workspace must not overlap on the GPU. */
+ * leaves it ready for the next); calls that share a workspace must not overlap on the GPU.  (On an sm_100 device with
+ * 16-byte aligned rows the call runs as a TMA + tcgen05 stream that needs no workspace; the SIMT kernel behind it
+ * splits the tokens of a segment over several CTAs and adds their partial sums through the workspace.) */
 size_t wa_kv_append_workspace_bytes(int B, int n_new, int H, int D, int segment_len, int block_size, int proj_rank);
 int wa_kv_append_compress(const wa_tensor4 *k_new, const wa_tensor4 *v_new, const wa_tensor4 *k_cache,
                           const wa_tensor4 *v_cache, const wa_tensor4 *k_coarse, const wa_tensor4 *v_coarse, int B,
                           int n_new, int position, int H, int D, int segment_len, int block_size, const void *k_proj,
                           const void *v_proj, int proj_dtype, int proj_rank, int proj_cols, void *workspace,
                           size_t workspace_bytes, void *stream);
+
+/* Failure detection for the tcgen05 compress / append stream: every wait inside it is bounded; a wait that ran out
+ * leaves its site code in a word inside the library (sticky; 0 = no failure so far).  Waits for the device. */
+int wa_compress_status(int *status);
 
 /* _linear_branch (attention.py:113-118): dense softmax attention of q over Lc compressed slots.
  * Output rounded to bf16 when `round_output_bf16`; `lse` as above, may be NULL. */

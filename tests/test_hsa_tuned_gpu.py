@@ -24,12 +24,6 @@ def wa():
     return pkg
 
 
-@pytest.fixture(params=["solo", "pair"])
-def kernel(request):
-    """Both forms of the tcgen05 kernel: one CTA per SM (the default) and two CTAs per SM."""
-    return request.param
-
-
 def _draw(rng, shape, scale):
     return O.bf16_round((rng.standard_normal(shape) * scale).astype(np.float32))
 
@@ -43,7 +37,7 @@ def _proj(rank, seg, bs, rng):
     return O.bf16_round(e + 0.002 * rng.standard_normal(e.shape).astype(np.float32))
 
 
-def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=True, coarse_len=None, kernel="auto"):
+def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=True, coarse_len=None):
     rng = np.random.default_rng(seed)
     q = _draw(rng, (bsz, q_len, heads, D), scale)
     k = _draw(rng, (bsz, kv_len, heads, D), scale)
@@ -66,7 +60,7 @@ def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=Tru
     if coarse_len:
         kwargs.update(k_coarse=to_gpu(kc, "bf16"), v_coarse=to_gpu(vc, "bf16"))
     args = [to_gpu(x, "bf16") for x in (q, k, v)]
-    out, (index, num, thr, used) = wa.hsa.hsa_attention(*args, check_status=True, kernel=kernel, **kwargs)
+    out, (index, num, thr, used) = wa.hsa.hsa_attention(*args, check_status=True, **kwargs)
     assert used, "the tcgen05 kernel did not run"
     ref, (index_g, num_g, thr_g, used_g) = wa.hsa.hsa_attention(*args, force_generic=True, **kwargs)
     assert not used_g
@@ -84,34 +78,34 @@ def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=Tru
     return to_np(out), parts
 
 
-def test_small_ragged_shapes_fixed_topk(wa, kernel):
-    _run_case(wa, seed=1, bsz=1, heads=2, q_len=300, kv_len=1170, seg=390, topk=[3, 10], scale=1.0 / math.sqrt(D), kernel=kernel)
+def test_small_ragged_shapes_fixed_topk(wa):
+    _run_case(wa, seed=1, bsz=1, heads=2, q_len=300, kv_len=1170, seg=390, topk=[3, 10], scale=1.0 / math.sqrt(D))
 
 
-def test_cumulative_mass_routing_batch_two(wa, kernel):
-    _run_case(wa, seed=2, bsz=2, heads=3, q_len=520, kv_len=2000, seg=500, topk=None, scale=0.5, kernel=kernel)
+def test_cumulative_mass_routing_batch_two(wa):
+    _run_case(wa, seed=2, bsz=2, heads=3, q_len=520, kv_len=2000, seg=500, topk=None, scale=0.5)
 
 
-def test_supplied_compressed_cache_spanning_several_tiles(wa, kernel):
-    _run_case(wa, seed=3, bsz=1, heads=4, q_len=128, kv_len=900, seg=300, topk=[1, 8, 2, 5], scale=0.3, coarse_len=300, kernel=kernel)
+def test_supplied_compressed_cache_spanning_several_tiles(wa):
+    _run_case(wa, seed=3, bsz=1, heads=4, q_len=128, kv_len=900, seg=300, topk=[1, 8, 2, 5], scale=0.3, coarse_len=300)
 
 
-def test_empty_selection_gives_the_linear_term_only(wa, kernel):
-    out, parts = _run_case(wa, seed=4, bsz=1, heads=2, q_len=200, kv_len=700, seg=350, topk=[0, 4], scale=0.3, kernel=kernel)
+def test_empty_selection_gives_the_linear_term_only(wa):
+    out, parts = _run_case(wa, seed=4, bsz=1, heads=2, q_len=200, kv_len=700, seg=350, topk=[0, 4], scale=0.3)
     assert np.count_nonzero(parts["sparse"][:, :, 0]) == 0
     want = O.as_dtype(parts["linear"][:, :, 0] * parts["gate"][:, :, 0], "bf16")
     assert np.max(np.abs(out[:, :, 0] - want)) < MAX_ABS
 
 
-def test_no_gate_module_uses_sigmoid_of_q(wa, kernel):
-    _run_case(wa, seed=5, bsz=1, heads=2, q_len=256, kv_len=512, seg=256, topk=[2, 4], scale=0.4, gate=False, kernel=kernel)
+def test_no_gate_module_uses_sigmoid_of_q(wa):
+    _run_case(wa, seed=5, bsz=1, heads=2, q_len=256, kv_len=512, seg=256, topk=[2, 4], scale=0.4, gate=False)
 
 
-def test_large_logits_exercise_the_running_max_rescale(wa, kernel):
-    _run_case(wa, seed=6, bsz=1, heads=2, q_len=256, kv_len=2048, seg=512, topk=[16, 9], scale=3.0, kernel=kernel)
+def test_large_logits_exercise_the_running_max_rescale(wa):
+    _run_case(wa, seed=6, bsz=1, heads=2, q_len=256, kv_len=2048, seg=512, topk=[16, 9], scale=3.0)
 
 
-def test_config2_shape_head_adaptive_topk(wa, kernel):
+def test_config2_shape_head_adaptive_topk(wa):
     """Benchmark config 2 at full size: the property checked is agreement with the SIMT path of this library."""
     heads, q_len, kv_len, seg = 12, 4680, 32760, 1560
     g = torch.Generator().manual_seed(1)
@@ -127,7 +121,7 @@ def test_config2_shape_head_adaptive_topk(wa, kernel):
         kc, vc = hsa.compress_kv_cache(k, v)
     kwargs = dict(k_coarse=kc, v_coarse=vc, k_proj_mat=hsa.k_proj_mat, v_proj_mat=hsa.v_proj_mat, gate_lin=hsa.gate_lin,
                   block_size=128, proj_segment_len=seg, topk_per_head=topk, return_routing=True)
-    out, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, check_status=True, kernel=kernel, **kwargs)
+    out, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, check_status=True, **kwargs)
     ref, (index_g, num_g, _, _) = wa.hsa.hsa_attention(q, k, v, force_generic=True, **kwargs)
     assert used and torch.equal(index, index_g) and torch.equal(num, num_g)
     assert torch.equal(num[0, :, 0].cpu(), topk)
@@ -136,7 +130,7 @@ def test_config2_shape_head_adaptive_topk(wa, kernel):
     assert torch.isfinite(out).all()
 
 
-def test_partial_output_mode_merges_to_the_full_result(wa, kernel):
+def test_partial_output_mode_merges_to_the_full_result(wa):
     """Two key shards through the partial-output mode (tcgen05 kernel) merge to the single-pass result."""
     from worldattention_b200 import sharded
     from worldattention_b200.hsa import branches
@@ -163,8 +157,7 @@ def test_partial_output_mode_merges_to_the_full_result(wa, kernel):
         s_lo, s_hi = -(-lo // seg), (-(-hi // seg) if i == 0 else kv_len // seg)   # segments partitioned by start token
         o_s, l_s, o_l, l_l, tuned = branches.hsa_partials(q, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(),
                                                           kc[:, s_lo * r:s_hi * r].contiguous(),
-                                                          vc[:, s_lo * r:s_hi * r].contiguous(), idx_l, num_l, 128,
-                                                          kernel=kernel)
+                                                          vc[:, s_lo * r:s_hi * r].contiguous(), idx_l, num_l, 128)
         assert tuned
         rows = lambda o: o.permute(0, 2, 1, 3).reshape(-1, D)
         outs_s.append(rows(o_s)); lses_s.append(l_s.reshape(-1)); outs_l.append(rows(o_l)); lses_l.append(l_l.reshape(-1))
@@ -200,7 +193,7 @@ def test_head_slices_of_a_resident_cache_equal_the_full_call(wa):
         assert torch.equal(part, full[:, :, hs])
 
 
-def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3, bsz=1, kernel="auto"):
+def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3, bsz=1):
     bs = 64
     rng = np.random.default_rng(seed)
     q = _draw(rng, (bsz, q_len, heads, D), scale)
@@ -216,7 +209,7 @@ def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3, bsz=1,
     kwargs = dict(k_proj_mat=to_gpu(ek, "bf16"), v_proj_mat=to_gpu(ek, "bf16"), gate_lin=lin, block_size=bs,
                   proj_segment_len=seg, topk_per_head=tk, return_routing=True)
     args = [to_gpu(x, "bf16") for x in (q, k, v)]
-    out, (index, num, _, used) = wa.hsa.hsa_attention(*args, check_status=True, kernel=kernel, **kwargs)
+    out, (index, num, _, used) = wa.hsa.hsa_attention(*args, check_status=True, **kwargs)
     ref, (index_g, num_g, _, used_g) = wa.hsa.hsa_attention(*args, force_generic=True, **kwargs)
     assert used and not used_g
     assert torch.equal(index, index_g) and torch.equal(num, num_g)
@@ -228,18 +221,18 @@ def _run_case_64(wa, *, seed, heads, q_len, kv_len, seg, topk, scale=0.3, bsz=1,
     assert max_abs_g < MAX_ABS and mean_rel_g < MEAN_REL, ("vs generic", max_abs_g, mean_rel_g)
 
 
-def test_64_token_blocks_run_on_the_tcgen05_kernel(wa, kernel):
+def test_64_token_blocks_run_on_the_tcgen05_kernel(wa):
     """Routing block size 64 (the reference class's default): a work item is a 64-row query block and a key tile holds
     two selected blocks.  Odd and even counts, an empty head, ragged query and key tails."""
-    _run_case_64(wa, seed=21, heads=3, q_len=500, kv_len=2100, seg=700, topk=[5, 12, 0], kernel=kernel)
-    _run_case_64(wa, seed=24, heads=2, q_len=150, kv_len=1400, seg=700, topk=[7, 2], bsz=2, kernel=kernel)
+    _run_case_64(wa, seed=21, heads=3, q_len=500, kv_len=2100, seg=700, topk=[5, 12, 0])
+    _run_case_64(wa, seed=24, heads=2, q_len=150, kv_len=1400, seg=700, topk=[7, 2], bsz=2)
 
 
-def test_64_token_blocks_with_the_ragged_last_key_block_anywhere_in_the_list(wa, kernel):
+def test_64_token_blocks_with_the_ragged_last_key_block_anywhere_in_the_list(wa):
     """Every key block selected (33 blocks, the last one 40 tokens): the short block sits wherever the routing order puts
     it, in the first or the second half of a tile; cumulative-mass routing for the second case."""
-    _run_case_64(wa, seed=22, heads=2, q_len=200, kv_len=2088, seg=696, topk=[33, 32], kernel=kernel)
-    _run_case_64(wa, seed=23, heads=2, q_len=130, kv_len=1000, seg=500, topk=None, scale=0.5, kernel=kernel)
+    _run_case_64(wa, seed=22, heads=2, q_len=200, kv_len=2088, seg=696, topk=[33, 32])
+    _run_case_64(wa, seed=23, heads=2, q_len=130, kv_len=1000, seg=500, topk=None, scale=0.5)
 
 
 def test_pooled_key_cache_gives_the_same_result_and_only_pools_new_blocks(wa):

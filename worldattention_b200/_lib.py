@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("WORLDATTENTION_B200_LIB") or os.path.join(_HERE, "lib
 
 WA_F32, WA_BF16 = 0, 1
 WA_ERR_ARG, WA_ERR_UNSUPPORTED, WA_ERR_WORKSPACE, WA_ERR_ALIGN, WA_ERR_DEVICE = -1, -2, -3, -4, -5
-WA_HSA_FORCE_GENERIC, WA_HSA_REQUIRE_TUNED, WA_HSA_KERNEL_PAIR = 1, 2, 4
+WA_HSA_FORCE_GENERIC, WA_HSA_REQUIRE_TUNED = 1, 2
 
 
 class Tensor4(C.Structure):
@@ -74,6 +74,7 @@ SIGNATURES = {
     "wa_kv_append_workspace_bytes": [_i, _i, _i, _i, _i, _i, _i],
     "wa_kv_append_compress": [_T4P, _T4P, _T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp,
                               C.c_size_t, _vp],
+    "wa_compress_status": [C.POINTER(C.c_int)],
     "wa_linear_branch": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "wa_gate_combine": [_T4P, _T4P, _T4P, _T4P, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp],
     "wa_merge_partials": [_vp, _vp, _i, _i64, _i, _vp, _vp, _vp],

@@ -5,6 +5,7 @@
 // SIMT kernel: one thread per (head, channel) column, the projection tile broadcast from shared
 // memory, float32 accumulation.
 #include "wa_common.cuh"
+#include "wa_internal.cuh"
 
 namespace wa {
 
@@ -291,6 +292,10 @@ extern "C" int wa_compress_kv(const wa_tensor4 *k, const wa_tensor4 *v, const wa
                longest, proj_cols);
     const int rank_full = proj_rank < ceil_div(longest, block_size) ? proj_rank : ceil_div(longest, block_size);
     WA_REQUIRE(n_seg <= 65535 && 2 * B <= 65535, WA_ERR_UNSUPPORTED, "%s: too many segments", what);
+    // bf16 with contiguous heads on an sm_100 device: the TMA + tcgen05 stream (reads K and V once at HBM speed)
+    if (compress_sm100_supported(k, v, out_k, out_v, nullptr, nullptr, H, D, proj_dtype, proj_cols, rank_full, k_proj, v_proj))
+        return compress_sm100_launch(k, v, out_k, out_v, nullptr, nullptr, 0, B, L, H, D, segment_len, block_size, k_proj, v_proj,
+                                     proj_rank, proj_cols, 0, rank_full, (cudaStream_t)stream);
     const bool fast = k->dtype == WA_BF16 && out_k->dtype == WA_BF16 && k->stride_h == D && v->stride_h == D &&
                       out_k->stride_h == D && (H * D) % 128 == 0 && rank_full <= 32 && k->stride_b == v->stride_b &&
                       k->stride_l == v->stride_l && k->stride_l % 4 == 0 && k->stride_b % 4 == 0 &&
@@ -370,6 +375,18 @@ extern "C" int wa_kv_append_compress(const wa_tensor4 *k_new, const wa_tensor4 *
     WA_REQUIRE(longest <= proj_cols, WA_ERR_ARG, "%s: segment length %d exceeds projection length %d", what, longest, proj_cols);
     WA_REQUIRE(valid_dtype(proj_dtype), WA_ERR_ARG, "%s: bad projection dtype", what);
     const AppendPlan a = append_plan(B, n_new, H, D, segment_len, block_size, proj_rank);
+    {   // the TMA + tcgen05 stream: token tiles are read once and leave twice (cache rows, compressed slots); no workspace
+        const bool in_place = (char *)k_new->ptr == (char *)k_cache->ptr + (size_t)position * k_cache->stride_l * 2 &&
+                              (char *)v_new->ptr == (char *)v_cache->ptr + (size_t)position * v_cache->stride_l * 2 &&
+                              k_new->stride_l == k_cache->stride_l && k_new->stride_b == k_cache->stride_b &&
+                              v_new->stride_l == v_cache->stride_l && v_new->stride_b == v_cache->stride_b;
+        if (k_coarse->stride_b == v_coarse->stride_b && k_coarse->stride_l == v_coarse->stride_l &&
+            compress_sm100_supported(k_new, v_new, k_coarse, v_coarse, in_place ? nullptr : k_cache, in_place ? nullptr : v_cache, H, D,
+                                     proj_dtype, proj_cols, a.rank_full, k_proj, v_proj))
+            return compress_sm100_launch(k_new, v_new, k_coarse, v_coarse, in_place ? nullptr : k_cache, in_place ? nullptr : v_cache,
+                                         position, B, n_new, H, D, segment_len, block_size, k_proj, v_proj, proj_rank, proj_cols,
+                                         position / segment_len * a.slot_stride, a.slot_stride, (cudaStream_t)stream);
+    }
     const wa_tensor4 *views[6] = {k_new, v_new, k_cache, v_cache, k_coarse, v_coarse};
     bool fast = (H * D) % 128 == 0 && a.rank_full <= 32 && a.n_seg * a.split <= 65535 && 2 * B <= 65535;
     for (const wa_tensor4 *t : views)

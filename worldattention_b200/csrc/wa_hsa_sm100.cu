@@ -996,29 +996,20 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     }
 
 
-    // Two forms of the kernel: one CTA per SM with three score buffers and two issuing warps (the default), or two
-    // CTAs per SM, each with one work item in flight.
-    const bool pair = (p->flags & WA_HSA_KERNEL_PAIR) != 0;
-    if (pair) {
-        if ((rc = pair_kernel_prepare())) return rc;
-    } else {
-        static PerDeviceOnce attr_set;
-        if (!attr_set.done()) {
-            cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-            if (e == cudaSuccess)
-                e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-            if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
-            attr_set.mark();
-        }
+    static PerDeviceOnce attr_set;
+    if (!attr_set.done()) {
+        cudaError_t e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(hsa_fwd_sm100_kernel<HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(e));
+        attr_set.mark();
     }
-    const int slots = max_grid() * (pair ? 2 : 1);
-    int grid = n_items < slots ? n_items : slots;
+    int grid = n_items < max_grid() ? n_items : max_grid();
 #ifdef WA_SM100_TRACE
     if (getenv("WA_SM100_ONE_CTA") && grid > max_grid() / 2) grid = max_grid() / 2;   // tuning aid: one CTA per SM
 #endif
     profile_mark(true, stream);
-    if (pair) pair_kernel_launch(blk, grid, stream, tq, tk, tv, tkc, tvc, tw, tout, kp);
-    else if (blk == TILE) hsa_fwd_sm100_kernel<TILE><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
+    if (blk == TILE) hsa_fwd_sm100_kernel<TILE><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     else hsa_fwd_sm100_kernel<HALF><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
     profile_mark(false, stream);
     return check_launch("wa_hsa_forward(tcgen05)");

@@ -108,4 +108,13 @@ bool hsa_sm100_linear_supported(const wa_hsa_params *p, int Lc, const wa_tensor4
 int hsa_sm100_launch_linear(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc, float *linear_out,
                             void *workspace, cudaStream_t stream);
 
+// compress_kv / KV-cache append as a TMA + tcgen05 stream (wa_compress_sm100.cu)
+bool compress_sm100_supported(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *ok, const wa_tensor4 *ov,
+                              const wa_tensor4 *dst_k, const wa_tensor4 *dst_v, int H, int D, int proj_dtype, int proj_cols,
+                              int rank_full, const void *k_proj, const void *v_proj);
+int compress_sm100_launch(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *ok, const wa_tensor4 *ov,
+                          const wa_tensor4 *dst_k, const wa_tensor4 *dst_v, int dst_row0, int B, int L, int H, int D,
+                          int segment_len, int block_size, const void *k_proj, const void *v_proj, int proj_rank, int proj_cols,
+                          int slot0, int slot_stride, cudaStream_t stream);
+
 }  // namespace wa

@@ -213,7 +213,6 @@ def hsa_attention(
     check_status: bool = False,
     k_pooled_cache: torch.Tensor | None = None,
     k_pooled_valid: int = 0,
-    kernel: str = "auto",
 ):
     """Run HSA over `[B, L, H, D]` queries, keys and values (attention.py:153-259).
 
@@ -222,8 +221,7 @@ def hsa_attention(
     `return_routing` also returns `(index, num, thresholds, used_tuned)`; `check_status` waits for
     the launch and raises if a bounded wait inside the tcgen05 kernel ran out (without it, such a
     failure raises at the next call on the device, or when the caller runs `_lib.raise_if_failed`
-    after its own synchronisation); `kernel="pair"` picks the two-CTAs-per-SM form of the tcgen05
-    kernel instead of the default one-CTA-per-SM form.
+    after its own synchronisation).
 
     `k_pooled_cache` (float32 `[B, H, ceil(Lkv / block_size), D]`, contiguous) is state the caller
     keeps next to a growing key cache: its first `k_pooled_valid` rows already hold the block means of
@@ -241,14 +239,12 @@ def hsa_attention(
         raise ValueError("q_len and kv_len must be positive")
     dev = _lib.require_cuda(q, k, v, k_coarse, v_coarse)
     _lib.raise_if_failed(dev)
-    if kernel not in ("auto", "pair", "solo"):
-        raise ValueError(f"kernel must be 'auto', 'pair' or 'solo', got {kernel!r}")
 
     p = _lib.HsaParams()
     p.B, p.H, p.D, p.Lq, p.Lkv = bsz, heads, head_dim, q_len, kv_len
     p.block_size = int(block_size)
     p.tau_min, p.tau_max = float(tau_min), float(tau_max)
-    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_PAIR if kernel == "pair" else 0)
+    p.flags = _lib.WA_HSA_FORCE_GENERIC if force_generic else 0
     p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     keep = [q, k, v]

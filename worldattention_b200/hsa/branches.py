@@ -78,8 +78,7 @@ def merge_partials(outs: torch.Tensor, lses: torch.Tensor):
     return out, lse
 
 
-def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, force_generic: bool = False,
-                 kernel: str = "auto"):
+def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, force_generic: bool = False):
     """Both branches over one key shard, in one `wa_hsa_forward` call with the routing supplied.
 
     `index` / `num` are the routing restricted to this shard (`sharded.local_selection`).  Returns
@@ -95,7 +94,7 @@ def hsa_partials(q, k, v, k_coarse, v_coarse, index, num, block_size: int, *, fo
     p = _lib.HsaParams()
     p.B, p.H, p.D, p.Lq, p.Lkv, p.Lc = bsz, heads, head_dim, q_len, k.shape[1], k_coarse.shape[1]
     p.block_size = int(block_size)
-    p.flags = (_lib.WA_HSA_FORCE_GENERIC if force_generic else 0) | (_lib.WA_HSA_KERNEL_PAIR if kernel == "pair" else 0)
+    p.flags = _lib.WA_HSA_FORCE_GENERIC if force_generic else 0
     p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     k_coarse, v_coarse = _unit_last(k_coarse.to(v_coarse.dtype)), _unit_last(v_coarse)
@@ -126,8 +125,7 @@ def record_floats(head_dim: int) -> int:
     return 2 * head_dim + 4
 
 
-def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int, records: torch.Tensor, *,
-                        kernel: str = "auto") -> bool:
+def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int, records: torch.Tensor) -> bool:
     """`hsa_partials` writing straight into packed records (`records`: float32 `[B, rows >= Lq, H, 2 D + 4]`, contiguous).
 
     Both branch outputs and both normalisers of a (token, head) land in one record, so the rows of a query range are
@@ -147,7 +145,7 @@ def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int
     p = _lib.HsaParams()
     p.B, p.H, p.D, p.Lq, p.Lkv, p.Lc = bsz, heads, head_dim, q_len, k.shape[1], k_coarse.shape[1]
     p.block_size = int(block_size)
-    p.flags = _lib.WA_HSA_REQUIRE_TUNED | (_lib.WA_HSA_KERNEL_PAIR if kernel == "pair" else 0)
+    p.flags = _lib.WA_HSA_REQUIRE_TUNED
     p.status_mirror = _lib.status_word(dev).data_ptr()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v.to(k.dtype))
     k_coarse, v_coarse = _unit_last(k_coarse.to(v_coarse.dtype)), _unit_last(v_coarse)

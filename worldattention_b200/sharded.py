@@ -221,14 +221,14 @@ def route_candidates(q_pooled, k_pooled_local, *, block_lo: int, blocks_total: i
                             block_hi=block_lo + nloc)
 
 
-def _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel):
+def _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs):
     """Per-branch partial outputs of one rank through the contiguous interface (any shape; SIMT kernels where the
     tcgen05 kernel does not apply; empty branches where the rank owns no keys or no compressed slots)."""
     bsz, q_len, heads, head_dim = q.shape
     has_kv = k_local is not None and k_local.shape[1] > 0
     has_coarse = kc_local is not None and kc_local.shape[1] > 0
     if has_kv and has_coarse:
-        return branches.hsa_partials(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel=kernel)
+        return branches.hsa_partials(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
     if has_kv:
         o_s, l_s = branches.sparse_branch(q, k_local, v_local, index_l, num_l, bs, kv_len=k_local.shape[1])
     else:
@@ -242,7 +242,7 @@ def _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, 
     return o_s, l_s, o_l, l_l, False
 
 
-def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records, *, kernel: str = "auto") -> bool:
+def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records) -> bool:
     """One rank's partials as packed records (`records`: float32 `[1, rows >= Lq, H, 2 D + 4]`, see
     `branches.hsa_partials_packed`): written by the tcgen05 kernel where it applies, packed here otherwise.  Rows from
     Lq on are zeroed so that whoever merges the last slice sees finite numbers.  Returns whether the tcgen05 kernel ran."""
@@ -251,10 +251,9 @@ def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs,
         records[:, q_len:].zero_()
     has_kv = k_local is not None and k_local.shape[1] > 0
     has_coarse = kc_local is not None and kc_local.shape[1] > 0
-    if has_kv and has_coarse and branches.hsa_partials_packed(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs,
-                                                              records, kernel=kernel):
+    if has_kv and has_coarse and branches.hsa_partials_packed(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records):
         return True
-    o_s, l_s, o_l, l_l, used = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel)
+    o_s, l_s, o_l, l_l, used = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
     records[:, :q_len, :, :head_dim] = o_s
     records[:, :q_len, :, head_dim:2 * head_dim] = o_l
     records[:, :q_len, :, 2 * head_dim] = l_s.transpose(1, 2)
@@ -264,8 +263,8 @@ def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs,
 
 
 def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local, *, kv_len: int,
-                             shards: List[Tuple[int, int]], topk_per_head=None, group=None, kernel: str = "auto",
-                             routing: str = "auto", topk_max: Optional[int] = None):
+                             shards: List[Tuple[int, int]], topk_per_head=None, group=None, routing: str = "auto",
+                             topk_max: Optional[int] = None):
     """KV-sharded forward.  `q` is replicated; `k_local`/`v_local` hold this rank's token range.
 
     `kc_local`/`vc_local` are the compressed slots of the segments this rank owns.  Returns the
@@ -316,9 +315,9 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     if world > 1 and bsz == 1:
         rp, row_plan = exchange_rows(q_len, world)
         records = torch.empty((1, rp * world, heads, rec), dtype=torch.float32, device=q.device)
-        used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records, kernel=kernel)
+        used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records)
     else:
-        o_s, l_s, o_l, l_l, used_tuned = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, kernel)
+        o_s, l_s, o_l, l_l, used_tuned = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
     last_call_info.update(used_tuned=bool(used_tuned), routing="candidates" if by_candidates else "gather", ranks=world)
 
     if records is not None:
