@@ -96,6 +96,23 @@ def test_block_mean_pool_matches_oracle_and_reference(wa, golden):
     assert torch.allclose(pooled[0, 0, 2], torch.ones(2, device=dev()))
 
 
+def test_block_mean_pool_token_major_rows_take_the_tma_stream(wa):
+    # [B, L, H, D] storage (what the forward hands over) is pooled by the TMA kernel; same bits as the oracle
+    rng = np.random.default_rng(11)
+    for B, L, H, D, bs in ((2, 700, 3, 64, 128), (1, 768, 2, 128, 128), (2, 333, 4, 32, 64), (1, 4680, 12, 128, 64),
+                           (1, 130, 1, 64, 128), (2, 333, 8, 32, 64), (2, 700, 4, 64, 128), (1, 130, 4, 64, 128),
+                           (1, 4680, 12, 128, 128), (3, 64, 2, 128, 32)):
+        nb = -(-L // bs)
+        x = (rng.standard_normal((B, nb * bs, H, D)) * 3).astype(np.float32)
+        x[:, L:] = 7.0                                            # padding rows must not reach the means
+        xt = to_gpu(x, "bf16")                                    # [B, tokens, H, D]
+        got = wa.hsa.block_mean_pool(xt.permute(0, 2, 1, 3), L, nb, bs)
+        xh = to_np(xt.float()).transpose(0, 2, 1, 3).copy()
+        xh[:, :, L:] = 0.0
+        want = O.block_mean_pool(xh, L, nb, bs, "bf16")
+        assert np.array_equal(to_np(got.float()), want), (B, L, H, D, bs)
+
+
 def test_block_attention_map_matches_oracle(wa, golden):
     g = golden("block_map")
     got = to_np(wa.hsa.block_attention_map(to_gpu(g["q_pooled"]), to_gpu(g["k_pooled"])))

@@ -6,6 +6,8 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <cstdlib>
+#include <utility>
 #include <cstdarg>
 #include <cstdio>
 
@@ -51,6 +53,40 @@ struct PerDeviceOnce {
         if (dev >= 0 && dev < 64) bits.fetch_or(1ull << dev, std::memory_order_release);
     }
 };
+
+// Programmatic dependent launch: the kernel may be placed on the SMs while the kernel before it on the stream is
+// still draining, runs its set-up (barriers, tensor memory, descriptor prefetch) and then blocks in
+// `pdl_wait()` until that kernel has completed and its writes are visible.  A kernel launched this way must reach
+// `pdl_wait()` in every thread block before it touches anything the stream's earlier work reads or writes.
+// WA_B200_PDL=0 in the environment turns the attribute off (plain stream order), for timing comparisons.
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("WA_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 #define WA_REQUIRE(cond, code, ...)                    \
     do {                                               \

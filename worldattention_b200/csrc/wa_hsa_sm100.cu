@@ -152,12 +152,15 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_init(&bar->o_free, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x >= 64 && threadIdx.x < 64 + TILE) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
     if (warp == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)),
                      "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // everything above is private to this CTA; from here on the routing kernel's results (work order, selection,
+    // converted gate weights) are read, so the launch before this one has to be complete
+    pdl_wait();
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + TILE) bar->bias[threadIdx.x - 64] = (p.has_gate && p.gate_bias) ? p.gate_bias[threadIdx.x - 64] : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -1009,9 +1012,12 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     if (getenv("WA_SM100_ONE_CTA") && grid > max_grid() / 2) grid = max_grid() / 2;   // tuning aid: one CTA per SM
 #endif
     profile_mark(true, stream);
-    if (blk == TILE) hsa_fwd_sm100_kernel<TILE><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
-    else hsa_fwd_sm100_kernel<HALF><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tkc, tvc, tw, tout, kp);
+    cudaError_t le = blk == TILE ? launch_dependent(hsa_fwd_sm100_kernel<TILE>, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tq, tk,
+                                                    tv, tkc, tvc, tw, tout, kp)
+                                 : launch_dependent(hsa_fwd_sm100_kernel<HALF>, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, tq, tk,
+                                                    tv, tkc, tvc, tw, tout, kp);
     profile_mark(false, stream);
+    if (le != cudaSuccess) return fail((int)le, "wa_hsa_forward(tcgen05): %s", cudaGetErrorString(le));
     return check_launch("wa_hsa_forward(tcgen05)");
 }
 

@@ -36,7 +36,18 @@ __device__ inline void schedule_items(const int32_t *num, int n_items, int Nkv, 
         *error_flag = 0;
     }
     __syncthreads();
-    for (int i = tid; i < n_items; i += T) atomicAdd(&hist[top - max(0, min(num[i], top))], 1);
+    // the counts were written by other CTAs of this launch: read them past L1, and only once when they fit in registers
+    constexpr int KEEP = 4;
+    int bin_of[KEEP];
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+        const int i = tid + u * T;
+        bin_of[u] = i < n_items ? top - max(0, min(__ldcg(num + i), top)) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u)
+        if (bin_of[u] >= 0) atomicAdd(&hist[bin_of[u]], 1);
+    for (int i = tid + KEEP * T; i < n_items; i += T) atomicAdd(&hist[top - max(0, min(__ldcg(num + i), top))], 1);
     __syncthreads();
     // exclusive prefix over the bins: a contiguous run of bins per thread, then a block scan of the run totals
     const int b0 = tid * per;
@@ -67,7 +78,10 @@ __device__ inline void schedule_items(const int32_t *num, int n_items, int Nkv, 
         base += c;
     }
     __syncthreads();
-    for (int i = tid; i < n_items; i += T) order[atomicAdd(&hist[top - max(0, min(num[i], top))], 1)] = i;
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u)
+        if (bin_of[u] >= 0) order[atomicAdd(&hist[bin_of[u]], 1)] = tid + u * T;
+    for (int i = tid + KEEP * T; i < n_items; i += T) order[atomicAdd(&hist[top - max(0, min(__ldcg(num + i), top))], 1)] = i;
 }
 
 // Elements [first, first + count) of the gate weight -> bf16 (it is an MMA operand) and of the bias -> float32.
@@ -107,6 +121,11 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
 bool hsa_sm100_linear_supported(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc);
 int hsa_sm100_launch_linear(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const wa_tensor4 *vc, float *linear_out,
                             void *workspace, cudaStream_t stream);
+
+// block-mean pooling as a TMA stream (wa_pool_sm100.cu); y may be null; out_blocks_y = rows per (batch, head) of py
+bool pool_sm100_supported(const wa_tensor4 *x, const wa_tensor4 *y, int H, int D, int block_size);
+int pool_sm100_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int out_blocks_y, int B, int H,
+                      int D, int block_size, cudaStream_t stream, int *zero, int n_zero);
 
 // compress_kv / KV-cache append as a TMA + tcgen05 stream (wa_compress_sm100.cu)
 bool compress_sm100_supported(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *ok, const wa_tensor4 *ov,

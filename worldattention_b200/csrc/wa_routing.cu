@@ -222,13 +222,13 @@ pool_warp_kernel(View4 x, int L, int H, int D, int block_size, int num_blocks, i
 constexpr int SCORE_THREADS = 256;
 
 #ifdef WA_ROUTE_TRACE   // tuning aid: per-CTA phase timestamps (ns) of the fused routing kernel
-__device__ long long g_route_trace[4096 * 8];
+__device__ long long g_route_trace[4096 * 12];
 #define ROUTE_STAMP(i)                                                                         \
     do {                                                                                       \
         if (threadIdx.x == 0 && blockIdx.x < 4096) {                                           \
             long long t_;                                                                      \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
-            g_route_trace[blockIdx.x * 8 + (i)] = t_;                                          \
+            g_route_trace[blockIdx.x * 12 + (i)] = t_;                                          \
         }                                                                                      \
     } while (0)
 #else
@@ -507,6 +507,9 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
     // CTAs are dealt to the SMs round-robin, so CTAs b, b + sm_count, ... tend to share an SM: give them
     // neighbouring rows (same head, same pooled keys) so that their key reads can meet in L1
     const long long row = (long long)(blockIdx.x % sm_count) * slots + blockIdx.x / sm_count;
+    // No early release of the attention kernel here: its CTAs, once resident and waiting, slowed the tail of this
+    // kernel (the per-head count and the work order are a few CTAs' work) by about 5 us.
+    pdl_wait();                 // pooled means and zeroed counters come from the launch before
     if (row >= (long long)B * H * Nq) return;
     const long long bh = row / Nq;
     const int h = (int)(bh % H);
@@ -563,15 +566,12 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
     ROUTE_STAMP(3);
     {
         int32_t *idx = index + row * Nkv;
-        float *srow = sorted + row * Nkv;
         double acc = 0.0;
         for (int m = tid; m < Nkv; m += T) {
             const int id = (int)(keys[m] & 0xFFFFFFFFull);
-            const float pm = probs[id];
             idx[m] = id;
-            srow[m] = pm;
             const float w = __fsub_rn((float)(Nkv + 1), __fmul_rn(2.0f, (float)(m + 1)));
-            acc += (double)__fmul_rn(w, pm);
+            acc += (double)__fmul_rn(w, probs[id]);
         }
         acc = warp_sum_d(acc);
         if (lane == 0) red[warp] = acc;
@@ -580,6 +580,32 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
             double t = 0.0;
             for (int w = 0; w < nwarps; ++w) t += red[w];
             gini_rows[row] = __fdiv_rn((float)t, (float)Nkv);
+        }
+        __syncthreads();
+    }
+    if (!fixed_num) {
+        // What the count needs of this row once the head's threshold is known: for every sorted position the
+        // cumulative mass before it, fl32(fl64 prefix including m) - p_m.  A contiguous run of positions per thread,
+        // float64 run totals scanned over the CTA (lane order inside a warp, warp order across warps).
+        float *crow = sorted + row * Nkv;
+        const int chunk = (Nkv + T - 1) / T;
+        const int m0 = min(Nkv, tid * chunk), m1 = min(Nkv, m0 + chunk);
+        double local = 0.0;
+        for (int m = m0; m < m1; ++m) local += (double)probs[(int)(keys[m] & 0xFFFFFFFFull)];
+        double incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) red[warp] = incl;
+        __syncthreads();
+        double run = incl - local;
+        for (int w = 0; w < warp; ++w) run += red[w];
+        for (int m = m0; m < m1; ++m) {
+            const float pm = probs[(int)(keys[m] & 0xFFFFFFFFull)];
+            run += (double)pm;
+            crow[m] = __fsub_rn((float)run, pm);
         }
     }
 
@@ -596,34 +622,86 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
 
     const float thr = head_threshold(gini_rows, B, H, Nq, h, tau_min, tau_span, red, &bcast);
     if (tid == 0) thresholds[h] = thr;
-
-    for (int r = warp; r < rows_per_head; r += nwarps) {
-        const int bb = r / Nq, ii = r % Nq;
-        const long long rid = ((long long)bb * H + h) * Nq + ii;
-        if (fixed_num) {
-            if (lane == 0) num[rid] = max(0, min(fixed_num[h], Nkv));
-            continue;
-        }
-        // float64 cumulative mass: a contiguous chunk per lane, lane totals prefixed in lane order
-        const float *p = sorted + rid * Nkv;
-        const int chunk = (Nkv + 31) / 32;
-        const int m0 = min(Nkv, lane * chunk), m1 = min(Nkv, m0 + chunk);
-        double local = 0.0;
-        for (int m = m0; m < m1; ++m) local += (double)__ldcg(p + m);
-        double run = 0.0;
-        for (int w = 0; w < 32; ++w) {
-            const double t = __shfl_sync(0xffffffffu, local, w);
-            if (w < lane) run += t;
-        }
-        int kept = 0;
-        for (int m = m0; m < m1; ++m) {
-            const float pm = __ldcg(p + m);
-            run += (double)pm;
-            kept += __fsub_rn((float)run, pm) < thr;
-        }
+    ROUTE_STAMP(8);
+    if (fixed_num) {
+        const int n = max(0, min(fixed_num[h], Nkv));
+        for (int r = tid; r < rows_per_head; r += T) num[((long long)(r / Nq) * H + h) * Nq + r % Nq] = n;
+    } else {
+        // kept blocks of a row = positions whose mass-before is under the threshold.  All rows of the head are
+        // counted together, sixteen independent loads per thread at a time: the loop is one CTA's, so it is the
+        // memory round trips, not the arithmetic, that it has to keep few.
+        constexpr int ROWS_AT_ONCE = 128, LOADS = 16;
+        __shared__ int row_count[ROWS_AT_ONCE];
+        __shared__ long long row_base[ROWS_AT_ONCE];
+        const int step_r = T / Nkv, step_m = T % Nkv;   // element e -> (row e / Nkv, position e % Nkv), advanced without dividing
+        for (int r0 = 0; r0 < rows_per_head; r0 += ROWS_AT_ONCE) {
+            const int nr = min(ROWS_AT_ONCE, rows_per_head - r0);
+            for (int r = tid; r < nr; r += T) {
+                const int rg = r0 + r;
+                row_count[r] = 0;
+                row_base[r] = (((long long)(rg / Nq) * H + h) * Nq + rg % Nq) * Nkv;
+            }
+            __syncthreads();
+            if ((Nkv & 3) == 0) {
+                // four positions per load; a thread's loads are all issued before the first is used
+                const int quads_per_row = Nkv >> 2, total = nr * quads_per_row;
+                constexpr int QLOADS = 10;
+                for (int e0 = 0; e0 < total; e0 += QLOADS * T) {
+                    float4 c[QLOADS];
+                    int rr[QLOADS];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) kept += __shfl_xor_sync(0xffffffffu, kept, o);
-        if (lane == 0) num[rid] = kept;
+                    for (int u = 0; u < QLOADS; ++u) {
+                        const int e = e0 + u * T + tid;
+                        rr[u] = -1;
+                        if (e < total) {
+                            const int r = e / quads_per_row;
+                            rr[u] = r;
+                            c[u] = __ldcg(reinterpret_cast<const float4 *>(sorted + row_base[r]) + (e - r * quads_per_row));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < QLOADS; ++u)
+                        if (rr[u] >= 0) {
+                            const int n = (c[u].x < thr) + (c[u].y < thr) + (c[u].z < thr) + (c[u].w < thr);
+                            if (n) atomicAdd(&row_count[rr[u]], n);
+                        }
+                }
+            } else {
+            const int total = nr * Nkv;   // <= 128 * 16384
+            int r = tid / Nkv, m = tid % Nkv;
+            for (int e0 = 0; e0 < total; e0 += LOADS * T) {
+                float c[LOADS];
+                int rr[LOADS];
+#pragma unroll
+                for (int u = 0; u < LOADS; ++u) {
+                    const bool in = e0 + u * T + tid < total;
+                    rr[u] = in ? r : -1;
+                    c[u] = in ? __ldcg(sorted + row_base[r] + m) : 0.f;
+                    r += step_r;
+                    m += step_m;
+                    if (m >= Nkv) {
+                        m -= Nkv;
+                        ++r;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < LOADS; ++u) {
+                    const bool keep = rr[u] >= 0 && c[u] < thr;
+                    const int first = __shfl_sync(0xffffffffu, rr[u], 0);
+                    if (__all_sync(0xffffffffu, rr[u] == first)) {   // the warp is inside one row: one atomic for all lanes
+                        const int n = __popc(__ballot_sync(0xffffffffu, keep));
+                        if (lane == 0 && first >= 0 && n) atomicAdd(&row_count[first], n);
+                    } else if (keep) {
+                        atomicAdd(&row_count[rr[u]], 1);
+                    }
+                }
+            }
+            }
+            __syncthreads();
+            ROUTE_STAMP(9);
+            for (int r2 = tid; r2 < nr; r2 += T) num[row_base[r2] / Nkv] = row_count[r2];
+            __syncthreads();
+        }
     }
 
     // ---- last head? ------------------------------------------------------------------------------
@@ -642,7 +720,7 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
 }  // namespace wa
 extern "C" int wa_route_trace_read(long long *dst, int n_ctas) {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(dst, wa::g_route_trace, (size_t)n_ctas * 8 * sizeof(long long));
+    cudaMemcpyFromSymbol(dst, wa::g_route_trace, (size_t)n_ctas * 12 * sizeof(long long));
     return 0;
 }
 namespace wa {
@@ -834,6 +912,8 @@ int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int
         py += (size_t)y_first_block * D;
     }
     const int nby = y ? ceil_div(Ly, block_size) : 0;
+    if (pool_sm100_supported(x, y, H, D, block_size) && (uintptr_t)px % 8 == 0 && (!y || (uintptr_t)py % 8 == 0))
+        return pool_sm100_launch(x, Lx, px, y, Ly, py, nby_all, B, H, D, block_size, stream, zero, n_zero);
     View4 vx = make_view(x), vy = y ? make_view(y) : vx;
     dim3 grid(nbx + nby, H, B);
     const bool vec = pool_vec_ok(x, D) && (!y || pool_vec_ok(y, D));
@@ -939,10 +1019,11 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
         sm_count = 148;
     if (rows < sm_count) sm_count = (int)rows;
     const int slots = (int)((rows + sm_count - 1) / sm_count);
-    route_fused_kernel<<<(unsigned)((long long)sm_count * slots), threads, smem, stream>>>(
-        q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2, D, (float)pow((double)D, -0.5), (float)tau_min,
-        (float)(tau_max - tau_min), fixed_num_per_head, sorted, index, num, thresholds, gini, counters, job, gate_per_cta,
-        sm_count, slots);
+    cudaError_t le = launch_dependent(route_fused_kernel, dim3((unsigned)((long long)sm_count * slots)), dim3(threads), smem, stream,
+                                      q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2, D, (float)pow((double)D, -0.5), (float)tau_min,
+                                      (float)(tau_max - tau_min), fixed_num_per_head, sorted, index, num, thresholds, gini, counters,
+                                      job, gate_per_cta, sm_count, slots);
+    if (le != cudaSuccess) return fail((int)le, "wa_hsa_forward(routing): %s", cudaGetErrorString(le));
     return check_launch("wa_hsa_forward(routing)");
 }
 }  // namespace wa
