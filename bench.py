@@ -766,6 +766,27 @@ def bench_hkv_centroids(dev, flush, pages=480, steps=5):
             "hbm_peak_gbs": peak_gbs, "a_page_s_offset_retrieves_that_page": own}
 
 
+def bench_config4(dev, chunks):
+    """Benchmark config 4: autoregressive generation with a random-init Wan2.1-T2V-1.3B-architecture DiT (30 blocks, dim
+    1536, 12 heads, FFN 8960, bf16), 480 x 832 latents, chunks of 3 latent frames, 4 denoising forwards + 1 clean-context
+    forward per chunk, HSA over a rolling 21-frame window (128-token blocks, per-head block counts drawn from
+    {4, 8, 16, 32} as in config 2), synthetic 512 x 4096 prompt embeddings, and a prompt switch served from the HKV bank
+    every 8 chunks (pages of 3 frames, top-4 pages, the four most recent banked windows kept in HBM, older ones in pinned host memory).  Text encoder and VAE are outside the timed region; frames are
+    latent frames.  Everything around the attention layer is plain torch (cuBLAS GEMMs, library cross-attention)."""
+    from worldattention_b200.causal_dit import DiTConfig, time_generation
+    rng = np.random.default_rng(1)
+    cfg = DiTConfig(hsa_topk=[int(v) for v in rng.choice([4, 8, 16, 32], size=12)])
+    try:
+        res = time_generation(cfg, chunks=chunks, switch_every_chunks=8,
+                              hkv_kwargs=dict(page_size_frames=3, topk_pages=4, cpu_max_chunks=64, hbm_max_chunks=4), device=dev)
+    except torch.OutOfMemoryError as exc:      # reported, not hidden: the harness needs about 12 GB
+        return {"error": f"out of memory: {exc}"}
+    res["workload"] = ("c4: 30-block DiT (dim 1536, 12 heads, FFN 8960), 1560 tokens/frame, 3-frame chunks, 4+1 forwards per chunk, "
+                       f"{chunks} chunks (the benchmark names 80), HSA window 21 frames, HKV switch every 8 chunks")
+    res["unit"] = "latent frames/s"
+    return res
+
+
 def bench_hkv_cold(dev, layers=2, pages_total=480, pages_hot=64, topk=16, steps=4):
     """Config 3 with its residency: pages 0..63 of every layer in HBM, the other 416 in page-locked host memory.
 
@@ -896,6 +917,8 @@ def main():
     ap.add_argument("--force-generic", action="store_true")
     ap.add_argument("--no-hkv", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip block64 / long_horizon / compress / triton_incumbent")
+    ap.add_argument("--c4-chunks", type=int, default=24,
+                    help="chunks generated by the end-to-end harness (benchmark config 4 asks for 80; 0 skips it)")
     ap.add_argument("--hkv-only", action="store_true", help="run only the HKV retrieval measurements (one GPU)")
     ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the hot HKV measurement (30 = benchmark config 3)")
     ap.add_argument("--hkv-cold-layers", type=int, default=2, help="layers in the cold-tier HKV measurement")
@@ -1179,6 +1202,9 @@ def main():
         line["hkv"]["cold_tier"] = bench_hkv_cold(dev, layers=args.hkv_cold_layers)
         torch.cuda.empty_cache()
         line["hkv"]["page_centroids"] = bench_hkv_centroids(dev, Flusher(dev))
+    if world == 1 and not args.no_extras and not args.force_generic and args.c4_chunks > 0:
+        torch.cuda.empty_cache()
+        line["config4"] = bench_config4(dev, args.c4_chunks)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

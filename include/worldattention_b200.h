@@ -278,6 +278,17 @@ int wa_qk_norm_rope(const wa_tensor4 *x, const wa_tensor4 *out, int B, int L, in
                     int weight_dtype, float eps, const double *freqs, int freq_rows, int start_frame, int grid_h,
                     int grid_w, void *stream);
 
+/* The element-wise wrappers of a DiT block's sub-layers (wan/modules/causal_model.py:586-659 with WanLayerNorm,
+ * wan/modules/model.py:89-103), bf16 rows `[rows, C]`, contiguous.  Frame f of the batch owns rows
+ * [f * tokens_per_frame, (f + 1) * tokens_per_frame); its modulation vectors start at `ptr + f * mod_stride` elements.
+ *   wa_ln_modulate:    out = LN(x) [* weight + bias], rounded to bf16, then * (1 + scale[f]) + shift[f] (each NULL = absent),
+ *                      every step rounded to bf16 as the reference's tensor expressions round it.
+ *   wa_gated_residual: out = x + y * gate[f] (gate NULL: x + y).  out may alias x. */
+int wa_ln_modulate(const void *x, void *out, long long rows, int C, float eps, const void *weight, const void *bias,
+                   const void *scale, const void *shift, long long mod_stride, int tokens_per_frame, void *stream);
+int wa_gated_residual(const void *x, const void *y, void *out, long long rows, int C, const void *gate, long long mod_stride,
+                      int tokens_per_frame, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * HKV retrieval -- pipeline/hkv/retrieval.py, rope.py, cache.py
  * ------------------------------------------------------------------------------------------- */

@@ -62,9 +62,24 @@ def main():
         max_abs = float(err.max())
         mean_rel = float(err.mean() / want.float().abs().mean())
         assert max_abs < 2e-2 and mean_rel < 1e-2, (max_abs, mean_rel)
+        info = dict(sharded.last_call_info)
+        assert info.get("collectives") == 3 or world == 1, info
         if rank == 0:
-            print(f"topk={'adaptive' if tk is not None else 'cum-mass'}: head-split exact, kv-shard max_abs={max_abs:.2e} "
-                  f"mean_rel={mean_rel:.2e}", flush=True)
+            print(f"topk={'fixed' if tk is not None else 'cum-mass'}: head-split exact, kv-shard max_abs={max_abs:.2e} "
+                  f"mean_rel={mean_rel:.2e} {info}", flush=True)
+        if tk is not None:
+            # fixed top-k again, routed by exchanging each rank's best candidates instead of gathering the pooled keys
+            got_c = sharded.hsa_attention_kv_sharded(hsa, q, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(),
+                                                     kc[:, seg_lo * r: seg_hi * r].contiguous(),
+                                                     vc[:, seg_lo * r: seg_hi * r].contiguous(), kv_len=kv_len, shards=shards,
+                                                     topk_per_head=tk, routing="candidates", topk_max=32)
+            err = (got_c.float() - want.float()).abs()
+            max_abs = float(err.max())
+            mean_rel = float(err.mean() / want.float().abs().mean())
+            assert max_abs < 2e-2 and mean_rel < 1e-2, ("candidates", max_abs, mean_rel)
+            if rank == 0:
+                print(f"topk=fixed routing=candidates: max_abs={max_abs:.2e} mean_rel={mean_rel:.2e} "
+                      f"{dict(sharded.last_call_info)}", flush=True)
     dist.destroy_process_group()
 
 

@@ -82,6 +82,8 @@ SIGNATURES = {
     "wa_hsa_workspace_bytes": [C.POINTER(HsaParams)],
     "wa_hsa_forward": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
     "wa_hsa_status": [C.POINTER(HsaParams), C.POINTER(C.c_int), _vp],
+    "wa_ln_modulate": [_vp, _vp, _i64, _i, _f, _vp, _vp, _vp, _vp, _i64, _i, _vp],
+    "wa_gated_residual": [_vp, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp],
     "wa_qk_norm_rope": [_T4P, _T4P, _i, _i, _i, _i, _vp, _i, _f, _vp, _i, _i, _i, _i, _vp],
     "wa_hkv_page_centroids": [_T4P, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "wa_hkv_score_topk": [_vp, _vp, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp],

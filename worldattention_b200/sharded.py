@@ -318,7 +318,9 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
         used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records)
     else:
         o_s, l_s, o_l, l_l, used_tuned = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
-    last_call_info.update(used_tuned=bool(used_tuned), routing="candidates" if by_candidates else "gather", ranks=world)
+    last_call_info.update(used_tuned=bool(used_tuned), routing="candidates" if by_candidates else "gather", ranks=world,
+                          # routing exchange + (packed: one all-to-all and one all-gather | unpacked: two all-gathers)
+                          collectives=0 if world == 1 else 3, packed_exchange=records is not None)
 
     if records is not None:
         recv = torch.empty_like(records[0])                                  # [W * rp, H, rec]: slice j of every rank
