@@ -776,9 +776,13 @@ def bench_config4(dev, chunks):
     from worldattention_b200.causal_dit import DiTConfig, time_generation
     rng = np.random.default_rng(1)
     cfg = DiTConfig(hsa_topk=[int(v) for v in rng.choice([4, 8, 16, 32], size=12)])
+    kwargs = dict(chunks=chunks, switch_every_chunks=8, device=dev,
+                  hkv_kwargs=dict(page_size_frames=3, topk_pages=4, cpu_max_chunks=64, hbm_max_chunks=4))
     try:
-        res = time_generation(cfg, chunks=chunks, switch_every_chunks=8,
-                              hkv_kwargs=dict(page_size_frames=3, topk_pages=4, cpu_max_chunks=64, hbm_max_chunks=4), device=dev)
+        res = time_generation(cfg, cuda_graph=True, **kwargs)      # steady-state chunks replayed from one captured graph
+        torch.cuda.empty_cache()
+        eager = time_generation(cfg, cuda_graph=False, **kwargs)
+        res["launch_by_launch"] = {k: eager[k] for k in ("frames_per_s", "frames_per_s_steady", "chunk_ms_median_second_half", "wall_s")}
     except torch.OutOfMemoryError as exc:      # reported, not hidden: the harness needs about 12 GB
         return {"error": f"out of memory: {exc}"}
     res["workload"] = ("c4: 30-block DiT (dim 1536, 12 heads, FFN 8960), 1560 tokens/frame, 3-frame chunks, 4+1 forwards per chunk, "

@@ -277,6 +277,11 @@ int wa_hsa_status(const wa_hsa_params *p, int *status, void *stream);
 int wa_qk_norm_rope(const wa_tensor4 *x, const wa_tensor4 *out, int B, int L, int H, int D, const void *norm_weight,
                     int weight_dtype, float eps, const double *freqs, int freq_rows, int start_frame, int grid_h,
                     int grid_w, void *stream);
+/* The same with the first frame's index read from device memory when the kernel runs, so that a captured launch
+ * (CUDA graph of a chunk's forwards) can be replayed at another position of the video. */
+int wa_qk_norm_rope_at(const wa_tensor4 *x, const wa_tensor4 *out, int B, int L, int H, int D, const void *norm_weight,
+                       int weight_dtype, float eps, const double *freqs, int freq_rows, const int32_t *start_frame_device,
+                       int grid_h, int grid_w, void *stream);
 
 /* The element-wise wrappers of a DiT block's sub-layers (wan/modules/causal_model.py:586-659 with WanLayerNorm,
  * wan/modules/model.py:89-103), bf16 rows `[rows, C]`, contiguous.  Frame f of the batch owns rows

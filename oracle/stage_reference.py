@@ -14,7 +14,7 @@ with the working tree.  Two consumers:
 * `bench.py` times the reference's PyTorch CPU path and its Triton kernel from there.
 
 Both skip, saying so, when the directory is absent.  The reference checkout is found through
-`--reference`, then `$WORLDATTENTION_REFERENCE`, then `/root/reference`.
+`--reference`, then `$WORLDATTENTION_REFERENCE`, then the default location in `DEFAULT_REFERENCE`.
 """
 from __future__ import annotations
 
@@ -26,10 +26,11 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DEFAULT_DEST = os.path.join(ROOT, "baseline", "_ref")
 PARTS = ["wan/modules/hsa", "pipeline/hkv", "trainer/hsa_stage.py", "tests"]
+DEFAULT_REFERENCE = "/root/reference"
 
 
 def find_reference(explicit: str | None = None) -> str | None:
-    for cand in (explicit, os.environ.get("WORLDATTENTION_REFERENCE"), "/root/reference"):
+    for cand in (explicit, os.environ.get("WORLDATTENTION_REFERENCE"), DEFAULT_REFERENCE):
         if cand and os.path.isdir(os.path.join(cand, "wan", "modules", "hsa")):
             return cand
     return None

@@ -124,3 +124,21 @@ def test_fused_and_unfused_models_agree():
     plain = pipe.generate(noise, prompts, generator=g)
     err = (fused.float() - plain.float()).abs()
     assert float(err.mean()) < 2e-2 * float(plain.float().abs().mean()) + 1e-3
+
+
+def test_graph_replay_of_steady_chunks_equals_launch_by_launch():
+    from worldattention_b200.causal_dit import ChunkPipeline
+    cfg = _small()
+    model, pipe = _build(cfg)
+    noise = torch.randn((1, 18, 16, 16, 32), device="cuda:0", dtype=torch.bfloat16)     # 6 chunks: 4 of them roll the window
+    prompts = [torch.randn(16, 64)]
+    g = torch.Generator(device="cuda:0").manual_seed(2)
+    plain = pipe.generate(noise, prompts, generator=g)
+    caches = [{k: v.clone() for k, v in c.items()} for c in pipe.kv_cache]
+    pipe2 = ChunkPipeline(model, device="cuda:0", cuda_graph=True)
+    g = torch.Generator(device="cuda:0").manual_seed(2)
+    replayed = pipe2.generate(noise, prompts, generator=g)
+    assert pipe2.stats.graph_error is None and pipe2.stats.graph_replays == 4
+    assert torch.equal(plain, replayed)
+    for a, b in zip(caches, pipe2.kv_cache):
+        assert torch.equal(a["k"], b["k"]) and torch.equal(a["k_coarse"], b["k_coarse"])

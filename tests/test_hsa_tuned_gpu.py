@@ -37,7 +37,7 @@ def _proj(rank, seg, bs, rng):
     return O.bf16_round(e + 0.002 * rng.standard_normal(e.shape).astype(np.float32))
 
 
-def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=True, coarse_len=None):
+def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=True, coarse_len=None, whole_order=False):
     rng = np.random.default_rng(seed)
     q = _draw(rng, (bsz, q_len, heads, D), scale)
     k = _draw(rng, (bsz, kv_len, heads, D), scale)
@@ -71,6 +71,9 @@ def _run_case(wa, *, seed, bsz, heads, q_len, kv_len, seg, topk, scale, gate=Tru
                                   gate_weight=gw_used, gate_bias=gb if gate else None, block_size=128,
                                   proj_segment_len=seg, dtype="bf16", topk_per_head=topk, return_parts=True)
     assert np.array_equal(to_np(num), parts["num"])
+    if whole_order:      # the complete descending order of every row, not only the counts
+        assert np.array_equal(to_np(index), parts["index"])
+        assert np.array_equal(to_np(thr), parts["thresholds"])
     max_abs, mean_rel = attention_error(to_np(out), want)
     assert max_abs < MAX_ABS and mean_rel < MEAN_REL, ("vs oracle", max_abs, mean_rel)
     max_abs_g, mean_rel_g = attention_error(to_np(out), to_np(ref))
@@ -103,6 +106,31 @@ def test_no_gate_module_uses_sigmoid_of_q(wa):
 
 def test_large_logits_exercise_the_running_max_rescale(wa):
     _run_case(wa, seed=6, bsz=1, heads=2, q_len=256, kv_len=2048, seg=512, topk=[16, 9], scale=3.0)
+
+
+def test_more_than_1024_key_blocks_route_four_rows_per_cta(wa):
+    # 1032 key blocks: the routing kernel scores four query blocks per CTA in one pass over the pooled keys; 5 query
+    # blocks = one full group and a group of one.  Same order, counts and thresholds as the oracle.
+    _run_case(wa, seed=7, bsz=1, heads=2, q_len=600, kv_len=132000, seg=1320, topk=[3, 10], scale=1.0 / math.sqrt(D),
+              whole_order=True)
+    _run_case(wa, seed=8, bsz=2, heads=1, q_len=300, kv_len=131100, seg=1311, topk=None, scale=0.5, whole_order=True)
+
+
+def test_fixed_counts_over_many_key_blocks_select_instead_of_sorting(wa):
+    # without `return_routing` nobody reads the whole order, so the routing kernel picks each head's k best blocks by
+    # radix select; the attention output must be the one the full sort gives, bit for bit (same ids, same order)
+    rng = np.random.default_rng(12)
+    heads, q_len, kv_len, seg = 3, 330, 80000, 1600
+    q, k, v = (to_gpu(_draw(rng, (1, n, heads, D), s), "bf16") for n, s in ((q_len, 0.2), (kv_len, 0.2), (kv_len, 1.0)))
+    ek = to_gpu(_proj(math.ceil(seg / 64), seg, 64, rng), "bf16")
+    lin = torch.nn.Linear(D, D).to(dev())
+    for topk in ([32, 1, 7], [0, 1300, 64]):        # 1300 > 1250 key blocks: every block kept
+        kw = dict(k_proj_mat=ek, v_proj_mat=ek, gate_lin=lin, block_size=64, proj_segment_len=seg,
+                  topk_per_head=torch.tensor(topk, dtype=torch.int32), check_status=True)
+        sorted_out, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, return_routing=True, **kw)
+        picked_out = wa.hsa.hsa_attention(q, k, v, **kw)
+        assert used and torch.equal(sorted_out, picked_out)
+        assert num[0, :, 0].tolist() == [min(t, 1250) for t in topk]
 
 
 def test_config2_shape_head_adaptive_topk(wa):

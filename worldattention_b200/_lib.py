@@ -85,6 +85,7 @@ SIGNATURES = {
     "wa_ln_modulate": [_vp, _vp, _i64, _i, _f, _vp, _vp, _vp, _vp, _i64, _i, _vp],
     "wa_gated_residual": [_vp, _vp, _vp, _i64, _i, _vp, _i64, _i, _vp],
     "wa_qk_norm_rope": [_T4P, _T4P, _i, _i, _i, _i, _vp, _i, _f, _vp, _i, _i, _i, _i, _vp],
+    "wa_qk_norm_rope_at": [_T4P, _T4P, _i, _i, _i, _i, _vp, _i, _f, _vp, _i, _vp, _i, _i, _vp],
     "wa_hkv_page_centroids": [_T4P, _i, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "wa_hkv_score_topk": [_vp, _vp, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp],
     "wa_hkv_score_topk_layers": [_vp, _vp, _i, _i, _i, _i, C.c_longlong, _f, _i, _vp, _vp, _vp, _vp],

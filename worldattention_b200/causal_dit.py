@@ -197,8 +197,13 @@ class _CrossAttention(nn.Module):   # model.py:165-200 (text-to-video), keys/val
         else:
             q = self.norm_q(self.q(x)).view(b, s, h, d // h).transpose(1, 2)
         if not cache.get("is_init", False):
-            cache["k"] = self.norm_k(self.k(context)).view(b, -1, h, d // h).transpose(1, 2).contiguous()
-            cache["v"] = self.v(context).view(b, -1, h, d // h).transpose(1, 2).contiguous()
+            k_new = self.norm_k(self.k(context)).view(b, -1, h, d // h).transpose(1, 2).contiguous()
+            v_new = self.v(context).view(b, -1, h, d // h).transpose(1, 2).contiguous()
+            if "k" in cache and cache["k"].shape == k_new.shape:      # keep the addresses: a captured graph may hold them
+                cache["k"].copy_(k_new)
+                cache["v"].copy_(v_new)
+            else:
+                cache["k"], cache["v"] = k_new, v_new
             cache["is_init"] = True
         y = F.scaled_dot_product_attention(q, cache["k"], cache["v"])
         return self.o(y.transpose(1, 2).reshape(b, s, d))
@@ -309,15 +314,22 @@ class _Stats:
     chunk_ms: List[float] = field(default_factory=list)
     switch_ms: List[float] = field(default_factory=list)
     switch_parts_ms: List[List[float]] = field(default_factory=list)      # [store, retrieve, apply] per switch
+    graph_replays: int = 0
+    graph_error: Optional[str] = None
 
 
 class ChunkPipeline:
     """The chunk loop with the rolling per-layer caches and an optional HKV bank for prompt switches."""
 
-    def __init__(self, model: CausalDiT, *, hkv: Optional[HKVCache] = None, device=None, dtype=torch.bfloat16):
+    def __init__(self, model: CausalDiT, *, hkv: Optional[HKVCache] = None, device=None, dtype=torch.bfloat16,
+                 cuda_graph: bool = False):
         self.model = model
         self.cfg = model.cfg
         self.hkv = hkv
+        # once the window is full every chunk runs the same launches on the same addresses (roll, write at the tail);
+        # with `cuda_graph` those five forwards are captured once and replayed, the frame index being read from device memory
+        self.cuda_graph = bool(cuda_graph)
+        self._graph = None
         self.dev = torch.device(device) if device is not None else next(model.parameters()).device
         self.dtype = dtype
         self.stats = _Stats()
@@ -341,6 +353,7 @@ class ChunkPipeline:
         self.cross_cache = [{"is_init": False} for _ in self.model.blocks]
         self.local_end = 0          # host copies of the two indices: the loop never reads them back from the device
         self.global_end = 0
+        self._graph = None
         if self.hkv is not None:
             self.hkv.reset()
 
@@ -397,6 +410,53 @@ class ChunkPipeline:
         self.stats.switch_parts_ms.append([round((b - a) * 1e3, 2) for a, b in zip(marks, marks[1:])])
         return installed
 
+    def _chunk_body(self, x_t, eps, context, plan: dict, start_frame):
+        """The chunk's denoising forwards and the clean-context forward (causal_inference.py:222-259) -> the clean latent."""
+        cfg, model = self.cfg, self.model
+        plan = dict(plan, start_frame=start_frame)
+        later = dict(plan, roll=False)          # the window is rolled once; later forwards rewrite the same rows
+        x0 = None
+        for i, t in enumerate(cfg.denoising_steps):
+            flow = model(x_t, self._timestep(t), context, self.kv_cache, self.cross_cache, plan if i == 0 else later)
+            x0 = x_t - (t / 1000.0) * flow                                  # flow prediction -> clean latent
+            if i + 1 < len(cfg.denoising_steps):
+                nxt = cfg.denoising_steps[i + 1] / 1000.0
+                x_t = (1 - nxt) * x0 + nxt * eps[i]                         # re-noise for the next step (utils/scheduler.py add_noise)
+        model(x0, self._timestep(cfg.context_noise), context, self.kv_cache, self.cross_cache, later)   # clean keys and values
+        return x0
+
+    def _timestep(self, t) -> torch.Tensor:
+        cache = self.__dict__.setdefault("_ts", {})
+        if t not in cache:
+            cache[t] = torch.full((1, self.cfg.frames_per_chunk), float(t), device=self.dev)
+        return cache[t]
+
+    def _replay(self, x_t, eps, context, plan, frame):
+        """A steady-state chunk through the captured graph (captured on first use; any failure turns graphs off)."""
+        if self._graph is None:
+            try:
+                static = {"x": x_t.clone(), "eps": eps.clone(), "ctx": context.clone(),
+                          "frame": torch.tensor([frame], dtype=torch.int32, device=self.dev)}
+                for t in list(self.cfg.denoising_steps) + [self.cfg.context_noise]:
+                    self._timestep(t)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    static["out"] = self._chunk_body(static["x"], static["eps"], static["ctx"], plan, static["frame"])
+                self._graph = (graph, static, (plan["evict"], plan["keep"], plan["write"]))
+            except Exception as exc:      # reported by the caller's stats; the chunk then runs launch by launch
+                self.stats.graph_error = f"{type(exc).__name__}: {exc}"
+                torch.cuda.synchronize(self.dev)
+                return self._chunk_body(x_t, eps, context, plan, frame)
+        graph, static, key = self._graph
+        assert key == (plan["evict"], plan["keep"], plan["write"])
+        static["x"].copy_(x_t)
+        static["eps"].copy_(eps)
+        static["ctx"].copy_(context)
+        static["frame"].fill_(frame)
+        graph.replay()
+        self.stats.graph_replays += 1
+        return static["out"]
+
     @torch.no_grad()
     def generate(self, noise: torch.Tensor, prompts: Sequence[torch.Tensor], switch_frames: Sequence[int] = (),
                  generator: Optional[torch.Generator] = None) -> torch.Tensor:
@@ -423,23 +483,16 @@ class ChunkPipeline:
             context = contexts[segment]
             x_t = noise[:, frame:frame + cfg.frames_per_chunk]
             plan = self._plan(frame)
-            first = True
-            for i, t in enumerate(cfg.denoising_steps):
-                ts = torch.full((1, cfg.frames_per_chunk), float(t), device=self.dev)
-                step_plan = plan if first else dict(plan, roll=False)      # later forwards of the chunk rewrite the same rows
-                flow = model(x_t, ts, context, self.kv_cache, self.cross_cache, step_plan)
-                first = False
-                sigma = t / 1000.0
-                x0 = x_t - sigma * flow                                     # flow prediction -> clean latent
-                if i + 1 < len(cfg.denoising_steps):
-                    nxt = cfg.denoising_steps[i + 1] / 1000.0
-                    eps = torch.randn(x0.shape, device=self.dev, dtype=x0.dtype, generator=generator)
-                    x_t = (1 - nxt) * x0 + nxt * eps                        # re-noise for the next step (utils/scheduler.py add_noise)
-                self.stats.forwards += 1
+            steps = len(cfg.denoising_steps)
+            eps = torch.randn((steps - 1,) + tuple(x_t.shape), device=self.dev, dtype=x_t.dtype, generator=generator)
+            steady = plan["roll"] and plan["write"] + x_t.shape[1] * cfg.frame_tokens == cfg.window_frames * cfg.frame_tokens
+            if (self.cuda_graph and steady and self.stats.graph_error is None
+                    and all(c.get("is_init", False) for c in self.cross_cache)):
+                x0 = self._replay(x_t, eps, context, plan, frame)
+            else:
+                x0 = self._chunk_body(x_t, eps, context, plan, frame)
+            self.stats.forwards += steps + 1
             out[:, frame:frame + cfg.frames_per_chunk] = x0
-            ts = torch.full((1, cfg.frames_per_chunk), float(cfg.context_noise), device=self.dev)
-            model(x0, ts, context, self.kv_cache, self.cross_cache, dict(plan, roll=False))   # clean keys and values into the cache
-            self.stats.forwards += 1
             self._commit(plan)
             ev[2].record()
             ev[2].synchronize()
@@ -451,7 +504,7 @@ class ChunkPipeline:
 
 
 def time_generation(cfg: DiTConfig, *, chunks: int, switch_every_chunks: int = 0, hkv_kwargs: Optional[dict] = None,
-                    seed: int = 0, device="cuda:0") -> dict:
+                    seed: int = 0, device="cuda:0", cuda_graph: bool = False) -> dict:
     """Build a random-init model, generate `chunks` chunks, and return frames/s with the per-chunk times."""
     dev = torch.device(device)
     torch.manual_seed(seed)
@@ -460,27 +513,38 @@ def time_generation(cfg: DiTConfig, *, chunks: int, switch_every_chunks: int = 0
     hkv = None
     if switch_every_chunks > 0:
         hkv = HKVCache(frame_seq_length=cfg.frame_tokens, **(hkv_kwargs or {}))
-    pipe = ChunkPipeline(model, hkv=hkv, device=dev)
+    pipe = ChunkPipeline(model, hkv=hkv, device=dev, cuda_graph=cuda_graph)
     frames = chunks * cfg.frames_per_chunk
     g = torch.Generator(device=dev).manual_seed(seed)
     noise = torch.randn((1, frames, cfg.in_channels) + tuple(cfg.latent_hw), device=dev, dtype=torch.bfloat16, generator=g)
     switches = [c * cfg.frames_per_chunk for c in range(switch_every_chunks, chunks, switch_every_chunks)] if switch_every_chunks else []
     gp = torch.Generator(device="cpu").manual_seed(seed + 1)
     prompts = [torch.randn((cfg.text_len, cfg.text_dim), generator=gp) for _ in range(len(switches) + 1)]
+    # untimed: two chunks and, with a bank, one store, so that library initialisation and the first growth of the
+    # allocator's pools are not counted as generation time
+    pipe.generate(noise[:, :2 * cfg.frames_per_chunk], prompts[:1], generator=g)
+    if hkv is not None:
+        hkv.store(pipe.kv_cache, prompt_embeds=prompts[0].to(dev, torch.bfloat16).unsqueeze(0), current_start_frame=2 * cfg.frames_per_chunk,
+                  temporal_freqs=temporal_band(model.freqs, cfg.head_dim).to(dev))
+    pipe.reset()
+    pipe.stats = _Stats()
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
     out = pipe.generate(noise, prompts, switches, generator=g)
     torch.cuda.synchronize(dev)
     wall = time.perf_counter() - t0
+    _lib.raise_if_failed(dev)         # replayed launches are not checked one by one
     st = pipe.stats
     steady = sorted(st.chunk_ms[len(st.chunk_ms) // 2:]) or [float("nan")]
     return {
         "frames": frames, "chunks": chunks, "forwards": st.forwards, "wall_s": wall, "frames_per_s": frames / wall,
+        "frames_per_s_steady": cfg.frames_per_chunk / (steady[len(steady) // 2] * 1e-3),
         "chunk_ms_median_second_half": steady[len(steady) // 2], "chunk_ms_first": st.chunk_ms[0] if st.chunk_ms else None,
         "switches": st.switches, "pages_installed": st.pages_installed,
         "switch_ms": [round(v, 3) for v in st.switch_ms if v > 0.05],
         "switch_store_retrieve_apply_ms": st.switch_parts_ms,
         "finite": bool(torch.isfinite(out.float()).all()),
+        "cuda_graph": {"asked": bool(cuda_graph), "replayed_chunks": st.graph_replays, "error": st.graph_error},
         "window_frames": cfg.window_frames, "hsa_block": cfg.hsa_block,
         "hsa_topk": "cumulative-mass" if cfg.hsa_topk is None else list(cfg.hsa_topk),
     }

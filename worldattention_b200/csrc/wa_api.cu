@@ -208,7 +208,8 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
         SchedJob job{};
         if (tuned) job = hsa_sm100_sched_job(p, ws + w.tuned);
         if ((rc = route_fused_launch(q_pooled, k_pooled, p->B, p->H, w.Nq, w.Nkv, p->D, p->tau_min, p->tau_max,
-                                     p->topk_per_head, block_attn, index, num, thresholds, gini, counters, job, stream)))
+                                     p->topk_per_head, block_attn, index, num, thresholds, gini, counters, job, stream,
+                                     /*whole_order=*/p->index_out != nullptr || p->thresholds_out != nullptr)))
             return rc;
         prepared = tuned;
     }

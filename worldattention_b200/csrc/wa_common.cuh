@@ -59,13 +59,14 @@ struct PerDeviceOnce {
 // `pdl_wait()` until that kernel has completed and its writes are visible.  A kernel launched this way must reach
 // `pdl_wait()` in every thread block before it touches anything the stream's earlier work reads or writes.
 // WA_B200_PDL=0 in the environment turns the attribute off (plain stream order), for timing comparisons.
-inline bool pdl_enabled() {
-    static const bool on = [] {
+inline int pdl_mode() {      // 0: plain stream order; 1: dependent launch (default); 2: and the routing kernel releases its dependents once a CTA's rows are done
+    static const int mode = [] {
         const char *e = getenv("WA_B200_PDL");
-        return !(e && e[0] == '0');
+        return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
     }();
-    return on;
+    return mode;
 }
+inline bool pdl_enabled() { return pdl_mode() != 0; }
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -15,6 +15,7 @@ struct SchedJob {
     int gate_dt;
     __nv_bfloat16 *w_out;   // [128 x 128] bf16
     float *b_out;           // [128] float32
+    int release_dependents_after_rows;   // timing experiment (WA_B200_PDL=2), see route_row
 };
 
 constexpr int SCHED_BINS = 4096;
@@ -101,7 +102,8 @@ int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int
 // `sorted` ([rows, Nkv] float32) and `gini` ([rows]) are scratch; `counters` are H + 1 ints that are zero on entry.
 int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int H, int Nq, int Nkv, int D, double tau_min,
                        double tau_max, const int32_t *fixed_num_per_head, float *sorted, int32_t *index, int32_t *num,
-                       float *thresholds, float *gini, int *counters, const SchedJob &job, cudaStream_t stream);
+                       float *thresholds, float *gini, int *counters, const SchedJob &job, cudaStream_t stream,
+                       bool whole_order = true);   // false: only the first num[row] ids of a row are needed (fixed counts)
 
 // optional CUDA-event bracket around the attention kernel (wa_api.cu)
 void profile_mark(bool begin, cudaStream_t stream);

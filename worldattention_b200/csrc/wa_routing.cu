@@ -289,15 +289,10 @@ __device__ __forceinline__ void row_logits(const float *__restrict__ q, const fl
     }
 }
 
-// One row: out[j] = softmax_j(q . k_j * scale) with float64 dots and sums, each rounded once to float32.
-// `out` may be shared or global memory; `red` holds >= 32 doubles.  Called by every thread of the CTA.
-__device__ __forceinline__ void row_block_attention(const float *__restrict__ q, const float *__restrict__ k, int Nkv, int D,
-                                                    float scale, float *out, double *red, float *bcast) {
+// Softmax of one row of logits in place: float64 sum, each value rounded once to float32.  `out` may be shared or global
+// memory; `red` holds >= 32 doubles.  Called by every thread of the CTA after the logits are complete (and a barrier).
+__device__ __forceinline__ void row_softmax(int Nkv, float *out, double *red, float *bcast) {
     const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
-    row_logits(q, k, Nkv, D, scale, out);
-    __syncthreads();
-    ROUTE_STAMP(1);
-
     float m = -INFINITY;
     for (int j = threadIdx.x; j < Nkv; j += T) m = fmaxf(m, out[j]);
     m = warp_max(m);
@@ -330,6 +325,101 @@ __device__ __forceinline__ void row_block_attention(const float *__restrict__ q,
     const float denom = *bcast;
     for (int j = threadIdx.x; j < Nkv; j += T) out[j] = __fdiv_rn(out[j], denom);
     __syncthreads();
+}
+
+// One row: out[j] = softmax_j(q . k_j * scale) with float64 dots and sums, each rounded once to float32.
+__device__ __forceinline__ void row_block_attention(const float *__restrict__ q, const float *__restrict__ k, int Nkv, int D,
+                                                    float scale, float *out, double *red, float *bcast) {
+    row_logits(q, k, Nkv, D, scale, out);
+    __syncthreads();
+    ROUTE_STAMP(1);
+    row_softmax(Nkv, out, red, bcast);
+}
+
+// Logits of FOUR neighbouring rows of one head against one pass over the head's pooled keys (D = 128 only): with
+// thousands of key blocks a row's CTA otherwise re-reads megabytes of pooled keys that its neighbours read too, and
+// converts each to float64 again.  Same additions in the same order as `row_logits`, so the same bits.  `q` holds the
+// rows `D` apart, `out` holds them `Nkv` apart; rows >= nrows repeat row 0's query and are not stored.  The queries stay
+// in registers as float64 (re-reading them from shared memory for every pair of keys made this routine
+// shared-memory-bound: 350 us per group at 11 700 key blocks).  The keys pass through
+// `stage` (shared memory, 4 * tile_keys rows of 512 bytes) in tiles fetched with asynchronous copies, three ahead of the
+// one being computed on.
+__device__ __forceinline__ void row_logits_x4(const float *__restrict__ q, int nrows, const float *__restrict__ k, int Nkv,
+                                              float scale, float *out, float4 *stage, int tile_keys) {
+    constexpr int D = 128, VPK = D / 4;   // 16-byte vectors per key
+    const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
+    double qd[4][4];      // this lane's four dimensions of the four rows (the kernel runs 512 threads: 128 registers each)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float4 qv = *reinterpret_cast<const float4 *>(q + (r < nrows ? r : 0) * D + lane * 4);
+        qd[r][0] = (double)qv.x; qd[r][1] = (double)qv.y; qd[r][2] = (double)qv.z; qd[r][3] = (double)qv.w;
+    }
+    const float4 *kvec = reinterpret_cast<const float4 *>(k);
+    const int tile_vecs = tile_keys * VPK;
+    const long long total_vecs = (long long)Nkv * VPK;
+    const int n_tiles = (Nkv + tile_keys - 1) / tile_keys;
+    // asynchronous 16-byte copies straight into shared memory (no registers held while they fly); vectors past the end
+    // of the keys are written as zeros (source size 0).  STAGES - 1 tiles are in flight while one is computed on: with a
+    // single tile in flight the routine ran at one tile per L2 round trip (21 GB/s per SM).
+    constexpr int STAGES = 4;
+    auto fetch = [&](int tile) {
+        if (tile < n_tiles) {
+            float4 *dst = stage + (tile % STAGES) * tile_vecs;
+            for (int v = threadIdx.x; v < tile_vecs; v += T) {
+                const long long g = (long long)tile * tile_vecs + v;
+                const bool real = g < total_vecs;
+                const unsigned saddr = (unsigned)__cvta_generic_to_shared(dst + v);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(kvec + (real ? g : 0)), "r"(real ? 16 : 0)
+                             : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");      // an empty group past the end keeps the count uniform
+    };
+#pragma unroll
+    for (int t0 = 0; t0 < STAGES - 1; ++t0) fetch(t0);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");      // this thread's copies of `tile` have landed
+        __syncthreads();      // everyone's have, and everyone is done with tile - 1, whose buffer the next fetch overwrites
+        fetch(tile + STAGES - 1);
+        const float4 *kt = stage + (tile % STAGES) * tile_vecs;
+        const int base = tile * tile_keys;
+        for (int j = warp * 2; j < tile_keys && base + j < Nkv; j += nwarps * 2) {      // two keys x four rows per warp and pass
+            double acc[8];     // acc[r * 2 + u]
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float4 kv = kt[(j + u) * VPK + lane];    // a key past the end of the tile's real keys is zeros
+                const double k0 = (double)kv.x, k1 = (double)kv.y, k2 = (double)kv.z, k3 = (double)kv.w;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    double a = fma(qd[r][0], k0, 0.0);
+                    a = fma(qd[r][1], k1, a);
+                    a = fma(qd[r][2], k2, a);
+                    a = fma(qd[r][3], k3, a);
+                    acc[r * 2 + u] = a;
+                }
+            }
+            // transposed reduction, as in row_logits: lane l ends with sum (l >> 2) & 7
+            const bool b16 = lane & 16, b8 = lane & 8, b4 = lane & 4;
+            double r4[4], r2[2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const double keep = b16 ? acc[i + 4] : acc[i], give = b16 ? acc[i] : acc[i + 4];
+                r4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const double keep = b8 ? r4[i + 2] : r4[i], give = b8 ? r4[i] : r4[i + 2];
+                r2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+            }
+            double t = (b4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, b4 ? r2[0] : r2[1], 4);
+            t += __shfl_xor_sync(0xffffffffu, t, 2);
+            t += __shfl_xor_sync(0xffffffffu, t, 1);
+            const int which = (lane >> 2) & 7, r = which >> 1, u = which & 1;
+            if ((lane & 3) == 0 && r < nrows && base + j + u < Nkv) out[(long long)r * Nkv + base + j + u] = __fmul_rn((float)t, scale);
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();      // the logits are complete (and visible to the whole CTA) and the staging memory is free
 }
 
 __global__ void __launch_bounds__(SCORE_THREADS)
@@ -491,36 +581,129 @@ route_count_kernel(const float *__restrict__ attn, const int32_t *__restrict__ i
 // last head prepares the attention kernel's launch (work order, counters).  Same arithmetic as the
 // three separate kernels above; no CTA ever waits for another.
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int B, int H, int Nq, int Nkv, int n_pow2,
-                   int D, float scale, float tau_min, float tau_span, const int32_t *__restrict__ fixed_num,
-                   float *sorted, int32_t *__restrict__ index, int32_t *num, float *__restrict__ thresholds,
-                   float *gini_rows, int *counters, SchedJob job, int gate_per_cta, int sm_count, int slots) {
-    extern __shared__ __align__(16) unsigned char fused_smem[];
-    unsigned long long *keys = reinterpret_cast<unsigned long long *>(fused_smem);   // max(n_pow2, threads)
-    float *probs = reinterpret_cast<float *>(keys + max(n_pow2, (int)blockDim.x));    // Nkv
-    __shared__ double red[256];
-    __shared__ float bcast;
-    __shared__ int last_flag;
+__device__ __forceinline__ void sort_keys_smem(unsigned long long *keys, int n_pow2);
 
+// The k best blocks of a row, in order, WITHOUT sorting the row: for a fixed per-head count over thousands of key blocks
+// the full bitonic sort (105 passes over 16384 keys) was two thirds of the routing kernel.  Keys are the sort's own
+// 64-bit keys (descending probability, then ascending id; all distinct).  A most-significant-byte-first radix select
+// finds the k-th smallest key (at most eight histogram passes over the row, usually three or four: it stops as soon as
+// one histogram bin holds exactly the keys still needed), the k keys at or below it are collected and only they are
+// sorted.  `idx[0..k)` receive the same ids in the same order as the full sort; slots past k are not written.
+// `keys` is shared memory for >= max(1024, pow2(k)) entries.  Called by every thread of the CTA (>= 256 threads).
+__device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, int k, unsigned long long *keys, int32_t *idx) {
+    __shared__ unsigned int hist[256];
+    __shared__ unsigned long long prefix_s, mask_s;
+    __shared__ int need_s, done_s;
+    __shared__ unsigned int taken_s;
+    const int T = blockDim.x, tid = threadIdx.x;
+    if (k <= 0) return;
+    auto key_of = [&](int j) { return ((unsigned long long)descending_key(probs[j]) << 32) | (unsigned)j; };
+    if (tid == 0) {
+        prefix_s = 0ull;
+        mask_s = 0ull;
+        need_s = k;
+        done_s = k >= Nkv;     // every block is kept: nothing to select
+        taken_s = 0u;
+    }
+    __syncthreads();
+    for (int byte = 7; byte >= 0 && !done_s; --byte) {
+        if (tid < 256) hist[tid] = 0u;
+        __syncthreads();
+        const unsigned long long prefix = prefix_s, mask = mask_s;
+        for (int j0 = 0; j0 < Nkv; j0 += T) {      // whole warps iterate together: the votes below need every lane
+            const int j = j0 + tid;
+            const unsigned long long key = j < Nkv ? key_of(j) : 0ull;
+            const bool cand = j < Nkv && (key & mask) == prefix;
+            const unsigned int voters = __ballot_sync(0xffffffffu, cand);
+            if (cand) {
+                // probabilities of one row share their leading bits, so most keys of a pass fall into one bin: one
+                // atomic per distinct digit of the warp instead of one per key
+                const unsigned int digit = (unsigned)(key >> (8 * byte)) & 255u;
+                const unsigned int peers = __match_any_sync(voters, digit);
+                if ((tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[digit], (unsigned)__popc(peers));
+            }
+        }
+        __syncthreads();
+        if (tid < 32) {      // first digit at which the running count reaches what is still needed
+            unsigned int mine[8], sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                mine[i] = hist[tid * 8 + i];
+                sum += mine[i];
+            }
+            unsigned int incl = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (tid >= o) incl += v;
+            }
+            const unsigned int need = (unsigned)need_s, before = incl - sum;
+            if (before < need && need <= incl) {      // exactly one lane
+                unsigned int run = before, in_bin = 0;
+                int d = -1;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (d < 0) {
+                        if (need <= run + mine[i]) {
+                            d = i;
+                            in_bin = mine[i];
+                        } else {
+                            run += mine[i];
+                        }
+                    }
+                }
+                prefix_s = prefix | ((unsigned long long)(tid * 8 + d) << (8 * byte));
+                mask_s = mask | (0xFFull << (8 * byte));
+                need_s = (int)(need - run);
+                if (in_bin == need - run) done_s = 1;      // the whole bin is wanted: no finer digit needed
+            }
+        }
+        __syncthreads();
+    }
+    // collect the keys at or below the k-th (with all keys kept when k >= Nkv: mask 0, prefix 0), then sort just those
+    const unsigned long long prefix = prefix_s, mask = mask_s;
+    for (int j = tid; j < Nkv; j += T) {
+        const unsigned long long key = key_of(j);
+        if ((key & mask) <= prefix) keys[atomicAdd(&taken_s, 1u)] = key;
+    }
+    __syncthreads();
+    const int kept = (int)taken_s;      // == min(k, Nkv)
+    int k_pow2 = 1;
+    while (k_pow2 < kept) k_pow2 <<= 1;
+    for (int j = kept + tid; j < k_pow2; j += T) keys[j] = 0xFFFFFFFFFFFFFFFFull;
+    __syncthreads();
+    sort_keys_smem(keys, k_pow2);
+    for (int m = tid; m < kept; m += T) idx[m] = (int32_t)(keys[m] & 0xFFFFFFFFull);
+    __syncthreads();
+}
+
+// One (batch, head, query block) row of the fused routing; called by every thread of the CTA.  With `logits_ready`
+// the row's scaled logits already lie in `sorted + row * Nkv` (written by this CTA).
+__device__ __forceinline__ void route_row(const long long row, const bool logits_ready, const float *__restrict__ qp,
+                                          const float *__restrict__ kp, int B, int H, int Nq, int Nkv, int n_pow2, int D, float scale,
+                                          float tau_min, float tau_span, const int32_t *__restrict__ fixed_num, float *sorted,
+                                          int32_t *__restrict__ index, int32_t *num, float *__restrict__ thresholds, float *gini_rows,
+                                          int *counters, const SchedJob &job, unsigned long long *keys, float *probs, double *red,
+                                          float &bcast, int &last_flag, const bool select_only) {
     const int T = blockDim.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = T >> 5;
-    // CTAs are dealt to the SMs round-robin, so CTAs b, b + sm_count, ... tend to share an SM: give them
-    // neighbouring rows (same head, same pooled keys) so that their key reads can meet in L1
-    const long long row = (long long)(blockIdx.x % sm_count) * slots + blockIdx.x / sm_count;
-    // No early release of the attention kernel here: its CTAs, once resident and waiting, slowed the tail of this
-    // kernel (the per-head count and the work order are a few CTAs' work) by about 5 us.
-    pdl_wait();                 // pooled means and zeroed counters come from the launch before
-    if (row >= (long long)B * H * Nq) return;
     const long long bh = row / Nq;
     const int h = (int)(bh % H);
 
-    ROUTE_STAMP(0);
-    if (job.order && job.gate_w) convert_gate_slice(job, (int)row * gate_per_cta, gate_per_cta);
-
-    row_block_attention(qp + row * D, kp + bh * (long long)Nkv * D, Nkv, D, scale, probs, red, &bcast);
+    if (logits_ready) {
+        const float *lrow = sorted + row * Nkv;
+        for (int j = tid; j < Nkv; j += T) probs[j] = lrow[j];
+    } else {
+        row_logits(qp + row * D, kp + bh * (long long)Nkv * D, Nkv, D, scale, probs);
+    }
+    __syncthreads();
+    ROUTE_STAMP(1);
+    row_softmax(Nkv, probs, red, &bcast);
     ROUTE_STAMP(2);
 
-    if (n_pow2 <= T) {
+    if (select_only) {
+        // fixed per-head count and nobody asked for the whole order or the thresholds: pick the head's k best blocks
+        select_top_blocks(probs, Nkv, max(0, min(fixed_num[h], Nkv)), keys, index + row * Nkv);
+    } else if (n_pow2 <= T) {
         // one key per thread in a register: exchange distances below 32 go through shuffles, the rest through smem
         unsigned long long key = tid < Nkv ? (((unsigned long long)descending_key(probs[tid]) << 32) | (unsigned)tid)
                                            : 0xFFFFFFFFFFFFFFFFull;
@@ -564,7 +747,7 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
         }
     }
     ROUTE_STAMP(3);
-    {
+    if (!select_only) {
         int32_t *idx = index + row * Nkv;
         double acc = 0.0;
         for (int m = tid; m < Nkv; m += T) {
@@ -617,20 +800,22 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
     if (tid == 0) last_flag = atomicAdd(&counters[1 + h], 1) == rows_per_head - 1;
     __syncthreads();
     ROUTE_STAMP(5);
+    // experiment: let the attention kernel's CTAs become resident while only the heads' last CTAs are still at work
+    if (job.release_dependents_after_rows) pdl_release_dependents();
     if (!last_flag) return;
     __threadfence();
 
-    const float thr = head_threshold(gini_rows, B, H, Nq, h, tau_min, tau_span, red, &bcast);
-    if (tid == 0) thresholds[h] = thr;
+    const float thr = select_only ? 0.f : head_threshold(gini_rows, B, H, Nq, h, tau_min, tau_span, red, &bcast);
+    if (tid == 0 && !select_only) thresholds[h] = thr;
     ROUTE_STAMP(8);
     if (fixed_num) {
         const int n = max(0, min(fixed_num[h], Nkv));
         for (int r = tid; r < rows_per_head; r += T) num[((long long)(r / Nq) * H + h) * Nq + r % Nq] = n;
     } else {
         // kept blocks of a row = positions whose mass-before is under the threshold.  All rows of the head are
-        // counted together, sixteen independent loads per thread at a time: the loop is one CTA's, so it is the
+        // counted together, a batch of independent loads per thread at a time: the loop is one CTA's, so it is the
         // memory round trips, not the arithmetic, that it has to keep few.
-        constexpr int ROWS_AT_ONCE = 128, LOADS = 16;
+        constexpr int ROWS_AT_ONCE = 128, LOADS = 8;
         __shared__ int row_count[ROWS_AT_ONCE];
         __shared__ long long row_base[ROWS_AT_ONCE];
         const int step_r = T / Nkv, step_m = T % Nkv;   // element e -> (row e / Nkv, position e % Nkv), advanced without dividing
@@ -645,7 +830,7 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
             if ((Nkv & 3) == 0) {
                 // four positions per load; a thread's loads are all issued before the first is used
                 const int quads_per_row = Nkv >> 2, total = nr * quads_per_row;
-                constexpr int QLOADS = 10;
+                constexpr int QLOADS = 8;
                 for (int e0 = 0; e0 < total; e0 += QLOADS * T) {
                     float4 c[QLOADS];
                     int rr[QLOADS];
@@ -714,6 +899,58 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
     __threadfence();
     schedule_items(num, B * H * Nq, Nkv, job.order, job.work_counter, job.error_flag);
     ROUTE_STAMP(7);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The forward's routing in ONE launch.  Each CTA owns one row, or (thousands of key blocks, head_dim 128) four
+// neighbouring rows of a head whose logits it computes in one pass over the pooled keys.
+// ------------------------------------------------------------------------------------------------
+template <int ROWS>   // rows per CTA: 1 or 4 (four rows: at most 512 threads, for the registers of row_logits_x4)
+__global__ void __launch_bounds__(ROWS > 1 ? 512 : 1024)
+route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int B, int H, int Nq, int Nkv, int n_pow2,
+                   int D, float scale, float tau_min, float tau_span, const int32_t *__restrict__ fixed_num,
+                   float *sorted, int32_t *__restrict__ index, int32_t *num, float *__restrict__ thresholds,
+                   float *gini_rows, int *counters, SchedJob job, int gate_per_cta, int sm_count, int slots, int groups_per_bh,
+                   int select_only) {
+    constexpr int rows_per_cta = ROWS;
+    extern __shared__ __align__(16) unsigned char fused_smem[];
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(fused_smem);   // max(n_pow2, threads)
+    float *probs = reinterpret_cast<float *>(keys + max(n_pow2, (int)blockDim.x));    // Nkv
+    __shared__ double red[256];
+    __shared__ float bcast;
+    __shared__ int last_flag;
+
+    // CTAs are dealt to the SMs round-robin, so CTAs b, b + sm_count, ... tend to share an SM: give them
+    // neighbouring rows (same head, same pooled keys) so that their key reads can meet in L1
+    const long long group = (long long)(blockIdx.x % sm_count) * slots + blockIdx.x / sm_count;
+    // No early release of the attention kernel here: its CTAs, once resident and waiting, slowed the tail of this
+    // kernel (the per-head count and the work order are a few CTAs' work) by about 5 us.
+    pdl_wait();                 // pooled means and zeroed counters come from the launch before
+    if (group >= (long long)B * H * groups_per_bh) return;
+    const long long bh = group / groups_per_bh;
+    const int i0 = (int)(group % groups_per_bh) * rows_per_cta, nrows = min(rows_per_cta, Nq - i0);
+    const long long row0 = bh * Nq + i0;
+
+    ROUTE_STAMP(0);
+    if (job.order && job.gate_w) convert_gate_slice(job, (int)group * gate_per_cta, gate_per_cta);
+
+    if constexpr (ROWS > 1) {
+        // the sort keys' shared memory is free until the first row is sorted: the pooled keys are staged through it
+        const int key_bytes = max(n_pow2, (int)blockDim.x) * 8;
+        const int tile_keys = min(key_bytes / 4 / 512, 64) & ~1;   // four staging buffers (row_logits_x4)
+        row_logits_x4(qp + row0 * D, nrows, kp + bh * (long long)Nkv * D, Nkv, scale, sorted + row0 * Nkv,
+                      reinterpret_cast<float4 *>(keys), tile_keys);   // ends with a barrier: the rows below read these logits back
+    }
+    if constexpr (ROWS == 1) {
+        route_row(row0, false, qp, kp, B, H, Nq, Nkv, n_pow2, D, scale, tau_min, tau_span, fixed_num, sorted, index, num, thresholds,
+                  gini_rows, counters, job, keys, probs, red, bcast, last_flag, select_only != 0);
+        return;
+    }
+    for (int r = 0; r < nrows; ++r) {
+        route_row(row0 + r, true, qp, kp, B, H, Nq, Nkv, n_pow2, D, scale, tau_min, tau_span, fixed_num, sorted, index,
+                  num, thresholds, gini_rows, counters, job, keys, probs, red, bcast, last_flag, select_only != 0);
+        __syncthreads();
+    }
 }
 
 #ifdef WA_ROUTE_TRACE
@@ -999,7 +1236,7 @@ int route_select_launch(const float *block_attn, int B, int H, int Nq, int Nkv, 
 namespace wa {
 int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int H, int Nq, int Nkv, int D, double tau_min,
                        double tau_max, const int32_t *fixed_num_per_head, float *sorted, int32_t *index, int32_t *num,
-                       float *thresholds, float *gini, int *counters, const SchedJob &job, cudaStream_t stream) {
+                       float *thresholds, float *gini, int *counters, const SchedJob &job_in, cudaStream_t stream, bool whole_order) {
     int n_pow2 = 1;
     while (n_pow2 < Nkv) n_pow2 <<= 1;
     WA_REQUIRE(n_pow2 <= 16384, WA_ERR_UNSUPPORTED, "wa_hsa_forward(routing): at most 16384 key blocks per row, got %d", Nkv);
@@ -1009,20 +1246,36 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
     threads = threads < 256 ? 256 : (threads > 1024 ? 1024 : threads);
     const size_t smem = (size_t)(n_pow2 > threads ? n_pow2 : threads) * sizeof(unsigned long long) + (size_t)Nkv * sizeof(float);
     if (smem > 24 * 1024) {   // static shared memory of the kernel takes ~19 KB of the default 48 KB
-        cudaError_t e = cudaFuncSetAttribute(route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(route_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(route_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(routing): %s", cudaGetErrorString(e));
     }
-    const int gate_per_cta = (int)((128 * 128 + rows - 1) / rows);
+    // four rows per CTA where a row's keys are megabytes (see row_logits_x4); one row per CTA where the kernel is latency
+    const int rows_per_cta = (Nkv > 1024 && D == 128 && ((uintptr_t)q_pooled % 16 == 0) && ((uintptr_t)k_pooled % 16 == 0)) ? 4 : 1;
+    const int groups_per_bh = (Nq + rows_per_cta - 1) / rows_per_cta;
+    const long long groups = (long long)B * H * groups_per_bh;
+    const int gate_per_cta = (int)((128 * 128 + groups - 1) / groups);
     int dev = 0, sm_count = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
         sm_count = 148;
-    if (rows < sm_count) sm_count = (int)rows;
-    const int slots = (int)((rows + sm_count - 1) / sm_count);
-    cudaError_t le = launch_dependent(route_fused_kernel, dim3((unsigned)((long long)sm_count * slots)), dim3(threads), smem, stream,
-                                      q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2, D, (float)pow((double)D, -0.5), (float)tau_min,
-                                      (float)(tau_max - tau_min), fixed_num_per_head, sorted, index, num, thresholds, gini, counters,
-                                      job, gate_per_cta, sm_count, slots);
+    if (groups < sm_count) sm_count = (int)groups;
+    const int slots = (int)((groups + sm_count - 1) / sm_count);
+    const dim3 grid((unsigned)((long long)sm_count * slots));
+    const float scale = (float)pow((double)D, -0.5), span = (float)(tau_max - tau_min);
+    SchedJob job = job_in;
+    job.release_dependents_after_rows = pdl_mode() == 2;
+    // a fixed count per head over more key blocks than one pass of the register sort covers, and nobody reads the whole
+    // order or the thresholds: select the best blocks instead of sorting all of them
+    const int select_only = fixed_num_per_head && !whole_order && n_pow2 > threads;
+    if (rows_per_cta == 4 && threads > 512) threads = 512;
+    cudaError_t le = rows_per_cta == 4
+                         ? launch_dependent(route_fused_kernel<4>, grid, dim3(threads), smem, stream, q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2,
+                                            D, scale, (float)tau_min, span, fixed_num_per_head, sorted, index, num, thresholds, gini,
+                                            counters, job, gate_per_cta, sm_count, slots, groups_per_bh, select_only)
+                         : launch_dependent(route_fused_kernel<1>, grid, dim3(threads), smem, stream, q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2,
+                                            D, scale, (float)tau_min, span, fixed_num_per_head, sorted, index, num, thresholds, gini,
+                                            counters, job, gate_per_cta, sm_count, slots, groups_per_bh, select_only);
     if (le != cudaSuccess) return fail((int)le, "wa_hsa_forward(routing): %s", cudaGetErrorString(le));
     return check_launch("wa_hsa_forward(routing)");
 }

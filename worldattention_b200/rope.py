@@ -31,10 +31,11 @@ def _grid(grid_sizes) -> tuple[int, int, int]:
 
 
 def qk_norm_rope(x: torch.Tensor, norm_weight: torch.Tensor | None, eps: float, grid_sizes, freqs: torch.Tensor | None,
-                 start_frame: int = 0, *, heads: int | None = None, table: torch.Tensor | None = None) -> torch.Tensor:
+                 start_frame=0, *, heads: int | None = None, table: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm over the last axis of `[B, L, H*D]` (or `[B, L, H, D]`), then the causal rotary embedding -> `[B, L, H, D]`.
 
-    `table` is `_table(freqs)` kept by the caller (saves the conversion per call)."""
+    `table` is `_table(freqs)` kept by the caller (saves the conversion per call).  `start_frame` may be an int32 device
+    tensor of one element: the kernel then reads the position when it runs (for launches replayed from a CUDA graph)."""
     dev = _lib.require_cuda(x)
     if x.dim() == 3:
         if heads is None:
@@ -50,10 +51,15 @@ def qk_norm_rope(x: torch.Tensor, norm_weight: torch.Tensor | None, eps: float, 
             raise NotImplementedError(f"the grid {f}x{h}x{w} must cover all {length} tokens")
         table = _table(freqs, dev) if table is None else table
     weight = None if norm_weight is None else norm_weight.detach().to(dev).contiguous()
-    _lib.check(_lib.lib().wa_qk_norm_rope(
-        _lib.t4_blhd(x), _lib.t4_blhd(out), bsz, length, n_heads, head_dim, _lib.ptr(weight),
-        _lib.dtype_code(weight.dtype) if weight is not None else 0, float(eps), _lib.ptr(table),
-        int(table.shape[0]) if table is not None else 0, int(start_frame), h, w, _lib.stream_ptr(dev)))
+    head = (_lib.t4_blhd(x), _lib.t4_blhd(out), bsz, length, n_heads, head_dim, _lib.ptr(weight),
+            _lib.dtype_code(weight.dtype) if weight is not None else 0, float(eps), _lib.ptr(table),
+            int(table.shape[0]) if table is not None else 0)
+    if isinstance(start_frame, torch.Tensor):
+        if start_frame.dtype != torch.int32 or start_frame.numel() != 1 or start_frame.device != dev:
+            raise ValueError("a device-resident start_frame must be one int32 on the tensors' device")
+        _lib.check(_lib.lib().wa_qk_norm_rope_at(*head, start_frame.data_ptr(), h, w, _lib.stream_ptr(dev)))
+    else:
+        _lib.check(_lib.lib().wa_qk_norm_rope(*head, int(start_frame), h, w, _lib.stream_ptr(dev)))
     return out
 
 
