@@ -111,9 +111,16 @@ def test_large_logits_exercise_the_running_max_rescale(wa):
 def test_more_than_1024_key_blocks_route_four_rows_per_cta(wa):
     # 1032 key blocks: the routing kernel scores four query blocks per CTA in one pass over the pooled keys; 5 query
     # blocks = one full group and a group of one.  Same order, counts and thresholds as the oracle.
-    _run_case(wa, seed=7, bsz=1, heads=2, q_len=600, kv_len=132000, seg=1320, topk=[3, 10], scale=1.0 / math.sqrt(D),
-              whole_order=True)
-    _run_case(wa, seed=8, bsz=2, heads=1, q_len=300, kv_len=131100, seg=1311, topk=None, scale=0.5, whole_order=True)
+    import os
+    try:
+        for rows in ("4", "2", "1"):      # rows scored per CTA: the launcher's choice depends on the SM count, so pin each
+            os.environ["WA_B200_ROUTE_ROWS"] = rows
+            _run_case(wa, seed=7, bsz=1, heads=2, q_len=600, kv_len=132000, seg=1320, topk=[3, 10], scale=1.0 / math.sqrt(D),
+                      whole_order=True)
+        os.environ["WA_B200_ROUTE_ROWS"] = "4"
+        _run_case(wa, seed=8, bsz=2, heads=1, q_len=300, kv_len=131100, seg=1311, topk=None, scale=0.5, whole_order=True)
+    finally:
+        os.environ.pop("WA_B200_ROUTE_ROWS", None)
 
 
 def test_fixed_counts_over_many_key_blocks_select_instead_of_sorting(wa):
@@ -124,13 +131,16 @@ def test_fixed_counts_over_many_key_blocks_select_instead_of_sorting(wa):
     q, k, v = (to_gpu(_draw(rng, (1, n, heads, D), s), "bf16") for n, s in ((q_len, 0.2), (kv_len, 0.2), (kv_len, 1.0)))
     ek = to_gpu(_proj(math.ceil(seg / 64), seg, 64, rng), "bf16")
     lin = torch.nn.Linear(D, D).to(dev())
-    for topk in ([32, 1, 7], [0, 1300, 64]):        # 1300 > 1250 key blocks: every block kept
+    import os
+    for topk, rows in (([32, 1, 7], "4"), ([0, 1300, 64], "2")):        # 1300 > 1250 key blocks: every block kept
+        os.environ["WA_B200_ROUTE_ROWS"] = rows
         kw = dict(k_proj_mat=ek, v_proj_mat=ek, gate_lin=lin, block_size=64, proj_segment_len=seg,
                   topk_per_head=torch.tensor(topk, dtype=torch.int32), check_status=True)
         sorted_out, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, return_routing=True, **kw)
         picked_out = wa.hsa.hsa_attention(q, k, v, **kw)
         assert used and torch.equal(sorted_out, picked_out)
         assert num[0, :, 0].tolist() == [min(t, 1250) for t in topk]
+    os.environ.pop("WA_B200_ROUTE_ROWS", None)
 
 
 def test_config2_shape_head_adaptive_topk(wa):

@@ -38,6 +38,23 @@ def _worker(rank, world, port, results):
         blob = [None] * world
         dist.all_gather_object(blob, (shards, sharded.plan_head_split(12, world, [4, 8, 16, 32] * 3)))
         assert all(b == blob[0] for b in blob)
+        # the row exchange of the KV-sharded forward: rank j receives rows [j * rp, (j + 1) * rp) of every shard's records
+        q_len, heads, rec = 7, 2, 5                      # ragged: 4 + 3 rows
+        rp, row_plan = sharded.exchange_rows(q_len, world)
+        assert (rp, row_plan) == (4, [(0, 4), (4, 3)])
+        records = torch.zeros((rp * world, heads, rec))
+        records[:q_len] = (rank * 1000 + torch.arange(q_len, dtype=torch.float32)).view(-1, 1, 1)
+        recv = torch.empty_like(records)
+        dist.all_to_all_single(recv, records)
+        got = recv.view(world, rp, heads, rec)
+        first, count = row_plan[rank]
+        for shard in range(world):
+            assert got[shard, :count, 0, 0].tolist() == [shard * 1000.0 + first + r for r in range(count)]
+        rows = torch.full((rp, heads, 3), -1.0)
+        rows[:count] = (first + torch.arange(count, dtype=torch.float32)).view(-1, 1, 1)
+        full = torch.empty((world * rp, heads, 3))
+        dist.all_gather_into_tensor(full, rows)
+        assert full[:q_len, 0, 0].tolist() == [float(r) for r in range(q_len)]
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()

@@ -336,7 +336,7 @@ __device__ __forceinline__ void row_block_attention(const float *__restrict__ q,
     row_softmax(Nkv, out, red, bcast);
 }
 
-// Logits of FOUR neighbouring rows of one head against one pass over the head's pooled keys (D = 128 only): with
+// Logits of R (2 or 4) neighbouring rows of one head against one pass over the head's pooled keys (D = 128 only): with
 // thousands of key blocks a row's CTA otherwise re-reads megabytes of pooled keys that its neighbours read too, and
 // converts each to float64 again.  Same additions in the same order as `row_logits`, so the same bits.  `q` holds the
 // rows `D` apart, `out` holds them `Nkv` apart; rows >= nrows repeat row 0's query and are not stored.  The queries stay
@@ -344,13 +344,15 @@ __device__ __forceinline__ void row_block_attention(const float *__restrict__ q,
 // shared-memory-bound: 350 us per group at 11 700 key blocks).  The keys pass through
 // `stage` (shared memory, 4 * tile_keys rows of 512 bytes) in tiles fetched with asynchronous copies, three ahead of the
 // one being computed on.
-__device__ __forceinline__ void row_logits_x4(const float *__restrict__ q, int nrows, const float *__restrict__ k, int Nkv,
+template <int R>   // rows scored together: 2 or 4; a warp's round is 8 / R keys x R rows
+__device__ __forceinline__ void row_logits_xr(const float *__restrict__ q, int nrows, const float *__restrict__ k, int Nkv,
                                               float scale, float *out, float4 *stage, int tile_keys) {
     constexpr int D = 128, VPK = D / 4;   // 16-byte vectors per key
     const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
-    double qd[4][4];      // this lane's four dimensions of the four rows (the kernel runs 512 threads: 128 registers each)
+    constexpr int KEYS = 8 / R;
+    double qd[R][4];      // this lane's four dimensions of the R rows (the kernel runs 512 threads: 128 registers each)
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < R; ++r) {
         const float4 qv = *reinterpret_cast<const float4 *>(q + (r < nrows ? r : 0) * D + lane * 4);
         qd[r][0] = (double)qv.x; qd[r][1] = (double)qv.y; qd[r][2] = (double)qv.z; qd[r][3] = (double)qv.w;
     }
@@ -383,19 +385,19 @@ __device__ __forceinline__ void row_logits_x4(const float *__restrict__ q, int n
         fetch(tile + STAGES - 1);
         const float4 *kt = stage + (tile % STAGES) * tile_vecs;
         const int base = tile * tile_keys;
-        for (int j = warp * 2; j < tile_keys && base + j < Nkv; j += nwarps * 2) {      // two keys x four rows per warp and pass
-            double acc[8];     // acc[r * 2 + u]
+        for (int j = warp * KEYS; j < tile_keys && base + j < Nkv; j += nwarps * KEYS) {      // KEYS keys x R rows per warp and round
+            double acc[8];     // acc[r * KEYS + u]
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < KEYS; ++u) {
                 const float4 kv = kt[(j + u) * VPK + lane];    // a key past the end of the tile's real keys is zeros
                 const double k0 = (double)kv.x, k1 = (double)kv.y, k2 = (double)kv.z, k3 = (double)kv.w;
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
+                for (int r = 0; r < R; ++r) {
                     double a = fma(qd[r][0], k0, 0.0);
                     a = fma(qd[r][1], k1, a);
                     a = fma(qd[r][2], k2, a);
                     a = fma(qd[r][3], k3, a);
-                    acc[r * 2 + u] = a;
+                    acc[r * KEYS + u] = a;
                 }
             }
             // transposed reduction, as in row_logits: lane l ends with sum (l >> 2) & 7
@@ -414,7 +416,7 @@ __device__ __forceinline__ void row_logits_x4(const float *__restrict__ q, int n
             double t = (b4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, b4 ? r2[0] : r2[1], 4);
             t += __shfl_xor_sync(0xffffffffu, t, 2);
             t += __shfl_xor_sync(0xffffffffu, t, 1);
-            const int which = (lane >> 2) & 7, r = which >> 1, u = which & 1;
+            const int which = (lane >> 2) & 7, r = which / KEYS, u = which % KEYS;
             if ((lane & 3) == 0 && r < nrows && base + j + u < Nkv) out[(long long)r * Nkv + base + j + u] = __fmul_rn((float)t, scale);
         }
     }
@@ -905,7 +907,7 @@ __device__ __forceinline__ void route_row(const long long row, const bool logits
 // The forward's routing in ONE launch.  Each CTA owns one row, or (thousands of key blocks, head_dim 128) four
 // neighbouring rows of a head whose logits it computes in one pass over the pooled keys.
 // ------------------------------------------------------------------------------------------------
-template <int ROWS>   // rows per CTA: 1 or 4 (four rows: at most 512 threads, for the registers of row_logits_x4)
+template <int ROWS>   // rows per CTA: 1, 2 or 4 (several rows: at most 512 threads, for the registers of row_logits_xr)
 __global__ void __launch_bounds__(ROWS > 1 ? 512 : 1024)
 route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int B, int H, int Nq, int Nkv, int n_pow2,
                    int D, float scale, float tau_min, float tau_span, const int32_t *__restrict__ fixed_num,
@@ -937,8 +939,8 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
     if constexpr (ROWS > 1) {
         // the sort keys' shared memory is free until the first row is sorted: the pooled keys are staged through it
         const int key_bytes = max(n_pow2, (int)blockDim.x) * 8;
-        const int tile_keys = min(key_bytes / 4 / 512, 64) & ~1;   // four staging buffers (row_logits_x4)
-        row_logits_x4(qp + row0 * D, nrows, kp + bh * (long long)Nkv * D, Nkv, scale, sorted + row0 * Nkv,
+        const int tile_keys = min(key_bytes / 4 / 512, 64) & ~7;   // four staging buffers (row_logits_xr)
+        row_logits_xr<ROWS>(qp + row0 * D, nrows, kp + bh * (long long)Nkv * D, Nkv, scale, sorted + row0 * Nkv,
                       reinterpret_cast<float4 *>(keys), tile_keys);   // ends with a barrier: the rows below read these logits back
     }
     if constexpr (ROWS == 1) {
@@ -1247,18 +1249,30 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
     const size_t smem = (size_t)(n_pow2 > threads ? n_pow2 : threads) * sizeof(unsigned long long) + (size_t)Nkv * sizeof(float);
     if (smem > 24 * 1024) {   // static shared memory of the kernel takes ~19 KB of the default 48 KB
         cudaError_t e = cudaFuncSetAttribute(route_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(route_fused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(route_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(routing): %s", cudaGetErrorString(e));
     }
-    // four rows per CTA where a row's keys are megabytes (see row_logits_x4); one row per CTA where the kernel is latency
-    const int rows_per_cta = (Nkv > 1024 && D == 128 && ((uintptr_t)q_pooled % 16 == 0) && ((uintptr_t)k_pooled % 16 == 0)) ? 4 : 1;
-    const int groups_per_bh = (Nq + rows_per_cta - 1) / rows_per_cta;
-    const long long groups = (long long)B * H * groups_per_bh;
-    const int gate_per_cta = (int)((128 * 128 + groups - 1) / groups);
+    // several rows per CTA where a row's keys are megabytes (see row_logits_xr); one row per CTA where the kernel is latency.
+    // Four rows share more key conversions than two, but the CTAs come in waves of one per SM (their shared memory fills
+    // it): take the count with fewer row-times on the busiest SM, four on a tie.
     int dev = 0, sm_count = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
         sm_count = 148;
+    int rows_per_cta = 1;
+    if (Nkv > 1024 && D == 128 && ((uintptr_t)q_pooled % 16 == 0) && ((uintptr_t)k_pooled % 16 == 0)) {
+        auto row_times = [&](int r) {
+            const long long g = (long long)B * H * ((Nq + r - 1) / r);
+            return ((g + sm_count - 1) / sm_count) * r;
+        };
+        rows_per_cta = row_times(2) < row_times(4) ? 2 : 4;
+        if (const char *e = getenv("WA_B200_ROUTE_ROWS"))      // tuning aid
+            if (e[0] == '1' || e[0] == '2' || e[0] == '4') rows_per_cta = e[0] - '0';
+    }
+    const int groups_per_bh = (Nq + rows_per_cta - 1) / rows_per_cta;
+    const long long groups = (long long)B * H * groups_per_bh;
+    const int gate_per_cta = (int)((128 * 128 + groups - 1) / groups);
     if (groups < sm_count) sm_count = (int)groups;
     const int slots = (int)((groups + sm_count - 1) / sm_count);
     const dim3 grid((unsigned)((long long)sm_count * slots));
@@ -1268,14 +1282,14 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
     // a fixed count per head over more key blocks than one pass of the register sort covers, and nobody reads the whole
     // order or the thresholds: select the best blocks instead of sorting all of them
     const int select_only = fixed_num_per_head && !whole_order && n_pow2 > threads;
-    if (rows_per_cta == 4 && threads > 512) threads = 512;
-    cudaError_t le = rows_per_cta == 4
-                         ? launch_dependent(route_fused_kernel<4>, grid, dim3(threads), smem, stream, q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2,
-                                            D, scale, (float)tau_min, span, fixed_num_per_head, sorted, index, num, thresholds, gini,
-                                            counters, job, gate_per_cta, sm_count, slots, groups_per_bh, select_only)
-                         : launch_dependent(route_fused_kernel<1>, grid, dim3(threads), smem, stream, q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2,
-                                            D, scale, (float)tau_min, span, fixed_num_per_head, sorted, index, num, thresholds, gini,
-                                            counters, job, gate_per_cta, sm_count, slots, groups_per_bh, select_only);
+    if (rows_per_cta > 1 && threads > 512) threads = 512;
+    auto launch = [&](auto kernel) {
+        return launch_dependent(kernel, grid, dim3(threads), smem, stream, q_pooled, k_pooled, B, H, Nq, Nkv, n_pow2, D, scale,
+                                (float)tau_min, span, fixed_num_per_head, sorted, index, num, thresholds, gini, counters, job,
+                                gate_per_cta, sm_count, slots, groups_per_bh, select_only);
+    };
+    cudaError_t le = rows_per_cta == 4 ? launch(route_fused_kernel<4>)
+                                       : (rows_per_cta == 2 ? launch(route_fused_kernel<2>) : launch(route_fused_kernel<1>));
     if (le != cudaSuccess) return fail((int)le, "wa_hsa_forward(routing): %s", cudaGetErrorString(le));
     return check_launch("wa_hsa_forward(routing)");
 }
