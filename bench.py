@@ -51,7 +51,7 @@ WORKLOADS = {
 L2_FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel on workload c2 (ncu capture summarised
 # in profiles/hsa_fwd_sm100_config2.md)
-NCU_TRAFFIC_BYTES = 165.6e6
+NCU_TRAFFIC_BYTES = 167.3e6   # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel (profiles/hsa_fwd_sm100_config2.md)
 
 
 # ------------------------------------------------------------------------------------------------

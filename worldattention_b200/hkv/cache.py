@@ -85,10 +85,24 @@ class HKVCache:
         _lib.require_cuda(kv_cache[0]["k"])
 
         chunk_id = len(self.chunks)
+        # one allocation for the whole chunk (views per layer) instead of one per layer and tensor: growing the
+        # allocator's pool costs a driver call per allocation, which at 60 calls per stored window showed as stalls of
+        # up to a second at a prompt switch
+        first = kv_cache[0]["k"]
+        uniform = all(block[name].shape == first.shape and block[name].dtype == first.dtype and block[name].device == first.device
+                      for block in kv_cache for name in ("k", "v"))
         blob = {"k": [], "v": []}
-        for block in kv_cache:
-            blob["k"].append(block["k"][:, :valid_tokens].detach().clone())
-            blob["v"].append(block["v"][:, :valid_tokens].detach().clone())
+        if uniform:
+            slab = torch.empty((2, len(kv_cache), first.shape[0], valid_tokens) + tuple(first.shape[2:]), dtype=first.dtype,
+                               device=first.device)
+            for layer, block in enumerate(kv_cache):
+                for which, name in enumerate(("k", "v")):
+                    slab[which, layer].copy_(block[name][:, :valid_tokens].detach())
+                    blob[name].append(slab[which, layer])
+        else:
+            for block in kv_cache:
+                blob["k"].append(block["k"][:, :valid_tokens].detach().clone())
+                blob["v"].append(block["v"][:, :valid_tokens].detach().clone())
 
         page_spans = [(start, min(start + self.page_tokens, valid_tokens))
                       for start in range(0, valid_tokens, self.page_tokens)]
