@@ -171,7 +171,7 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def raise_if_failed(device: torch.device) -> None:
-    """Raise if an earlier tcgen05 launch on `device` gave up at a bounded wait (its output is invalid).
+    """Raise if an earlier launch of an HSA forward on `device` gave up at a bounded wait (its output is invalid).
 
     Reads host memory only: no copy, no synchronisation.  A failure of a launch that is still in flight shows
     at the next call or at the caller's next synchronisation point followed by this check.
@@ -180,7 +180,9 @@ def raise_if_failed(device: torch.device) -> None:
     if word is not None and int(word[0]) != 0:
         code = int(word[0])
         word.zero_()
-        raise RuntimeError(f"an earlier tcgen05 HSA launch on {device} gave up at wait site {code}; its output is invalid")
+        kernel = "block-pooling (TMA stream)" if code in (201, 202) else "tcgen05 attention"
+        raise RuntimeError(f"an earlier {kernel} launch of an HSA forward on {device} gave up at wait site {code}; "
+                           "its output is invalid")
 
 
 def device_guard(device: torch.device):

@@ -203,7 +203,7 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
         // pooling, then scores + sort + thresholds + counts (+ the tcgen05 kernel's work order) in one launch
         int *counters = (int *)(ws + w.counters);
         if ((rc = pool_launch(&p->q, p->Lq, q_pooled, &p->k, p->Lkv, k_pooled, p->B, p->H, p->D, p->block_size, stream,
-                              counters, p->H + 1, k_first)))
+                              counters, p->H + 1, k_first, p->status_mirror)))
             return rc;
         SchedJob job{};
         if (tuned) job = hsa_sm100_sched_job(p, ws + w.tuned);

@@ -96,7 +96,8 @@ __device__ inline void convert_gate_slice(const SchedJob &job, int first, int co
 // routing (wa_routing.cu): pools x and optionally y in one launch; zeroes `n_zero` ints at `zero` on the way.
 // `y_first_block`: the first blocks of y are already pooled in py (rows [0, y_first_block) per batch and head).
 int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
-                int block_size, cudaStream_t stream, int *zero = nullptr, int n_zero = 0, int y_first_block = 0);
+                int block_size, cudaStream_t stream, int *zero = nullptr, int n_zero = 0, int y_first_block = 0,
+                int *status_mirror = nullptr);   // host-visible word that receives a non-zero code if a bounded wait of the TMA kernel runs out
 
 // routing (wa_routing.cu): scores, sort, Gini thresholds and counts in ONE launch (plus `job` when its order is set).
 // `sorted` ([rows, Nkv] float32) and `gini` ([rows]) are scratch; `counters` are H + 1 ints that are zero on entry.
@@ -127,7 +128,7 @@ int hsa_sm100_launch_linear(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc
 // block-mean pooling as a TMA stream (wa_pool_sm100.cu); y may be null; out_blocks_y = rows per (batch, head) of py
 bool pool_sm100_supported(const wa_tensor4 *x, const wa_tensor4 *y, int H, int D, int block_size);
 int pool_sm100_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int out_blocks_y, int B, int H,
-                      int D, int block_size, cudaStream_t stream, int *zero, int n_zero);
+                      int D, int block_size, cudaStream_t stream, int *zero, int n_zero, int *status_mirror);
 
 // compress_kv / KV-cache append as a TMA + tcgen05 stream (wa_compress_sm100.cu)
 bool compress_sm100_supported(const wa_tensor4 *k, const wa_tensor4 *v, const wa_tensor4 *ok, const wa_tensor4 *ov,

@@ -40,7 +40,7 @@ struct Job {
     float *px, *py;
     int *zero;
     int n_zero;
-    int *status;
+    int *status, *status_mirror;
 };
 
 __device__ int g_status;
@@ -53,7 +53,7 @@ pool_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     Barriers *bar = reinterpret_cast<Barriers *>(smem + GROUPS * STAGES * STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &bar->abort_flag;
-    const FailSink sink{job.status, nullptr};
+    const FailSink sink{job.status, job.status_mirror};
 
     if (threadIdx.x == 0) {
         bar->abort_flag = 0;
@@ -82,7 +82,7 @@ pool_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 const uint32_t g = n_item % GROUPS;
                 for (int sub = 0; sub < subs; ++sub) {
                     const uint32_t count = (n_item / GROUPS) * subs + sub, s = count % STAGES;
-                    if (!mbar_wait(&bar->empty[g][s], ((count / STAGES) & 1u) ^ 1u, abort_flag, sink, 1)) return;
+                    if (!mbar_wait(&bar->empty[g][s], ((count / STAGES) & 1u) ^ 1u, abort_flag, sink, 201)) return;   // 201, 202: wait sites of this kernel in the status word
                     mbar_expect_tx(&bar->full[g][s], (uint32_t)STAGE_BYTES);
                     // rows past the end of the tensor arrive as zeros
                     tma_load_3d(smem + (g * STAGES + s) * STAGE_BYTES, second ? &tm_y : &tm_x, &bar->full[g][s], ct * COLS,
@@ -102,17 +102,11 @@ pool_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const long long it = second ? item - items_x : item;
         const int nb_all = second ? job.nby : job.nbx, L = second ? job.Ly : job.Lx;
         const int ct = (int)(it % job.tiles), nb = (int)((it / job.tiles) % nb_all), b = (int)(it / ((long long)job.tiles * nb_all));
-#ifdef WA_POOLT_F32ACC   /* timing experiment only: inexact */
-        float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-#define WA_POOLT_CVT(x) (x)
-#else
-#define WA_POOLT_CVT(x) (double)(x)
         double lo[4] = {0.0, 0.0, 0.0, 0.0}, hi[4] = {0.0, 0.0, 0.0, 0.0};   // four chains per column: additions of one chain wait on each other
-#endif
         bool ok = true;
         for (int sub = 0; sub < subs; ++sub) {
             const uint32_t count = (n_item / GROUPS) * subs + sub, s = count % STAGES;
-            ok = mbar_wait(&bar->full[gid][s], (count / STAGES) & 1u, abort_flag, sink, 2);
+            ok = mbar_wait(&bar->full[gid][s], (count / STAGES) & 1u, abort_flag, sink, 202);
             if (!ok) break;
             const uint32_t *box = reinterpret_cast<const uint32_t *>(smem + (gid * STAGES + s) * STAGE_BYTES) + t;
 #pragma unroll
@@ -122,15 +116,15 @@ pool_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 for (int c = 0; c < 4; ++c) w[c] = box[(r + c) * (COLS / 2)];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    lo[c] += WA_POOLT_CVT(__uint_as_float(w[c] << 16));
-                    hi[c] += WA_POOLT_CVT(__uint_as_float(w[c] & 0xffff0000u));
+                    lo[c] += (double)__uint_as_float(w[c] << 16);
+                    hi[c] += (double)__uint_as_float(w[c] & 0xffff0000u);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar->empty[gid][s]);
         }
         if (!ok) break;
-        const double s0 = ((double)lo[0] + lo[1]) + ((double)lo[2] + lo[3]), s1 = ((double)hi[0] + hi[1]) + ((double)hi[2] + hi[3]);
+        const double s0 = (lo[0] + lo[1]) + (lo[2] + lo[3]), s1 = (hi[0] + hi[1]) + (hi[2] + hi[3]);
         const int n_real = min(job.block_size, L - nb * job.block_size);
         float2 out;
         if (L % job.block_size == 0) {
@@ -178,9 +172,6 @@ static bool map_rows(CUtensorMap *map, const wa_tensor4 *x, int cols, int rows, 
 
 bool pool_sm100_supported(const wa_tensor4 *x, const wa_tensor4 *y, int H, int D, int block_size) {
     using namespace sm100::pool;
-#ifdef WA_POOL_NO_TMA
-    return false;
-#endif
     for (const wa_tensor4 *t : {x, y}) {
         if (!t) continue;
         if (t->dtype != WA_BF16 || t->stride_h != D || (uintptr_t)t->ptr % 16 || t->stride_l % 8 || t->stride_b % 8 ||
@@ -196,7 +187,7 @@ bool pool_sm100_supported(const wa_tensor4 *x, const wa_tensor4 *y, int H, int D
 }
 
 int pool_sm100_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int out_blocks_y, int B, int H,
-                      int D, int block_size, cudaStream_t stream, int *zero, int n_zero) {
+                      int D, int block_size, cudaStream_t stream, int *zero, int n_zero, int *status_mirror) {
     using namespace sm100::pool;
     const char *what = "wa_pool_blocks(tma)";
     CUtensorMap tx, ty;
@@ -222,7 +213,7 @@ int pool_sm100_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *
     job.B = B; job.H = H; job.D = D; job.block_size = block_size; job.tiles = H * D / COLS;
     job.Lx = Lx; job.nbx = ceil_div(Lx, block_size);
     job.Ly = y ? Ly : 0; job.nby = y ? ceil_div(Ly, block_size) : 0; job.out_blocks_y = out_blocks_y;
-    job.px = px; job.py = py; job.zero = zero; job.n_zero = n_zero; job.status = status_of[dev];
+    job.px = px; job.py = py; job.zero = zero; job.n_zero = n_zero; job.status = status_of[dev]; job.status_mirror = status_mirror;
     const long long items = (long long)B * (job.nbx + job.nby) * job.tiles;
     WA_REQUIRE(items < (1ll << 40), WA_ERR_UNSUPPORTED, "%s: too many blocks", what);
     const int grid = items < sms ? (int)items : sms;

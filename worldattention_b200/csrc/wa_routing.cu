@@ -1137,7 +1137,7 @@ static bool pool_vec_ok(const wa_tensor4 *x, int D) {
 
 // Pools `x` (and, when given, `y`, e.g. queries and keys of one forward) in a single launch.
 int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int Ly, float *py, int B, int H, int D,
-                int block_size, cudaStream_t stream, int *zero, int n_zero, int y_first_block) {
+                int block_size, cudaStream_t stream, int *zero, int n_zero, int y_first_block, int *status_mirror) {
     const int nbx = ceil_div(Lx, block_size);
     const int nby_all = y ? ceil_div(Ly, block_size) : 0;   // rows per (batch, head) of py
     const int y_aligned = y ? Ly % block_size == 0 : 0;
@@ -1152,7 +1152,7 @@ int pool_launch(const wa_tensor4 *x, int Lx, float *px, const wa_tensor4 *y, int
     }
     const int nby = y ? ceil_div(Ly, block_size) : 0;
     if (pool_sm100_supported(x, y, H, D, block_size) && (uintptr_t)px % 8 == 0 && (!y || (uintptr_t)py % 8 == 0))
-        return pool_sm100_launch(x, Lx, px, y, Ly, py, nby_all, B, H, D, block_size, stream, zero, n_zero);
+        return pool_sm100_launch(x, Lx, px, y, Ly, py, nby_all, B, H, D, block_size, stream, zero, n_zero, status_mirror);
     View4 vx = make_view(x), vy = y ? make_view(y) : vx;
     dim3 grid(nbx + nby, H, B);
     const bool vec = pool_vec_ok(x, D) && (!y || pool_vec_ok(y, D));
