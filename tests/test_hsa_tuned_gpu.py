@@ -108,17 +108,17 @@ def test_large_logits_exercise_the_running_max_rescale(wa):
     _run_case(wa, seed=6, bsz=1, heads=2, q_len=256, kv_len=2048, seg=512, topk=[16, 9], scale=3.0)
 
 
-def test_more_than_1024_key_blocks_route_four_rows_per_cta(wa):
-    # 1032 key blocks: the routing kernel scores four query blocks per CTA in one pass over the pooled keys; 5 query
-    # blocks = one full group and a group of one.  Same order, counts and thresholds as the oracle.
+def test_thousands_of_key_blocks_route_several_rows_per_cta(wa):
+    # 2063 key blocks: the routing kernel scores four or eight query blocks per CTA in one pass over the pooled keys; 5
+    # query blocks = a full group and a ragged one.  Same order, counts and thresholds as the oracle.
     import os
     try:
-        for rows in ("4", "2", "1"):      # rows scored per CTA: the launcher's choice depends on the SM count, so pin each
+        for rows in ("8", "4", "1"):      # rows scored per CTA: the launcher's choice depends on the SM count, so pin each
             os.environ["WA_B200_ROUTE_ROWS"] = rows
-            _run_case(wa, seed=7, bsz=1, heads=2, q_len=600, kv_len=132000, seg=1320, topk=[3, 10], scale=1.0 / math.sqrt(D),
+            _run_case(wa, seed=7, bsz=1, heads=2, q_len=600, kv_len=264000, seg=1320, topk=[3, 10], scale=1.0 / math.sqrt(D),
                       whole_order=True)
         os.environ["WA_B200_ROUTE_ROWS"] = "4"
-        _run_case(wa, seed=8, bsz=2, heads=1, q_len=300, kv_len=131100, seg=1311, topk=None, scale=0.5, whole_order=True)
+        _run_case(wa, seed=8, bsz=2, heads=1, q_len=300, kv_len=262200, seg=1311, topk=None, scale=0.5, whole_order=True)
     finally:
         os.environ.pop("WA_B200_ROUTE_ROWS", None)
 
@@ -127,19 +127,19 @@ def test_fixed_counts_over_many_key_blocks_select_instead_of_sorting(wa):
     # without `return_routing` nobody reads the whole order, so the routing kernel picks each head's k best blocks by
     # radix select; the attention output must be the one the full sort gives, bit for bit (same ids, same order)
     rng = np.random.default_rng(12)
-    heads, q_len, kv_len, seg = 3, 330, 80000, 1600
+    heads, q_len, kv_len, seg = 3, 650, 160000, 1600
     q, k, v = (to_gpu(_draw(rng, (1, n, heads, D), s), "bf16") for n, s in ((q_len, 0.2), (kv_len, 0.2), (kv_len, 1.0)))
     ek = to_gpu(_proj(math.ceil(seg / 64), seg, 64, rng), "bf16")
     lin = torch.nn.Linear(D, D).to(dev())
     import os
-    for topk, rows in (([32, 1, 7], "4"), ([0, 1300, 64], "2")):        # 1300 > 1250 key blocks: every block kept
+    for topk, rows in (([32, 1, 7], "8"), ([0, 2600, 64], "4"), ([5, 9, 2], "1")):        # 2600 > 2500 key blocks: every block kept
         os.environ["WA_B200_ROUTE_ROWS"] = rows
         kw = dict(k_proj_mat=ek, v_proj_mat=ek, gate_lin=lin, block_size=64, proj_segment_len=seg,
                   topk_per_head=torch.tensor(topk, dtype=torch.int32), check_status=True)
         sorted_out, (index, num, _, used) = wa.hsa.hsa_attention(q, k, v, return_routing=True, **kw)
         picked_out = wa.hsa.hsa_attention(q, k, v, **kw)
         assert used and torch.equal(sorted_out, picked_out)
-        assert num[0, :, 0].tolist() == [min(t, 1250) for t in topk]
+        assert num[0, :, 0].tolist() == [min(t, 2500) for t in topk]
     os.environ.pop("WA_B200_ROUTE_ROWS", None)
 
 

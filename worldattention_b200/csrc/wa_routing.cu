@@ -336,92 +336,85 @@ __device__ __forceinline__ void row_block_attention(const float *__restrict__ q,
     row_softmax(Nkv, out, red, bcast);
 }
 
-// Logits of R (2 or 4) neighbouring rows of one head against one pass over the head's pooled keys (D = 128 only): with
-// thousands of key blocks a row's CTA otherwise re-reads megabytes of pooled keys that its neighbours read too, and
-// converts each to float64 again.  Same additions in the same order as `row_logits`, so the same bits.  `q` holds the
-// rows `D` apart, `out` holds them `Nkv` apart; rows >= nrows repeat row 0's query and are not stored.  The queries stay
-// in registers as float64 (re-reading them from shared memory for every pair of keys made this routine
-// shared-memory-bound: 350 us per group at 11 700 key blocks).  The keys pass through
-// `stage` (shared memory, 4 * tile_keys rows of 512 bytes) in tiles fetched with asynchronous copies, three ahead of the
-// one being computed on.
-template <int R>   // rows scored together: 2 or 4; a warp's round is 8 / R keys x R rows
-__device__ __forceinline__ void row_logits_xr(const float *__restrict__ q, int nrows, const float *__restrict__ k, int Nkv,
-                                              float scale, float *out, float4 *stage, int tile_keys) {
-    constexpr int D = 128, VPK = D / 4;   // 16-byte vectors per key
-    const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = T >> 5;
-    constexpr int KEYS = 8 / R;
-    double qd[R][4];      // this lane's four dimensions of the R rows (the kernel runs 512 threads: 128 registers each)
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const float4 qv = *reinterpret_cast<const float4 *>(q + (r < nrows ? r : 0) * D + lane * 4);
-        qd[r][0] = (double)qv.x; qd[r][1] = (double)qv.y; qd[r][2] = (double)qv.z; qd[r][3] = (double)qv.w;
-    }
+// Logits of R neighbouring rows of one head against ONE pass over the head's pooled keys (D = 128 only): with thousands
+// of key blocks a row's CTA otherwise re-reads megabytes of pooled keys that its neighbours read too and converts each to
+// float64 again.  A lane owns a key: the keys are staged through `stage` (shared memory, 2 tiles of `tile_keys` rows)
+// TRANSPOSED in 16-byte pieces ([piece][key] with an odd pitch, filled one tile ahead through registers: coalesced reads,
+// conflict-free writes), so that a warp reads the same piece of 32 keys without bank conflicts, converts it once and uses
+// it for all R rows, whose float64 queries come from
+// shared memory as broadcasts.  No sum crosses a lane; a dot is accumulated dimension by dimension in float64 and rounded
+// once, like every other sum on the routing path.  Measured at 11 700 key blocks (one group = its rows x 11 700 keys):
+// see the numbers in the design notes.  Other forms that were built and measured: each key split over all 32 lanes with the queries
+// in registers (no transposition, but most instructions go into the transposed float64 reduction: 284 us for four rows);
+// a key per 4 lanes with a quarter of the dimensions each, so that all 16 warps compute (the query reads are then four
+// different addresses per load instead of one broadcast: 220 us + 56 us per row).  `q` holds the
+// rows 128 apart, `out` holds them `Nkv` apart; rows >= nrows repeat row 0's query and are not stored.
+template <int R>
+__device__ __forceinline__ void row_logits_keys(const float *__restrict__ q, int nrows, const float *__restrict__ k, int Nkv,
+                                                float scale, float *out, double *qsh, float4 *stage, int tile_keys) {
+    constexpr int D = 128, VPK = D / 4;   // 16-byte pieces per key
+    const int T = blockDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < R * D; i += T) qsh[i] = (double)q[((i / D) < nrows ? (i / D) : 0) * D + (i % D)];
     const float4 *kvec = reinterpret_cast<const float4 *>(k);
-    const int tile_vecs = tile_keys * VPK;
-    const long long total_vecs = (long long)Nkv * VPK;
+    const int pitch = tile_keys + 1;                  // 16-byte slots per piece row: the odd pitch spreads a key's 32 pieces over the banks
+    const int tile_vecs = tile_keys * VPK, tile_slots = pitch * VPK;
     const int n_tiles = (Nkv + tile_keys - 1) / tile_keys;
-    // asynchronous 16-byte copies straight into shared memory (no registers held while they fly); vectors past the end
-    // of the keys are written as zeros (source size 0).  STAGES - 1 tiles are in flight while one is computed on: with a
-    // single tile in flight the routine ran at one tile per L2 round trip (21 GB/s per SM).
-    constexpr int STAGES = 4;
+    // a warp loads one key's 512 bytes per instruction (coalesced) into registers while the previous tile is computed on,
+    // and stores them transposed afterwards (16-byte asynchronous copies were measured at about 16 bytes per clock per SM,
+    // which made the staging, not the arithmetic, the larger part of this routine)
+    constexpr int PER_THREAD = 8;      // 16-byte loads per thread and tile: tile_keys * 32 <= 8 * 512
+    float4 pre[PER_THREAD];
     auto fetch = [&](int tile) {
-        if (tile < n_tiles) {
-            float4 *dst = stage + (tile % STAGES) * tile_vecs;
-            for (int v = threadIdx.x; v < tile_vecs; v += T) {
-                const long long g = (long long)tile * tile_vecs + v;
-                const bool real = g < total_vecs;
-                const unsigned saddr = (unsigned)__cvta_generic_to_shared(dst + v);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(kvec + (real ? g : 0)), "r"(real ? 16 : 0)
-                             : "memory");
-            }
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int v = i * T + threadIdx.x, key = v / VPK, piece = v % VPK;
+            const long long gkey = (long long)tile * tile_keys + key;
+            pre[i] = (v < tile_vecs && gkey < Nkv) ? __ldg(kvec + gkey * VPK + piece) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");      // an empty group past the end keeps the count uniform
     };
+    auto park = [&](int tile) {
+        float4 *dst = stage + (tile & 1) * tile_slots;
 #pragma unroll
-    for (int t0 = 0; t0 < STAGES - 1; ++t0) fetch(t0);
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int v = i * T + threadIdx.x, key = v / VPK, piece = v % VPK;
+            if (v < tile_vecs) dst[piece * pitch + key] = pre[i];
+        }
+    };
+    fetch(0);
+    park(0);
+    __syncthreads();
     for (int tile = 0; tile < n_tiles; ++tile) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");      // this thread's copies of `tile` have landed
-        __syncthreads();      // everyone's have, and everyone is done with tile - 1, whose buffer the next fetch overwrites
-        fetch(tile + STAGES - 1);
-        const float4 *kt = stage + (tile % STAGES) * tile_vecs;
-        const int base = tile * tile_keys;
-        for (int j = warp * KEYS; j < tile_keys && base + j < Nkv; j += nwarps * KEYS) {      // KEYS keys x R rows per warp and round
-            double acc[8];     // acc[r * KEYS + u]
+        if (tile + 1 < n_tiles) fetch(tile + 1);
+        const int key = warp * 32 + lane;      // a lane owns a key of the tile: the first tile_keys / 32 warps compute, all warps fetch
+        const long long gkey = (long long)tile * tile_keys + key;
+        if (key < tile_keys && (long long)tile * tile_keys + warp * 32 < Nkv) {
+            const float4 *kt = stage + (tile & 1) * tile_slots + key;
+            double acc[R];
 #pragma unroll
-            for (int u = 0; u < KEYS; ++u) {
-                const float4 kv = kt[(j + u) * VPK + lane];    // a key past the end of the tile's real keys is zeros
+            for (int r = 0; r < R; ++r) acc[r] = 0.0;
+#pragma unroll 4
+            for (int piece = 0; piece < VPK; ++piece) {
+                const float4 kv = kt[piece * pitch];
                 const double k0 = (double)kv.x, k1 = (double)kv.y, k2 = (double)kv.z, k3 = (double)kv.w;
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    double a = fma(qd[r][0], k0, 0.0);
-                    a = fma(qd[r][1], k1, a);
-                    a = fma(qd[r][2], k2, a);
-                    a = fma(qd[r][3], k3, a);
-                    acc[r * KEYS + u] = a;
+                    const double2 qa = *reinterpret_cast<const double2 *>(qsh + r * D + piece * 4);      // broadcast reads
+                    const double2 qb = *reinterpret_cast<const double2 *>(qsh + r * D + piece * 4 + 2);
+                    double a = fma(qa.x, k0, acc[r]);
+                    a = fma(qa.y, k1, a);
+                    a = fma(qb.x, k2, a);
+                    acc[r] = fma(qb.y, k3, a);
                 }
             }
-            // transposed reduction, as in row_logits: lane l ends with sum (l >> 2) & 7
-            const bool b16 = lane & 16, b8 = lane & 8, b4 = lane & 4;
-            double r4[4], r2[2];
+            if (gkey < Nkv) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const double keep = b16 ? acc[i + 4] : acc[i], give = b16 ? acc[i] : acc[i + 4];
-                r4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+                for (int r = 0; r < R; ++r)
+                    if (r < nrows) out[(long long)r * Nkv + gkey] = __fmul_rn((float)acc[r], scale);
             }
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const double keep = b8 ? r4[i + 2] : r4[i], give = b8 ? r4[i] : r4[i + 2];
-                r2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
-            }
-            double t = (b4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, b4 ? r2[0] : r2[1], 4);
-            t += __shfl_xor_sync(0xffffffffu, t, 2);
-            t += __shfl_xor_sync(0xffffffffu, t, 1);
-            const int which = (lane >> 2) & 7, r = which / KEYS, u = which % KEYS;
-            if ((lane & 3) == 0 && r < nrows && base + j + u < Nkv) out[(long long)r * Nkv + base + j + u] = __fmul_rn((float)t, scale);
         }
+        if (tile + 1 < n_tiles) park(tile + 1);      // that buffer was last read while tile - 1 was computed, before the last barrier
+        __syncthreads();      // (after the last tile: the logits are complete and visible to the whole CTA, the staging memory is free)
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();      // the logits are complete (and visible to the whole CTA) and the staging memory is free
 }
 
 __global__ void __launch_bounds__(SCORE_THREADS)
@@ -588,11 +581,12 @@ __device__ __forceinline__ void sort_keys_smem(unsigned long long *keys, int n_p
 // The k best blocks of a row, in order, WITHOUT sorting the row: for a fixed per-head count over thousands of key blocks
 // the full bitonic sort (105 passes over 16384 keys) was two thirds of the routing kernel.  Keys are the sort's own
 // 64-bit keys (descending probability, then ascending id; all distinct).  A most-significant-byte-first radix select
-// finds the k-th smallest key (at most eight histogram passes over the row, usually three or four: it stops as soon as
-// one histogram bin holds exactly the keys still needed), the k keys at or below it are collected and only they are
-// sorted.  `idx[0..k)` receive the same ids in the same order as the full sort; slots past k are not written.
-// `keys` is shared memory for >= max(1024, pow2(k)) entries.  Called by every thread of the CTA (>= 256 threads).
-__device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, int k, unsigned long long *keys, int32_t *idx) {
+// narrows down the k-th smallest key (histogram passes over the row: it stops as soon as one histogram bin holds exactly the
+// keys still needed, or the keys at or below the bin are at most 1024), the keys at or below it are collected and only
+// they are sorted.  `idx[0..k)` receive the same ids in the same order as the full sort; slots past k are not written.
+// `keys` is shared memory for `key_slots` >= max(1024, pow2(k)) entries.  Called by every thread of the CTA (>= 256 threads).
+__device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, int k, unsigned long long *keys, int key_slots,
+                                                  int32_t *idx) {
     __shared__ unsigned int hist[256];
     __shared__ unsigned long long prefix_s, mask_s;
     __shared__ int need_s, done_s;
@@ -600,16 +594,51 @@ __device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, i
     const int T = blockDim.x, tid = threadIdx.x;
     if (k <= 0) return;
     auto key_of = [&](int j) { return ((unsigned long long)descending_key(probs[j]) << 32) | (unsigned)j; };
+    // the keys of a row usually agree in their leading bytes (probabilities of one softmax share sign and most of the
+    // exponent; near-uniform attention agrees much further): find the common prefix with one min/max pass and start the
+    // digit passes below it
+    __shared__ unsigned long long lo_s[32], hi_s[32];
+    unsigned long long lo = 0xFFFFFFFFFFFFFFFFull, hi = 0ull;
+    for (int j = tid; j < Nkv; j += T) {
+        const unsigned long long key = key_of(j);
+        lo = key < lo ? key : lo;
+        hi = key > hi ? key : hi;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long l2 = __shfl_xor_sync(0xffffffffu, lo, o), h2 = __shfl_xor_sync(0xffffffffu, hi, o);
+        lo = l2 < lo ? l2 : lo;
+        hi = h2 > hi ? h2 : hi;
+    }
+    if ((tid & 31) == 0) {
+        lo_s[tid >> 5] = lo;
+        hi_s[tid >> 5] = hi;
+    }
+    __syncthreads();
+    int first_byte = 7;
     if (tid == 0) {
-        prefix_s = 0ull;
-        mask_s = 0ull;
+        for (int w = 1; w < (T >> 5); ++w) {
+            lo = lo_s[w] < lo ? lo_s[w] : lo;
+            hi = hi_s[w] > hi ? hi_s[w] : hi;
+        }
+        const unsigned long long diff = lo ^ hi;
+        const int top = diff ? (63 - __clzll((long long)diff)) >> 3 : 0;      // highest byte in which two keys differ
+        const unsigned long long mask = top >= 7 ? 0ull : (0xFFFFFFFFFFFFFFFFull << (8 * (top + 1)));
+        prefix_s = lo & mask;
+        mask_s = mask;
         need_s = k;
         done_s = k >= Nkv;     // every block is kept: nothing to select
         taken_s = 0u;
+        lo_s[0] = (unsigned long long)top;
     }
     __syncthreads();
-    for (int byte = 7; byte >= 0 && !done_s; --byte) {
-        if (tid < 256) hist[tid] = 0u;
+    first_byte = (int)lo_s[0];
+    // a histogram per warp (in the keys' memory, idle until the collection below): the probabilities of a row share their
+    // leading bits, so in the first passes every warp adds to the same bin, and one shared bin serialised them
+    unsigned int *warp_hist = reinterpret_cast<unsigned int *>(keys);
+    const int copies = min(T >> 5, key_slots / 128), wid = (tid >> 5) % copies;      // 256 counters of 4 bytes per copy
+    for (int byte = first_byte; byte >= 0 && !done_s; --byte) {
+        for (int i = tid; i < copies * 256; i += T) warp_hist[i] = 0u;
         __syncthreads();
         const unsigned long long prefix = prefix_s, mask = mask_s;
         for (int j0 = 0; j0 < Nkv; j0 += T) {      // whole warps iterate together: the votes below need every lane
@@ -617,13 +646,22 @@ __device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, i
             const unsigned long long key = j < Nkv ? key_of(j) : 0ull;
             const bool cand = j < Nkv && (key & mask) == prefix;
             const unsigned int voters = __ballot_sync(0xffffffffu, cand);
-            if (cand) {
-                // probabilities of one row share their leading bits, so most keys of a pass fall into one bin: one
-                // atomic per distinct digit of the warp instead of one per key
+            if (voters) {
+                // the probabilities of a row share their leading bits: the digit of the warp's first candidate is usually
+                // the digit of most of them; those are counted with one addition, the others add for themselves
                 const unsigned int digit = (unsigned)(key >> (8 * byte)) & 255u;
-                const unsigned int peers = __match_any_sync(voters, digit);
-                if ((tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[digit], (unsigned)__popc(peers));
+                const int leader = __ffs(voters) - 1;
+                const unsigned int common = __shfl_sync(0xffffffffu, digit, leader);
+                const unsigned int same = __ballot_sync(0xffffffffu, cand && digit == common);
+                if ((tid & 31) == leader) atomicAdd(&warp_hist[wid * 256 + common], (unsigned)__popc(same));
+                else if (cand && digit != common) atomicAdd(&warp_hist[wid * 256 + digit], 1u);
             }
+        }
+        __syncthreads();
+        if (tid < 256) {
+            unsigned int total = 0;
+            for (int w = 0; w < copies; ++w) total += warp_hist[w * 256 + tid];
+            hist[tid] = total;
         }
         __syncthreads();
         if (tid < 32) {      // first digit at which the running count reaches what is still needed
@@ -657,11 +695,14 @@ __device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, i
                 prefix_s = prefix | ((unsigned long long)(tid * 8 + d) << (8 * byte));
                 mask_s = mask | (0xFFull << (8 * byte));
                 need_s = (int)(need - run);
-                if (in_bin == need - run) done_s = 1;      // the whole bin is wanted: no finer digit needed
+                // stop refining when the whole bin is wanted, or when the keys at or below this bin are few enough to sort
+                // directly (every further digit would cost another pass over the whole row)
+                if (in_bin == need - run || (unsigned)k - (need - run) + in_bin <= 1024u) done_s = 1;
             }
         }
         __syncthreads();
     }
+    ROUTE_STAMP(11);
     // collect the keys at or below the k-th (with all keys kept when k >= Nkv: mask 0, prefix 0), then sort just those
     const unsigned long long prefix = prefix_s, mask = mask_s;
     for (int j = tid; j < Nkv; j += T) {
@@ -669,13 +710,13 @@ __device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, i
         if ((key & mask) <= prefix) keys[atomicAdd(&taken_s, 1u)] = key;
     }
     __syncthreads();
-    const int kept = (int)taken_s;      // == min(k, Nkv)
+    const int kept = (int)taken_s;      // >= min(k, Nkv): the k best and, when the selection stopped early, the rest of the last bin
     int k_pow2 = 1;
     while (k_pow2 < kept) k_pow2 <<= 1;
     for (int j = kept + tid; j < k_pow2; j += T) keys[j] = 0xFFFFFFFFFFFFFFFFull;
     __syncthreads();
     sort_keys_smem(keys, k_pow2);
-    for (int m = tid; m < kept; m += T) idx[m] = (int32_t)(keys[m] & 0xFFFFFFFFull);
+    for (int m = tid; m < min(k, kept); m += T) idx[m] = (int32_t)(keys[m] & 0xFFFFFFFFull);
     __syncthreads();
 }
 
@@ -704,7 +745,7 @@ __device__ __forceinline__ void route_row(const long long row, const bool logits
 
     if (select_only) {
         // fixed per-head count and nobody asked for the whole order or the thresholds: pick the head's k best blocks
-        select_top_blocks(probs, Nkv, max(0, min(fixed_num[h], Nkv)), keys, index + row * Nkv);
+        select_top_blocks(probs, Nkv, max(0, min(fixed_num[h], Nkv)), keys, max(n_pow2, T), index + row * Nkv);
     } else if (n_pow2 <= T) {
         // one key per thread in a register: exchange distances below 32 go through shuffles, the rest through smem
         unsigned long long key = tid < Nkv ? (((unsigned long long)descending_key(probs[tid]) << 32) | (unsigned)tid)
@@ -907,7 +948,7 @@ __device__ __forceinline__ void route_row(const long long row, const bool logits
 // The forward's routing in ONE launch.  Each CTA owns one row, or (thousands of key blocks, head_dim 128) four
 // neighbouring rows of a head whose logits it computes in one pass over the pooled keys.
 // ------------------------------------------------------------------------------------------------
-template <int ROWS>   // rows per CTA: 1, 2 or 4 (several rows: at most 512 threads, for the registers of row_logits_xr)
+template <int ROWS>   // rows per CTA: 1, 4 or 8 (several rows: 512 threads)
 __global__ void __launch_bounds__(ROWS > 1 ? 512 : 1024)
 route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, int B, int H, int Nq, int Nkv, int n_pow2,
                    int D, float scale, float tau_min, float tau_span, const int32_t *__restrict__ fixed_num,
@@ -919,6 +960,7 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
     unsigned long long *keys = reinterpret_cast<unsigned long long *>(fused_smem);   // max(n_pow2, threads)
     float *probs = reinterpret_cast<float *>(keys + max(n_pow2, (int)blockDim.x));    // Nkv
     __shared__ double red[256];
+    __shared__ __align__(16) double q_rows[ROWS > 1 ? ROWS * 128 : 2];
     __shared__ float bcast;
     __shared__ int last_flag;
 
@@ -938,10 +980,13 @@ route_fused_kernel(const float *__restrict__ qp, const float *__restrict__ kp, i
 
     if constexpr (ROWS > 1) {
         // the sort keys' shared memory is free until the first row is sorted: the pooled keys are staged through it
-        const int key_bytes = max(n_pow2, (int)blockDim.x) * 8;
-        const int tile_keys = min(key_bytes / 4 / 512, 64) & ~7;   // four staging buffers (row_logits_xr)
-        row_logits_xr<ROWS>(qp + row0 * D, nrows, kp + bh * (long long)Nkv * D, Nkv, scale, sorted + row0 * Nkv,
-                      reinterpret_cast<float4 *>(keys), tile_keys);   // ends with a barrier: the rows below read these logits back
+        // (and through the head of the probabilities' memory behind it, which is not in use yet either)
+        const int stage_bytes = max(n_pow2, (int)blockDim.x) * 8 + Nkv * 4;
+        int tile_keys = 128;      // two staging buffers of (tile_keys + 1) x 512 bytes; whole warps of keys
+        while (tile_keys > 32 && 2 * (tile_keys + 1) * 512 > stage_bytes) tile_keys -= 32;
+        row_logits_keys<ROWS>(qp + row0 * D, nrows, kp + bh * (long long)Nkv * D, Nkv, scale, sorted + row0 * Nkv, q_rows,
+                              reinterpret_cast<float4 *>(keys), tile_keys);      // ends with a barrier: the rows below read these logits back
+        ROUTE_STAMP(10);
     }
     if constexpr (ROWS == 1) {
         route_row(row0, false, qp, kp, B, H, Nq, Nkv, n_pow2, D, scale, tau_min, tau_span, fixed_num, sorted, index, num, thresholds,
@@ -1249,26 +1294,26 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
     const size_t smem = (size_t)(n_pow2 > threads ? n_pow2 : threads) * sizeof(unsigned long long) + (size_t)Nkv * sizeof(float);
     if (smem > 24 * 1024) {   // static shared memory of the kernel takes ~19 KB of the default 48 KB
         cudaError_t e = cudaFuncSetAttribute(route_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(route_fused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(route_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(route_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(routing): %s", cudaGetErrorString(e));
     }
-    // several rows per CTA where a row's keys are megabytes (see row_logits_xr); one row per CTA where the kernel is latency.
-    // Four rows share more key conversions than two, but the CTAs come in waves of one per SM (their shared memory fills
-    // it): take the count with fewer row-times on the busiest SM, four on a tie.
+    // several rows per CTA where a row's keys are megabytes (see row_logits_keys); one row per CTA where the kernel is latency.
+    // Eight rows share more key reads and conversions than four, but the CTAs come in waves of one per SM (their shared memory fills
+    // it): take the count with fewer row-times on the busiest SM, eight on a tie.
     int dev = 0, sm_count = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
         sm_count = 148;
     int rows_per_cta = 1;
-    if (Nkv > 1024 && D == 128 && ((uintptr_t)q_pooled % 16 == 0) && ((uintptr_t)k_pooled % 16 == 0)) {
+    if (Nkv > 2048 && D == 128 && ((uintptr_t)q_pooled % 16 == 0) && ((uintptr_t)k_pooled % 16 == 0)) {
         auto row_times = [&](int r) {
             const long long g = (long long)B * H * ((Nq + r - 1) / r);
             return ((g + sm_count - 1) / sm_count) * r;
         };
-        rows_per_cta = row_times(2) < row_times(4) ? 2 : 4;
+        rows_per_cta = row_times(4) < row_times(8) ? 4 : 8;
         if (const char *e = getenv("WA_B200_ROUTE_ROWS"))      // tuning aid
-            if (e[0] == '1' || e[0] == '2' || e[0] == '4') rows_per_cta = e[0] - '0';
+            if (e[0] == '1' || e[0] == '4' || e[0] == '8') rows_per_cta = e[0] - '0';
     }
     const int groups_per_bh = (Nq + rows_per_cta - 1) / rows_per_cta;
     const long long groups = (long long)B * H * groups_per_bh;
@@ -1288,8 +1333,8 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
                                 (float)tau_min, span, fixed_num_per_head, sorted, index, num, thresholds, gini, counters, job,
                                 gate_per_cta, sm_count, slots, groups_per_bh, select_only);
     };
-    cudaError_t le = rows_per_cta == 4 ? launch(route_fused_kernel<4>)
-                                       : (rows_per_cta == 2 ? launch(route_fused_kernel<2>) : launch(route_fused_kernel<1>));
+    cudaError_t le = rows_per_cta == 8 ? launch(route_fused_kernel<8>)
+                                       : (rows_per_cta == 4 ? launch(route_fused_kernel<4>) : launch(route_fused_kernel<1>));
     if (le != cudaSuccess) return fail((int)le, "wa_hsa_forward(routing): %s", cudaGetErrorString(le));
     return check_launch("wa_hsa_forward(routing)");
 }
