@@ -347,7 +347,9 @@ __device__ __forceinline__ void row_block_attention(const float *__restrict__ q,
 // see the numbers in the design notes.  Other forms that were built and measured: each key split over all 32 lanes with the queries
 // in registers (no transposition, but most instructions go into the transposed float64 reduction: 284 us for four rows);
 // a key per 4 lanes with a quarter of the dimensions each, so that all 16 warps compute (the query reads are then four
-// different addresses per load instead of one broadcast: 220 us + 56 us per row).  `q` holds the
+// different addresses per load instead of one broadcast: 220 us + 56 us per row); the rows spread over four warp groups
+// so that all 16 warps compute whole keys (each key converted four times: 25-40 us slower).  What is left of the fixed
+// part is the keys' way from L2: every group streams its head's 6 MB, 720 MB for the 120 groups of config 5.  `q` holds the
 // rows 128 apart, `out` holds them `Nkv` apart; rows >= nrows repeat row 0's query and are not stored.
 template <int R>
 __device__ __forceinline__ void row_logits_keys(const float *__restrict__ q, int nrows, const float *__restrict__ k, int Nkv,
