@@ -1301,19 +1301,22 @@ int route_fused_launch(const float *q_pooled, const float *k_pooled, int B, int 
         if (e != cudaSuccess) return fail((int)e, "wa_hsa_forward(routing): %s", cudaGetErrorString(e));
     }
     // several rows per CTA where a row's keys are megabytes (see row_logits_keys); one row per CTA where the kernel is latency.
-    // Eight rows share more key reads and conversions than four, but the CTAs come in waves of one per SM (their shared memory fills
-    // it): take the count with fewer row-times on the busiest SM, eight on a tie.
+    // More rows per CTA share more key reads and conversions, but the CTAs come in waves of one per SM (their shared memory
+    // fills it) and a CTA's rows are softmaxed and selected one after the other: take the count with the lowest estimate.
     int dev = 0, sm_count = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
         sm_count = 148;
     int rows_per_cta = 1;
     if (Nkv > 2048 && D == 128 && ((uintptr_t)q_pooled % 16 == 0) && ((uintptr_t)k_pooled % 16 == 0)) {
-        auto row_times = [&](int r) {
+        // measured at 11 700 key blocks (microseconds; everything scales with the block count, so the comparison holds):
+        // scoring one row per CTA 115, R rows per CTA 190 + 29 R, and 21 per row for softmax and selection
+        auto cost = [&](int r) {
             const long long g = (long long)B * H * ((Nq + r - 1) / r);
-            return ((g + sm_count - 1) / sm_count) * r;
+            return ((g + sm_count - 1) / sm_count) * (r == 1 ? 115 + 21 : 190 + (29 + 21) * r);
         };
-        rows_per_cta = row_times(4) < row_times(8) ? 4 : 8;
+        rows_per_cta = cost(4) < cost(8) ? 4 : 8;
+        if (cost(1) < cost(rows_per_cta)) rows_per_cta = 1;
         if (const char *e = getenv("WA_B200_ROUTE_ROWS"))      // tuning aid
             if (e[0] == '1' || e[0] == '4' || e[0] == '8') rows_per_cta = e[0] - '0';
     }
