@@ -111,3 +111,23 @@ def test_kv_shard_pipeline_emulated_on_one_gpu(routing, world):
     assert torch.equal(chosen[..., :nkv], want_sel[..., :nkv])
     diff = (got.float() - want.float()).abs()
     assert float(diff.max()) < 2e-2 and float(diff.mean() / want.float().abs().mean()) < 1e-2
+
+
+def test_local_candidates_of_a_long_shard_are_the_best_blocks_in_order():
+    """Thousands of local key blocks: the candidate kernel selects instead of sorting; the candidates must still be the
+    `topk_max` highest logits of the row, best first, as (descending logit, ascending global id) keys."""
+    from worldattention_b200 import sharded
+    rng = np.random.default_rng(21)
+    heads, nq, d, block_lo, kcap = 2, 3, 128, 5000, 32
+    for nloc in (3000, 700):                                    # radix selection; full sort
+        q = rng.standard_normal((1, heads, nq, d)).astype(np.float32)
+        k = rng.standard_normal((1, heads, nloc, d)).astype(np.float32)
+        cand = sharded.local_candidates(torch.from_numpy(q).to(dev()), torch.from_numpy(k).to(dev()), block_lo=block_lo,
+                                        topk_max=kcap).cpu().numpy().view(np.uint64).reshape(heads, nq, kcap)
+        logits = np.einsum("hqd,hkd->hqk", q[0].astype(np.float64), k[0].astype(np.float64))
+        for h in range(heads):
+            for i in range(nq):
+                keys = cand[h, i]
+                assert np.all(keys[:-1] < keys[1:])                                        # ascending keys = best first
+                ids = (keys & np.uint64(0xFFFFFFFF)).astype(np.int64) - block_lo
+                assert np.array_equal(ids, np.argsort(-logits[h, i], kind="stable")[:kcap])

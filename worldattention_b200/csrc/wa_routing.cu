@@ -588,14 +588,14 @@ __device__ __forceinline__ void sort_keys_smem(unsigned long long *keys, int n_p
 // they are sorted.  `idx[0..k)` receive the same ids in the same order as the full sort; slots past k are not written.
 // `keys` is shared memory for `key_slots` >= max(1024, pow2(k)) entries.  Called by every thread of the CTA (>= 256 threads).
 __device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, int k, unsigned long long *keys, int key_slots,
-                                                  int32_t *idx) {
+                                                  int32_t *idx, int id_offset = 0, unsigned long long *keys_out = nullptr) {
     __shared__ unsigned int hist[256];
     __shared__ unsigned long long prefix_s, mask_s;
     __shared__ int need_s, done_s;
     __shared__ unsigned int taken_s;
     const int T = blockDim.x, tid = threadIdx.x;
     if (k <= 0) return;
-    auto key_of = [&](int j) { return ((unsigned long long)descending_key(probs[j]) << 32) | (unsigned)j; };
+    auto key_of = [&](int j) { return ((unsigned long long)descending_key(probs[j]) << 32) | (unsigned)(id_offset + j); };
     // the keys of a row usually agree in their leading bytes (probabilities of one softmax share sign and most of the
     // exponent; near-uniform attention agrees much further): find the common prefix with one min/max pass and start the
     // digit passes below it
@@ -718,7 +718,10 @@ __device__ __forceinline__ void select_top_blocks(const float *probs, int Nkv, i
     for (int j = kept + tid; j < k_pow2; j += T) keys[j] = 0xFFFFFFFFFFFFFFFFull;
     __syncthreads();
     sort_keys_smem(keys, k_pow2);
-    for (int m = tid; m < min(k, kept); m += T) idx[m] = (int32_t)(keys[m] & 0xFFFFFFFFull);
+    for (int m = tid; m < min(k, kept); m += T) {
+        if (idx) idx[m] = (int32_t)(keys[m] & 0xFFFFFFFFull);
+        if (keys_out) keys_out[m] = keys[m];      // the sortable keys themselves (ids offset by `id_offset`)
+    }
     __syncthreads();
 }
 
@@ -1052,6 +1055,13 @@ route_local_candidates_kernel(const float *__restrict__ qp, const float *__restr
     const long long bh = row / Nq;
     row_logits(qp + row * D, kp + bh * (long long)Nloc * D, Nloc, D, scale, logits);
     __syncthreads();
+    if (n_pow2 > (int)blockDim.x && kcap <= 1024) {
+        // a long row: pick the kcap best instead of sorting all of them (same keys, same order)
+        const int k = min(kcap, Nloc);
+        select_top_blocks(logits, Nloc, k, keys, n_pow2, nullptr, block_lo, cand + row * kcap);
+        for (int j = k + threadIdx.x; j < kcap; j += blockDim.x) cand[row * kcap + j] = 0xFFFFFFFFFFFFFFFFull;
+        return;
+    }
     for (int j = threadIdx.x; j < n_pow2; j += blockDim.x)
         keys[j] = j < Nloc ? (((unsigned long long)descending_key(logits[j]) << 32) | (unsigned)(block_lo + j))
                            : 0xFFFFFFFFFFFFFFFFull;
