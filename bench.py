@@ -786,7 +786,7 @@ def bench_config4(dev, chunks):
     except torch.OutOfMemoryError as exc:      # reported, not hidden: the harness needs about 12 GB
         return {"error": f"out of memory: {exc}"}
     res["workload"] = ("c4: 30-block DiT (dim 1536, 12 heads, FFN 8960), 1560 tokens/frame, 3-frame chunks, 4+1 forwards per chunk, "
-                       f"{chunks} chunks (the benchmark names 80), HSA window 21 frames, HKV switch every 8 chunks")
+                       f"{chunks} chunks (80 in the benchmark definition), HSA window 21 frames, HKV switch every 8 chunks")
     res["unit"] = "latent frames/s"
     return res
 
@@ -921,8 +921,8 @@ def main():
     ap.add_argument("--force-generic", action="store_true")
     ap.add_argument("--no-hkv", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip block64 / long_horizon / compress / triton_incumbent")
-    ap.add_argument("--c4-chunks", type=int, default=24,
-                    help="chunks generated by the end-to-end harness (benchmark config 4 asks for 80; 0 skips it)")
+    ap.add_argument("--c4-chunks", type=int, default=80,
+                    help="chunks generated by the end-to-end harness (80 = benchmark config 4; 0 skips it)")
     ap.add_argument("--hkv-only", action="store_true", help="run only the HKV retrieval measurements (one GPU)")
     ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the hot HKV measurement (30 = benchmark config 3)")
     ap.add_argument("--hkv-cold-layers", type=int, default=2, help="layers in the cold-tier HKV measurement")

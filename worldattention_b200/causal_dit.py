@@ -520,12 +520,13 @@ def time_generation(cfg: DiTConfig, *, chunks: int, switch_every_chunks: int = 0
     switches = [c * cfg.frames_per_chunk for c in range(switch_every_chunks, chunks, switch_every_chunks)] if switch_every_chunks else []
     gp = torch.Generator(device="cpu").manual_seed(seed + 1)
     prompts = [torch.randn((cfg.text_len, cfg.text_dim), generator=gp) for _ in range(len(switches) + 1)]
-    # untimed: two chunks and, with a bank, one store, so that library initialisation and the first growth of the
-    # allocator's pools are not counted as generation time
-    pipe.generate(noise[:, :2 * cfg.frames_per_chunk], prompts[:1], generator=g)
+    # untimed: three chunks, with a bank one prompt switch among them (store, retrieve, install), so that library
+    # initialisation and first-call set-up are not counted as generation time
+    fpc = cfg.frames_per_chunk
     if hkv is not None:
-        hkv.store(pipe.kv_cache, prompt_embeds=prompts[0].to(dev, torch.bfloat16).unsqueeze(0), current_start_frame=2 * cfg.frames_per_chunk,
-                  temporal_freqs=temporal_band(model.freqs, cfg.head_dim).to(dev))
+        pipe.generate(noise[:, :3 * fpc], [prompts[0], prompts[0]], [2 * fpc], generator=g)
+    else:
+        pipe.generate(noise[:, :2 * fpc], prompts[:1], generator=g)
     pipe.reset()
     pipe.stats = _Stats()
     torch.cuda.synchronize(dev)
