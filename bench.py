@@ -771,13 +771,13 @@ def bench_config4(dev, chunks):
     1536, 12 heads, FFN 8960, bf16), 480 x 832 latents, chunks of 3 latent frames, 4 denoising forwards + 1 clean-context
     forward per chunk, HSA over a rolling 21-frame window (128-token blocks, per-head block counts drawn from
     {4, 8, 16, 32} as in config 2), synthetic 512 x 4096 prompt embeddings, and a prompt switch served from the HKV bank
-    every 8 chunks (pages of 3 frames, top-4 pages, the four most recent banked windows kept in HBM, older ones in pinned host memory).  Text encoder and VAE are outside the timed region; frames are
+    every 8 chunks (pages of 3 frames, top-4 pages, up to twelve banked windows (6 GB each) kept in HBM, older ones in pinned host memory).  Text encoder and VAE are outside the timed region; frames are
     latent frames.  Everything around the attention layer is plain torch (cuBLAS GEMMs, library cross-attention)."""
     from worldattention_b200.causal_dit import DiTConfig, time_generation
     rng = np.random.default_rng(1)
     cfg = DiTConfig(hsa_topk=[int(v) for v in rng.choice([4, 8, 16, 32], size=12)])
     kwargs = dict(chunks=chunks, switch_every_chunks=8, device=dev,
-                  hkv_kwargs=dict(page_size_frames=3, topk_pages=4, cpu_max_chunks=64, hbm_max_chunks=4))
+                  hkv_kwargs=dict(page_size_frames=3, topk_pages=4, cpu_max_chunks=64, hbm_max_chunks=12))
     try:
         res = time_generation(cfg, cuda_graph=True, **kwargs)      # steady-state chunks replayed from one captured graph
         torch.cuda.empty_cache()
