@@ -123,17 +123,20 @@ def all_gather_cat(t: torch.Tensor, dim: int, group=None, sizes: Optional[Sequen
         return t
     t = t.contiguous()
     if sizes is None:
-        parts = [torch.empty_like(t) for _ in range(world)]
-        dist.all_gather(parts, t, group=group)
-        return torch.cat(parts, dim=dim)
+        flat = torch.empty(world * t.numel(), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(flat, t.view(-1), group=group)
+        return torch.cat(list(flat.view([world] + list(t.shape)).unbind(0)), dim=dim)
     longest = max(sizes)
     pad_shape = list(t.shape)
     pad_shape[dim] = longest
     padded = torch.zeros(pad_shape, dtype=t.dtype, device=t.device)
     padded.narrow(dim, 0, t.shape[dim]).copy_(t)
-    parts = [torch.empty_like(padded) for _ in range(world)]
-    dist.all_gather(parts, padded, group=group)
-    return torch.cat([p.narrow(dim, 0, n) for p, n in zip(parts, sizes)], dim=dim)
+    flat = torch.empty(world * padded.numel(), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(flat, padded.view(-1), group=group)      # one collective on one buffer (the list form copies per rank)
+    every = flat.view([world] + pad_shape)
+    if all(n == longest for n in sizes):
+        return torch.cat(list(every.unbind(0)), dim=dim)
+    return torch.cat([every[r].narrow(dim, 0, n) for r, n in enumerate(sizes)], dim=dim)
 
 
 def gather_heads(out_local: torch.Tensor, head_plan: List[List[int]], group=None) -> torch.Tensor:
