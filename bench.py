@@ -1110,8 +1110,8 @@ def main():
                                            block_size=block, proj_segment_len=FRAME_TOKENS, topk_per_head=d["topk"],
                                            force_generic=args.force_generic)
                 d["out"] = out
-        # outputs leave after the last group's rows have arrived: on this platform a device-to-host copy that runs
-        # against a host-to-device copy slows both down several times
+        # outputs leave after the last group's rows have arrived (sending each group's output as soon as it is computed
+        # measured the same: 1.09-1.12 ms either way; large copies in both directions do overlap on this link)
         for g, st in enumerate(streams):
             d = grp[g]
             with torch.cuda.stream(st):
