@@ -300,8 +300,9 @@ def workload_config(name, n_gpus, mode=None):
     if mode is None:
         mode = "single" if n_gpus == 1 else ("heads" if HEADS % n_gpus == 0 and n_gpus <= 4 else "kv")
     sharding = {"single": "none", "heads": "head-split, no data-path collective (outputs stay head-sharded)",
-                "kv": "kv-shard: pooled keys all-gathered, per-branch partial outputs + log-sum-exp exchanged by query rows in ONE "
-                      "all-to-all, merge + gate fused, finished rows all-gathered (NCCL)"}[mode]
+                "kv": "kv-shard: pooled keys all-gathered; per-branch partial outputs + log-sum-exp go to the rank that merges "
+                      "their query rows (stored by the attention kernel into that rank's buffer over NVLink, or ONE NCCL "
+                      "all-to-all: see 'exchange'); merge + gate fused; finished rows all-gathered"}[mode]
     note = "" if spec["block"] == 64 else " (128-token blocks are the benchmark's; the reference's HSAAttention class accepts 64 only, " \
                                           "its functional hsa_attention any size)"
     return {
@@ -319,13 +320,14 @@ def workload_config(name, n_gpus, mode=None):
 # ------------------------------------------------------------------------------------------------
 class Work:
     def __init__(self, name, dev, world, rank, *, shard="auto", force_generic=False, gather_heads=False,
-                 on_device=False):
+                 on_device=False, exchange="auto"):
         import worldattention_b200 as wa
         from worldattention_b200 import sharded
         from worldattention_b200.hsa.attention import _compress_blhd
         self.wa, self.sharded = wa, sharded
         self.name, self.dev, self.world, self.rank = name, dev, world, rank
         self.force_generic, self.gather = force_generic, gather_heads
+        self.exchange, self.exchange_used = exchange, None
         spec = self.spec = WORKLOADS[name]
         self.block = block = spec["block"]
         self.topk_all = draw_topk(spec)
@@ -400,8 +402,9 @@ class Work:
                 return self.sharded.gather_heads(out, self.plan) if gather else out
             out = self.sharded.hsa_attention_kv_sharded(self.hsa, self.q, self.k_loc, self.v_loc, self.kc, self.vc,
                                                         kv_len=self.kv_len, shards=self.shards, topk_per_head=self.topk,
-                                                        topk_max=int(self.topk_all.max()))
+                                                        topk_max=int(self.topk_all.max()), exchange=self.exchange)
             self.used_tuned = bool(self.sharded.last_call_info.get("used_tuned"))
+            self.exchange_used = self.sharded.last_call_info.get("exchange")
             return out
 
     def flops(self):
@@ -479,10 +482,10 @@ def max_over_ranks(x: float, dev, world) -> float:
     return float(t.item())
 
 
-def side_workload(name, dev, world, rank, lib, flush, *, steps, shard="auto", on_device=False, check=True):
+def side_workload(name, dev, world, rank, lib, flush, *, steps, shard="auto", on_device=False, check=True, exchange="auto"):
     """A second workload measured the same way as the headline (fewer steps): ms/chunk, kernel time, fractions."""
     import torch.distributed as dist
-    work = Work(name, dev, world, rank, shard=shard, on_device=on_device)
+    work = Work(name, dev, world, rank, shard=shard, on_device=on_device, exchange=exchange)
     sparse_f, linear_f, gate_f = work.flops()
     barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if world > 1 else None
     lib.wa_profile_enable(1)
@@ -492,8 +495,8 @@ def side_workload(name, dev, world, rank, lib, flush, *, steps, shard="auto", on
     peak_tf, _, _ = measured_peaks()
     kernel_ms = float(np.mean(kern_ms)) if kern_ms else None
     counted = sparse_f + (linear_f + gate_f if work.used_tuned else 0.0)
-    out = {"workload": workload_config(name, world, work.mode)["workload"], "sharding": work.mode, "ms_per_step": total / steps,
-           "steps": steps, "kernel_ms_rank0": kernel_ms, "tcgen05_kernel": work.used_tuned,
+    out = {"workload": workload_config(name, world, work.mode)["workload"], "sharding": work.mode, "exchange": work.exchange_used,
+           "ms_per_step": total / steps, "steps": steps, "kernel_ms_rank0": kernel_ms, "tcgen05_kernel": work.used_tuned,
            "flops_rank0": {"sparse": sparse_f, "linear": linear_f, "gate": gate_f},
            "frac_of_bf16_peak": (counted / (kernel_ms * 1e-3) / 1e12 / peak_tf) if kernel_ms else None,
            "sparse_only_frac": (sparse_f / (kernel_ms * 1e-3) / 1e12 / peak_tf) if kernel_ms else None}
@@ -938,6 +941,9 @@ def main():
     ap.add_argument("--hkv-layers", type=int, default=30, help="layers in the hot HKV measurement (30 = benchmark config 3)")
     ap.add_argument("--hkv-cold-layers", type=int, default=2, help="layers in the cold-tier HKV measurement")
     ap.add_argument("--shard", default="auto", choices=["auto", "heads", "kv"], help="sharding for --gpus > 1")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
+                    help="kv sharding: how the partial records reach the merging rank (peer = stored by the attention kernel "
+                         "into the peers' buffers over NVLink; nccl = one all-to-all; auto = peer where it applies)")
     ap.add_argument("--gather-heads", action="store_true",
                     help="head split: also all-gather the outputs (off: they stay head-sharded for a head-parallel consumer)")
     ap.add_argument("--triton-incumbent-child", action="store_true", help=argparse.SUPPRESS)
@@ -975,7 +981,7 @@ def main():
     block = spec["block"]
 
     work = Work(args.workload, dev, world, rank, shard=args.shard, force_generic=args.force_generic,
-                gather_heads=args.gather_heads)
+                gather_heads=args.gather_heads, exchange=args.exchange)
     mode, hsa = work.mode, work.hsa
     q, k, v, kc, vc = work.q, work.k, work.v, work.kc, work.vc
     q_h, k_h, v_h = work.q_h, work.k_h, work.v_h
@@ -1156,12 +1162,13 @@ def main():
 
     # ---- the long-horizon cache (config 5) sharded the way the headline is: the configuration the sharding is for -----
     extras = {}
+    exchange_used = work.exchange_used
     if not args.no_extras and not args.force_generic:
         del work, q, k, v, kc, vc, forward
         torch.cuda.empty_cache()
         if args.workload != "c5":
             extras["long_horizon"] = side_workload("c5", dev, world, rank, lib, flush_l2, steps=10,
-                                                   shard=args.shard, on_device=True)
+                                                   shard=args.shard, on_device=True, exchange=args.exchange)
         if world == 1 and args.workload != "c2-64":
             extras["block64"] = side_workload("c2-64", dev, 1, 0, lib, flush_l2, steps=30)
 
@@ -1196,6 +1203,7 @@ def main():
         "pooled_key_cache": pooled_cache,
         "head_split_on_the_same_ranks": head_split_alt,
         "equals_single_gpu": equals_single,
+        "exchange": exchange_used,
         "clocks": clocks,
         "wall_s": wall,
     }

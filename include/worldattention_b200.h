@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define WA_ABI_VERSION 2
+#define WA_ABI_VERSION 3
 
 /* element types */
 #define WA_F32 0
@@ -252,6 +252,15 @@ typedef struct wa_hsa_params {
      * record [sparse | linear | lse_s lse_l pad pad] and the rows of a query range one contiguous block: the unit the
      * KV-sharded path exchanges.  tcgen05 kernel only. */
     int64_t part_stride, lse_stride_token, lse_stride_head;
+    /* Partial outputs written straight into the buffers of the ranks that merge them (KV-sharded multi-GPU, B = 1, packed
+     * records as above).  peer_rows > 0 switches it on: query row t belongs to rank t / peer_rows and is stored as that
+     * rank's row peer_self * peer_rows + t % peer_rows, i.e. the record of (t, head) goes to
+     * part_sparse + peer_delta[t / peer_rows] + ((peer_self * peer_rows + t % peer_rows) * H + head) * part_stride
+     * (likewise part_linear and the normalisers).  peer_delta[r] is the distance IN FLOATS from this rank's buffer to rank
+     * r's buffer as mapped into this process (CUDA IPC / peer access; 0 for the rank itself).  Plain stores over NVLink: the
+     * caller orders them against the readers (a collective or an event after the launch).  tcgen05 kernel only. */
+    int32_t peer_rows, peer_self;
+    int64_t peer_delta[8];
 } wa_hsa_params;
 
 /* Bytes of workspace wa_hsa_forward needs for these sizes (pointers in `p` are ignored). */

@@ -64,6 +64,18 @@ def main():
         assert max_abs < 2e-2 and mean_rel < 1e-2, (max_abs, mean_rel)
         info = dict(sharded.last_call_info)
         assert info.get("collectives") == 3 or world == 1, info
+        # the same forward with the all-to-all instead of peer stores (or the other way round): identical records, so
+        # identical output
+        other = "nccl" if info.get("exchange") == "peer stores" else "peer"
+        try:
+            got_other = sharded.hsa_attention_kv_sharded(hsa, q, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(),
+                                                         kc[:, seg_lo * r: seg_hi * r].contiguous(),
+                                                         vc[:, seg_lo * r: seg_hi * r].contiguous(), kv_len=kv_len, shards=shards,
+                                                         topk_per_head=tk, exchange=other)
+            assert torch.equal(got_other, got_kv), f"exchange={other} differs from exchange={info.get('exchange')}"
+            info["other_exchange_equal"] = other
+        except (ValueError, RuntimeError) as exc:      # e.g. a shard without compressed slots: peer stores do not apply
+            info["other_exchange_skipped"] = str(exc)[:80]
         if rank == 0:
             print(f"topk={'fixed' if tk is not None else 'cum-mass'}: head-split exact, kv-shard max_abs={max_abs:.2e} "
                   f"mean_rel={mean_rel:.2e} {info}", flush=True)

@@ -20,14 +20,14 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(handle, name), f"{name} is declared in the header but not exported"
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
-    assert handle.wa_abi_version() == 2
+    assert handle.wa_abi_version() == 3
 
 
 def test_struct_layouts_match_the_header():
     from worldattention_b200 import _lib
     assert ctypes.sizeof(_lib.Tensor4) == 40
     assert ctypes.sizeof(_lib.PageCopy) == 40
-    assert ctypes.sizeof(_lib.HsaParams) == 14 * 4 + 2 * 8 + 6 * 40 + 9 * 8 + 8 + 6 * 8 + 8 + 2 * 4 + 8 + 3 * 8
+    assert ctypes.sizeof(_lib.HsaParams) == 14 * 4 + 2 * 8 + 6 * 40 + 9 * 8 + 8 + 6 * 8 + 8 + 2 * 4 + 8 + 3 * 8 + 2 * 4 + 8 * 8
     assert ctypes.sizeof(_lib.HsaParams) == _lib.lib().wa_hsa_params_size()       # what the compiler laid out
     assert _lib.HsaParams.tau_min.offset == 56 and _lib.HsaParams.q.offset == 72
 

@@ -131,3 +131,51 @@ def test_local_candidates_of_a_long_shard_are_the_best_blocks_in_order():
                 assert np.all(keys[:-1] < keys[1:])                                        # ascending keys = best first
                 ids = (keys & np.uint64(0xFFFFFFFF)).astype(np.int64) - block_lo
                 assert np.array_equal(ids, np.argsort(-logits[h, i], kind="stable")[:kcap])
+
+
+@pytest.mark.parametrize("world", [3, 8])
+def test_partial_records_stored_into_the_merging_ranks_buffers(world):
+    """The peer-store form of the exchange with the ranks' receive buffers all on one GPU: every "rank" runs the partial
+    kernel with the distances to the other buffers, and each buffer must end up holding exactly what the all-to-all form
+    delivers (slice j of every rank's records)."""
+    import worldattention_b200 as wa
+    from worldattention_b200 import sharded
+    from worldattention_b200.hsa import branches
+    from worldattention_b200.hsa.routing import block_attention_map, build_block_routing
+    heads, d, q_len, kv_len, seg, bs = 4, 128, 333, 24960, 1560, 128      # 16 segments: every shard owns compressed slots
+    g = torch.Generator().manual_seed(4)
+    q = (torch.randn(1, q_len, heads, d, generator=g) * 0.6).to(dev(), torch.bfloat16)
+    k = (torch.randn(1, kv_len, heads, d, generator=g) * 0.6).to(dev(), torch.bfloat16)
+    v = torch.randn(1, kv_len, heads, d, generator=g).to(dev(), torch.bfloat16)
+    hsa = wa.hsa.HSAAttention(heads, d, block_size=bs, proj_segment_len=seg).to(dev())
+    wa.hsa_stage.init_hsa_parameters(hsa)
+    with torch.no_grad():
+        kc, vc = hsa.compress_kv_cache(k, v)
+    topk = torch.tensor([3, 17, 1, 8], dtype=torch.int32, device=dev())
+    shards = sharded.plan_kv_shards(kv_len, bs, world, seg)
+    blocks = [-(-(b - a) // bs) for a, b in shards]
+    q_pooled = sharded._pool_blhd(q, bs)
+    pooled = torch.cat([sharded._pool_blhd(k[:, a:b].contiguous(), bs) for a, b in shards], dim=2)
+    decided = build_block_routing(block_attention_map(q_pooled, pooled), hsa.tau_min, hsa.tau_max, topk_per_head=topk)
+    rp, _ = sharded.exchange_rows(q_len, world)
+    rec = branches.record_floats(d)
+    receive = [torch.zeros((1, world * rp, heads, rec), device=dev()) for _ in range(world)]      # one buffer per "rank"
+    r_ = hsa.proj_rank
+    sent = []
+    for r, (a, b) in enumerate(shards):
+        idx, n = sharded.local_selection(decided.index, decided.num, sum(blocks[:r]), sum(blocks[:r + 1]))
+        s_lo, s_hi = -(-a // seg), (-(-b // seg) if r < world - 1 else -(-kv_len // seg))
+        args = (q, k[:, a:b].contiguous(), v[:, a:b].contiguous(), kc[:, s_lo * r_: s_hi * r_].contiguous(),
+                vc[:, s_lo * r_: s_hi * r_].contiguous(), idx, n, bs)
+        plain = torch.zeros((1, rp * world, heads, rec), device=dev())
+        assert branches.hsa_partials_packed(*args, plain)
+        sent.append(plain[0])
+        deltas = [(receive[t].data_ptr() - receive[r].data_ptr()) // 4 for t in range(world)]
+        assert branches.hsa_partials_packed(*args, receive[r], peer=(rp, r, deltas))
+    torch.cuda.synchronize()
+    for j in range(world):
+        want = torch.stack([s[j * rp:(j + 1) * rp] for s in sent])                           # [W, rp, H, rec]
+        got = receive[j][0].view(world, rp, heads, rec)
+        rows = max(0, min(q_len, (j + 1) * rp) - j * rp)
+        assert torch.equal(got[:, :rows], want[:, :rows]), j
+        assert torch.count_nonzero(got[:, rows:]) == 0

@@ -41,6 +41,7 @@ class HsaParams(C.Structure):
         ("k_pooled", C.c_void_p), ("k_pooled_valid", C.c_int32), ("reserved2", C.c_int32),
         ("status_mirror", C.c_void_p),
         ("part_stride", C.c_int64), ("lse_stride_token", C.c_int64), ("lse_stride_head", C.c_int64),
+        ("peer_rows", C.c_int32), ("peer_self", C.c_int32), ("peer_delta", C.c_int64 * 8),
     ]
 
 
@@ -114,7 +115,7 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = _RESTYPES.get(name, C.c_int)
-        if handle.wa_abi_version() != 2 or handle.wa_hsa_params_size() != C.sizeof(HsaParams):
+        if handle.wa_abi_version() != 3 or handle.wa_hsa_params_size() != C.sizeof(HsaParams):
             raise RuntimeError("libwa_b200.so ABI mismatch (version or wa_hsa_params layout); rebuild the library")
         _lib = handle
     return _lib

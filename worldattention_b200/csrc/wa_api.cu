@@ -192,6 +192,9 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
     WA_REQUIRE(tuned || !(p->flags & WA_HSA_REQUIRE_TUNED), WA_ERR_UNSUPPORTED,
                "%s: shape not covered by the tcgen05 kernel (needs bf16, head_dim 128, block 64 or 128)", what);
 
+    WA_REQUIRE(p->peer_rows == 0 || (tuned && partial && p->B == 1 && p->peer_rows > 0 && p->peer_self >= 0 && p->peer_self < 8 &&
+                                     (long long)p->peer_rows * 8 >= p->Lq && p->part_stride > 0 && p->lse_stride_token > 0),
+               WA_ERR_ARG, "%s: peer stores need the tcgen05 kernel, packed partial records, B = 1 and at most 8 ranks covering Lq", what);
     WA_REQUIRE(tuned || (p->part_stride == 0 && p->lse_stride_token == 0 && p->lse_stride_head == 0), WA_ERR_UNSUPPORTED,
                "%s: a partial-output layout other than the contiguous one needs the tcgen05 kernel", what);
 

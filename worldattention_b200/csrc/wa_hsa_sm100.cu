@@ -492,9 +492,20 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const int tokenA = qb * BLK + rowA, tokenB = tokenA + 8;
             const bool okA = rowA < BLK && tokenA < p.Lq, okB = rowB < BLK && tokenB < p.Lq;
             // float32 offsets of this thread's first column pair in the partial outputs, and of the rows' normalisers
-            const long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
-            const long long partB = partA + 8ll * p.H * p.part_stride;
-            const long long lseA = (long long)b * p.lse_sb + (long long)h * p.lse_sh + (long long)tokenA * p.lse_st, lseB = lseA + 8 * p.lse_st;
+            long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
+            long long partB = partA + 8ll * p.H * p.part_stride;
+            long long lseA = (long long)b * p.lse_sb + (long long)h * p.lse_sh + (long long)tokenA * p.lse_st, lseB = lseA + 8 * p.lse_st;
+            if (p.peer_rows > 0) {
+                // the rank that merges a query row receives it directly (plain stores into its buffer, over NVLink for
+                // another GPU): row t is rank t / peer_rows' row peer_self * peer_rows + t % peer_rows
+                const int dA = min(tokenA / p.peer_rows, 7), dB = min(tokenB / p.peer_rows, 7);
+                const long long rA = (long long)p.peer_self * p.peer_rows + (tokenA - dA * p.peer_rows);
+                const long long rB = (long long)p.peer_self * p.peer_rows + (tokenB - dB * p.peer_rows);
+                partA = (rA * p.H + h) * p.part_stride + 2 * c2 + p.peer_delta[dA];
+                partB = (rB * p.H + h) * p.part_stride + 2 * c2 + p.peer_delta[dB];
+                lseA = (long long)h * p.lse_sh + rA * p.lse_st + p.peer_delta[dA];
+                lseB = (long long)h * p.lse_sh + rB * p.lse_st + p.peer_delta[dB];
+            }
             const int gbuf = (sg + n_kv) % S_BUFS;
             float inv_linA = 0.f, inv_linB = 0.f, inv_spA = 0.f, inv_spB = 0.f;
             uint32_t park[32];   // the sparse branch's result: word 2j = row A, 2j + 1 = row B, bf16 pair of step j
@@ -989,6 +1000,8 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     kp.scale_log2 = (float)(pow((double)TILE, -0.5) * 1.4426950408889634);
     kp.part_sparse = p->part_sparse; kp.part_linear = p->part_linear;
     kp.lse_sparse = p->lse_sparse; kp.lse_linear = p->lse_linear;
+    kp.peer_rows = p->part_sparse ? p->peer_rows : 0; kp.peer_self = p->peer_self;
+    for (int r = 0; r < 8; ++r) kp.peer_delta[r] = p->peer_delta[r];
     // default layouts: contiguous [B, Lq, H, 128] vectors and [B, H, Lq] normalisers; the packed exchange layout of the
     // KV-sharded path puts both branches of a (token, head) into one record
     kp.part_stride = p->part_stride > 0 ? p->part_stride : TILE;

@@ -125,13 +125,19 @@ def record_floats(head_dim: int) -> int:
     return 2 * head_dim + 4
 
 
-def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int, records: torch.Tensor) -> bool:
+def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int, records: torch.Tensor, *,
+                        peer=None) -> bool:
     """`hsa_partials` writing straight into packed records (`records`: float32 `[B, rows >= Lq, H, 2 D + 4]`, contiguous).
 
     Both branch outputs and both normalisers of a (token, head) land in one record, so the rows of a query range are
     one contiguous block -- the unit the KV-sharded path sends to the rank that merges those rows.  Only the tcgen05
     kernel writes this layout; returns False (nothing launched) where it does not cover the shape, and the caller packs
     the output of `hsa_partials` itself.
+
+    `peer = (rows_per_rank, this_rank, deltas)`: the records go straight into the buffers of the ranks that merge them
+    (`records` is then this rank's receive buffer `[1, ranks * rows_per_rank, H, 2 D + 4]`, `deltas[r]` the distance in
+    floats from it to rank r's buffer as mapped into this process): query row t becomes row
+    `this_rank * rows_per_rank + t % rows_per_rank` of rank `t // rows_per_rank`.
     """
     import ctypes
     from .attention import _unit_last, _workspace
@@ -160,6 +166,13 @@ def hsa_partials_packed(q, k, v, k_coarse, v_coarse, index, num, block_size: int
     p.part_sparse, p.part_linear = base, base + 4 * head_dim
     p.lse_sparse, p.lse_linear = base + 8 * head_dim, base + 8 * head_dim + 4
     p.part_stride, p.lse_stride_token, p.lse_stride_head = rec, heads * rec, rec
+    if peer is not None:
+        rows_per_rank, this_rank, deltas = peer
+        if bsz != 1 or len(deltas) > 8 or rows_per_rank * len(deltas) < q_len or records.shape[1] < rows_per_rank * len(deltas):
+            raise ValueError("peer stores need B = 1, at most 8 ranks whose rows cover Lq, and a receive buffer of ranks * rows")
+        p.peer_rows, p.peer_self = int(rows_per_rank), int(this_rank)
+        for r, delta in enumerate(deltas):
+            p.peer_delta[r] = int(delta)
     lib = _lib.lib()
     ws = _workspace(dev, lib.wa_hsa_workspace_bytes(ctypes.byref(p)))
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()

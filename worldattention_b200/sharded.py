@@ -245,6 +245,99 @@ def _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, 
     return o_s, l_s, o_l, l_l, False
 
 
+_peer_exchange_failed = False      # set when the IPC set-up did not work on this machine: "auto" then stays on NCCL
+
+
+def _peer_exchange(world, rank, rows, heads, rec, dev, group, *, required: bool):
+    """The cached `PeerExchange` for these sizes, or None when it cannot be set up (every rank then agrees to use NCCL)."""
+    global _peer_exchange_failed
+    key = (world, rank, rows, heads, rec, dev.index, id(group))
+    if key in PeerExchange._cache:
+        return PeerExchange._cache[key]
+    xchg, error = None, None
+    try:
+        xchg = PeerExchange(world, rank, rows, heads, rec, dev, group)
+    except Exception as exc:      # reported below; the decision has to be common to all ranks
+        error = f"{type(exc).__name__}: {exc}"
+    flags = [None] * world
+    dist.all_gather_object(flags, error, group=group)
+    if any(f is not None for f in flags):
+        _peer_exchange_failed = True
+        if required:
+            raise RuntimeError(f"peer exchange set-up failed: {[f for f in flags if f is not None][0]}")
+        return None
+    PeerExchange._cache[key] = xchg
+    return xchg
+
+
+class PeerExchange:
+    """This rank's receive buffer for the partial records, mapped into every rank of the group.
+
+    The partial-output kernel of rank s then stores the record of query row t directly into the buffer of the rank that
+    merges t (`branches.hsa_partials_packed(peer=...)`): the all-to-all of the exchange disappears into the kernel's own
+    stores, which travel over NVLink while the kernel computes.  The buffer is one `cudaMalloc` allocation shared through
+    a CUDA IPC handle (peer access is enabled when a handle is opened); it lives as long as the process.
+
+    Ordering: a receiver may read after every sender's kernel has completed -- the forward puts a one-element all-reduce
+    on the stream behind the kernel -- and a sender may overwrite after the receivers have merged, which the all-gather of
+    the finished rows at the end of the forward implies.
+    """
+
+    _cache: dict = {}
+
+    def __init__(self, world: int, rank: int, rows: int, heads: int, rec: int, dev: torch.device, group=None):
+        from cuda.bindings import runtime as rt
+        self.world, self.rank, self.rows, self.heads, self.rec = world, rank, rows, heads, rec
+        nbytes = world * rows * heads * rec * 4
+
+        def ok(result):
+            err = result[0] if isinstance(result, tuple) else result
+            if int(err) != 0:
+                raise RuntimeError(f"CUDA runtime error {int(err)} while setting up the peer exchange")
+            return result[1] if isinstance(result, tuple) and len(result) > 1 else None
+
+        with torch.cuda.device(dev):
+            self.ptr = int(ok(rt.cudaMalloc(nbytes)))
+            ok(rt.cudaMemset(self.ptr, 0, nbytes))          # rows past the query length are never written: keep them finite
+            handle = ok(rt.cudaIpcGetMemHandle(self.ptr))
+            mine = bytes(handle.reserved)
+            every = [None] * world
+            if world > 1:
+                dist.all_gather_object(every, mine, group=group)
+            else:
+                every = [mine]
+            self.ptrs = []
+            for r in range(world):
+                if r == rank:
+                    self.ptrs.append(self.ptr)
+                else:
+                    h = rt.cudaIpcMemHandle_t()
+                    h.reserved = every[r]
+                    self.ptrs.append(int(ok(rt.cudaIpcOpenMemHandle(h, rt.cudaIpcMemLazyEnablePeerAccess))))
+        if any((p - self.ptr) % 4 for p in self.ptrs):
+            raise RuntimeError("peer buffers are not float-aligned relative to each other")
+        self.deltas = [(p - self.ptr) // 4 for p in self.ptrs]
+        self.local = _raw_tensor(self.ptr, (1, world * rows, heads, rec), dev)      # [1, W * rows, H, rec] float32
+
+    @classmethod
+    def get(cls, world, rank, rows, heads, rec, dev, group=None):
+        key = (world, rank, rows, heads, rec, dev.index, id(group))
+        if key not in cls._cache:
+            cls._cache[key] = cls(world, rank, rows, heads, rec, dev, group)
+        return cls._cache[key]
+
+
+class _RawBuffer:
+    def __init__(self, ptr: int, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False), "version": 3,
+                                         "strides": None}
+
+
+def _raw_tensor(ptr: int, shape, dev: torch.device) -> torch.Tensor:
+    """A float32 tensor over device memory that torch did not allocate."""
+    return torch.as_tensor(_RawBuffer(ptr, shape), device=dev)
+
+
 def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records) -> bool:
     """One rank's partials as packed records (`records`: float32 `[1, rows >= Lq, H, 2 D + 4]`, see
     `branches.hsa_partials_packed`): written by the tcgen05 kernel where it applies, packed here otherwise.  Rows from
@@ -267,7 +360,7 @@ def partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs,
 
 def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local, *, kv_len: int,
                              shards: List[Tuple[int, int]], topk_per_head=None, group=None, routing: str = "auto",
-                             topk_max: Optional[int] = None):
+                             topk_max: Optional[int] = None, exchange: str = "auto"):
     """KV-sharded forward.  `q` is replicated; `k_local`/`v_local` hold this rank's token range.
 
     `kc_local`/`vc_local` are the compressed slots of the segments this rank owns.  Returns the
@@ -282,6 +375,11 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     (token, head) into one packed record; ONE all-to-all hands rank j the records of query rows
     `[j * rp, (j + 1) * rp)` of every shard; rank j merges them, gate-combines its rows, and one all-gather
     distributes the finished bf16 rows.  Three collectives per forward.
+
+    `exchange="peer"` (and `"auto"` where it applies: at most 8 ranks, every shard with keys and compressed slots, the
+    tcgen05 kernel's shapes) removes the all-to-all: the kernel stores every record directly into the receive buffer of
+    the rank that merges its row (`PeerExchange`: CUDA IPC, plain stores over NVLink during the kernel), and a one-element
+    all-reduce behind the kernel tells every rank that its rows have arrived.  `exchange="nccl"` keeps the all-to-all.
     """
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -314,20 +412,51 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
 
     rec = branches.record_floats(head_dim)
     records = None
+    recv = None
     o_s = l_s = o_l = l_l = None
+    if exchange not in ("auto", "nccl", "peer"):
+        raise ValueError("exchange must be 'auto', 'nccl' or 'peer'")
     if world > 1 and bsz == 1:
         rp, row_plan = exchange_rows(q_len, world)
-        records = torch.empty((1, rp * world, heads, rec), dtype=torch.float32, device=q.device)
-        used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records)
+        # every rank takes the same decision from what every rank knows: the shard plan and the shapes
+        seg = hsa_module.proj_segment_len
+        owns_segments = all((-(-(b if r < world - 1 else kv_len) // seg)) > -(-a // seg) for r, (a, b) in enumerate(shards))
+        peer_ok = (world <= 8 and head_dim == 128 and q.dtype == torch.bfloat16 and bs in (64, 128)
+                   and all(b > a for a, b in shards) and owns_segments)
+        if exchange == "peer" and not peer_ok:
+            raise ValueError("the peer exchange needs <= 8 ranks, bf16, head_dim 128, 64- or 128-token blocks and no empty shard")
+        use_peer = peer_ok and exchange != "nccl" and not _peer_exchange_failed
+        xchg = None
+        if use_peer:
+            xchg = _peer_exchange(world, rank, rp, heads, rec, q.device, group, required=exchange == "peer")
+        if xchg is not None:
+            used_tuned = branches.hsa_partials_packed(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, xchg.local,
+                                                      peer=(rp, rank, xchg.deltas))
+            if not used_tuned:      # the kernel declined: deliver the records with plain peer copies instead
+                records = torch.empty((1, rp * world, heads, rec), dtype=torch.float32, device=q.device)
+                used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records)
+                for r in range(world):
+                    dst = _raw_tensor(xchg.ptrs[r], (world, rp, heads, rec), q.device)[rank]
+                    dst.copy_(records[0, r * rp:(r + 1) * rp])
+                records = None
+            arrived = torch.zeros(1, dtype=torch.int32, device=q.device)
+            dist.all_reduce(arrived, group=group)      # every rank's kernel is behind its contribution: the rows are here
+            recv = xchg.local[0]
+        else:
+            records = torch.empty((1, rp * world, heads, rec), dtype=torch.float32, device=q.device)
+            used_tuned = partial_records(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs, records)
     else:
         o_s, l_s, o_l, l_l, used_tuned = _partials_unpacked(q, k_local, v_local, kc_local, vc_local, index_l, num_l, bs)
     last_call_info.update(used_tuned=bool(used_tuned), routing="candidates" if by_candidates else "gather", ranks=world,
-                          # routing exchange + (packed: one all-to-all and one all-gather | unpacked: two all-gathers)
-                          collectives=0 if world == 1 else 3, packed_exchange=records is not None)
+                          # routing exchange + (packed: one all-to-all, or a one-element all-reduce behind peer stores, and
+                          # one all-gather | unpacked: two all-gathers)
+                          collectives=0 if world == 1 else 3, packed_exchange=records is not None or recv is not None,
+                          exchange="peer stores" if recv is not None else ("all-to-all" if records is not None else "all-gather"))
 
     if records is not None:
         recv = torch.empty_like(records[0])                                  # [W * rp, H, rec]: slice j of every rank
         dist.all_to_all_single(recv, records[0], group=group)
+    if recv is not None:
         sparse, linear = branches.merge_packed(recv.view(world, rp * heads, rec), head_dim)
         first, count = row_plan[rank]
         out_rows = q.new_zeros((rp, heads, head_dim)) if count < rp else q.new_empty((rp, heads, head_dim))
