@@ -195,6 +195,9 @@ extern "C" int wa_hsa_forward(const wa_hsa_params *p, int *used_tuned, void *str
     WA_REQUIRE(p->peer_rows == 0 || (tuned && partial && p->B == 1 && p->peer_rows > 0 && p->peer_self >= 0 && p->peer_self < 8 &&
                                      (long long)p->peer_rows * 8 >= p->Lq && p->part_stride > 0 && p->lse_stride_token > 0),
                WA_ERR_ARG, "%s: peer stores need the tcgen05 kernel, packed partial records, B = 1 and at most 8 ranks covering Lq", what);
+    if (p->peer_rows > 0)
+        for (int d = 0; d < 8; ++d)
+            WA_REQUIRE(p->peer_delta[d] % 4 == 0, WA_ERR_ALIGN, "%s: peer_delta[%d] must be a multiple of 4 floats (16 bytes)", what, d);
     WA_REQUIRE(tuned || (p->part_stride == 0 && p->lse_stride_token == 0 && p->lse_stride_head == 0), WA_ERR_UNSUPPORTED,
                "%s: a partial-output layout other than the contiguous one needs the tcgen05 kernel", what);
 

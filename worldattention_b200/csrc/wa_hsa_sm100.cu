@@ -19,6 +19,7 @@
 //
 // Every mbarrier wait is bounded (about two seconds); on expiry the kernel raises a flag in
 // global memory, all roles leave their loops, tensor memory is released and the kernel returns.
+#include <climits>
 #include <cstdlib>
 
 #include "wa_internal.cuh"
@@ -491,9 +492,7 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             uint8_t *q_stage = q_s + qs * TILE_BYTES;
             const int tokenA = qb * BLK + rowA, tokenB = tokenA + 8;
             const bool okA = rowA < BLK && tokenA < p.Lq, okB = rowB < BLK && tokenB < p.Lq;
-            // float32 offsets of this thread's first column pair in the partial outputs, and of the rows' normalisers
-            long long partA = (((long long)b * p.Lq + tokenA) * p.H + h) * p.part_stride + 2 * c2;
-            long long partB = partA + 8ll * p.H * p.part_stride;
+            // float32 offsets of the rows' normalisers
             long long lseA = (long long)b * p.lse_sb + (long long)h * p.lse_sh + (long long)tokenA * p.lse_st, lseB = lseA + 8 * p.lse_st;
             if (p.peer_rows > 0) {
                 // the rank that merges a query row receives it directly (plain stores into its buffer, over NVLink for
@@ -501,14 +500,16 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const int dA = min(tokenA / p.peer_rows, 7), dB = min(tokenB / p.peer_rows, 7);
                 const long long rA = (long long)p.peer_self * p.peer_rows + (tokenA - dA * p.peer_rows);
                 const long long rB = (long long)p.peer_self * p.peer_rows + (tokenB - dB * p.peer_rows);
-                partA = (rA * p.H + h) * p.part_stride + 2 * c2 + p.peer_delta[dA];
-                partB = (rB * p.H + h) * p.part_stride + 2 * c2 + p.peer_delta[dB];
                 lseA = (long long)h * p.lse_sh + rA * p.lse_st + p.peer_delta[dA];
                 lseB = (long long)h * p.lse_sh + rB * p.lse_st + p.peer_delta[dB];
             }
             const int gbuf = (sg + n_kv) % S_BUFS;
             float inv_linA = 0.f, inv_linB = 0.f, inv_spA = 0.f, inv_spB = 0.f;
-            uint32_t park[32];   // the sparse branch's result: word 2j = row A, 2j + 1 = row B, bf16 pair of step j
+            // The sparse branch's result, parked until the item's end.  Combined output: park word 2j = row A, 2j + 1 = row B,
+            // bf16 pair of step j (gpk then holds the gate values in the same form).  Partial-output mode: float32, park
+            // words 2j, 2j + 1 = row A's column pair of step j, gpk the same of row B.
+            uint32_t park[32], gpk[32];
+            float ls_spA = 0.f, ls_spB = 0.f;   // the sparse branch's log-sum-exp (packed records write both in one store)
 
             for (int phase = 0; phase < 2 && ok; ++phase) {
                 const int t0 = phase == 0 ? 0 : n_sel, t1 = phase == 0 ? n_sel : n_kv;
@@ -641,8 +642,10 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                                 const float a0 = __uint_as_float(ro[4 * j]) * inv_spA, a1 = __uint_as_float(ro[4 * j + 1]) * inv_spA;
                                 const float b0 = __uint_as_float(ro[4 * j + 2]) * inv_spB, b1 = __uint_as_float(ro[4 * j + 3]) * inv_spB;
                                 if (p.part_sparse) {
-                                    if (okA) *reinterpret_cast<float2 *>(p.part_sparse + partA + 8 * (4 * c + j)) = make_float2(a0, a1);
-                                    if (okB) *reinterpret_cast<float2 *>(p.part_sparse + partB + 8 * (4 * c + j)) = make_float2(b0, b1);
+                                    park[2 * (4 * c + j)] = __float_as_uint(a0);
+                                    park[2 * (4 * c + j) + 1] = __float_as_uint(a1);
+                                    gpk[2 * (4 * c + j)] = __float_as_uint(b0);
+                                    gpk[2 * (4 * c + j) + 1] = __float_as_uint(b1);
                                 } else {
                                     __nv_bfloat162 ha = __floats2bfloat162_rn(a0, a1), hbv = __floats2bfloat162_rn(b0, b1);
                                     park[2 * (4 * c + j)] = *reinterpret_cast<uint32_t *>(&ha);
@@ -666,35 +669,33 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (phase == 0) {
                     inv_spA = invA;
                     inv_spB = invB;
-                    if (p.lse_sparse && c2 == 0) {
+                    ls_spA = lsA;
+                    ls_spB = lsB;
+                    if (p.lse_sparse && !p.lse_packed && c2 == 0) {
                         if (okA) p.lse_sparse[lseA] = lsA;
                         if (okB) p.lse_sparse[lseB] = lsB;
                     }
                     if (n_sel == 0) {   // no selected block: the sparse term is zero and there is no accumulator to wait for
-                        if (p.part_sparse) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                if (okA) *reinterpret_cast<float2 *>(p.part_sparse + partA + 8 * j) = make_float2(0.f, 0.f);
-                                if (okB) *reinterpret_cast<float2 *>(p.part_sparse + partB + 8 * j) = make_float2(0.f, 0.f);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) park[j] = 0u;
-                        }
+                        for (int j = 0; j < 32; ++j) park[j] = gpk[j] = 0u;   // +0.0f and a bf16 pair of zeros alike
                     }
                 } else {
                     inv_linA = invA;
                     inv_linB = invB;
                     if (p.lse_linear && c2 == 0) {
-                        if (okA) p.lse_linear[lseA] = lsA;
-                        if (okB) p.lse_linear[lseB] = lsB;
+                        if (p.lse_packed) {   // [lse_sparse, lse_linear, 0, 0] behind the two branches of the record: one 16-byte store
+                            if (okA) *reinterpret_cast<float4 *>(p.lse_sparse + lseA) = make_float4(ls_spA, lsA, 0.f, 0.f);
+                            if (okB) *reinterpret_cast<float4 *>(p.lse_sparse + lseB) = make_float4(ls_spB, lsB, 0.f, 0.f);
+                        } else {
+                            if (okA) p.lse_linear[lseA] = lsA;
+                            if (okB) p.lse_linear[lseB] = lsB;
+                        }
                     }
                 }
             }
             // ---- gate tile + combine ----
             // gate values of this thread's columns, rounded to bf16 as the reference's gate is (word 2j = row A, 2j + 1 =
             // row B); computed while the last PV product of the linear branch is still in flight
-            uint32_t gpk[32];
             // byte offset of this thread's 4 bytes inside 16-byte chunk j of a row in the swizzled 128 x 128 bf16 tiles
             auto tile_off = [&](int row, int j) -> int {
                 return (j >> 3) * HALF_BYTES + row * 128 + (((j & 7) ^ (row & 7)) << 4) + 4 * c2;
@@ -753,7 +754,70 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     WA_TRACE(12);
                 }
             }
-            if (ok) {
+            if (ok && p.part_linear) {
+                // Partial outputs leave as whole rows: a quad holds 32 bytes of a row per step, and stores of that size are
+                // what a peer's buffer takes worst over NVLink.  The Q stage is free by now (every score product of the item
+                // has landed), so each warp turns its 16 rows x 64 columns of float32 around in 4 KB of it (32-byte pieces
+                // XOR-swizzled by row) and writes 512 contiguous bytes of two rows per instruction.
+                uint8_t *scr = q_stage + warp * 4096;
+                const int lr = lane & 15, row_l = rg * 32 + hb * 16 + lr;
+                const int token_l = qb * BLK + row_l;
+                constexpr long long NO_ROW = LLONG_MIN;   // (a peer's buffer may lie below this rank's: offsets can be negative)
+                long long rec = NO_ROW;      // float offset of this lane's row (rows 0..15 of the warp) in the records
+                if (row_l < BLK && token_l < p.Lq) {
+                    if (p.peer_rows > 0) {
+                        const int d = min(token_l / p.peer_rows, 7);
+                        rec = (((long long)p.peer_self * p.peer_rows + (token_l - d * p.peer_rows)) * p.H + h) * p.part_stride
+                              + p.peer_delta[d];
+                    } else {
+                        rec = (((long long)b * p.Lq + token_l) * p.H + h) * p.part_stride;
+                    }
+                }
+                const int q16 = lane & 15, up = lane >> 4;
+                auto put = [&](int jl, float x0, float x1, float y0, float y1) {   // step jl (0..7) of this 64-column half
+                    *reinterpret_cast<float2 *>(scr + g * 256 + ((jl ^ g) << 5) + c2 * 8) = make_float2(x0, x1);
+                    *reinterpret_cast<float2 *>(scr + (8 + g) * 256 + ((jl ^ g) << 5) + c2 * 8) = make_float2(y0, y1);
+                };
+                auto flush = [&](float *base, int half) {
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r16 = 2 * i + up;
+                        const long long at = __shfl_sync(0xffffffffu, rec, r16);
+                        const float4 val = *reinterpret_cast<const float4 *>(scr + r16 * 256 + (((q16 >> 1) ^ (r16 & 7)) << 5) + (q16 & 1) * 16);
+                        if (at != NO_ROW) *reinterpret_cast<float4 *>(base + at + 64 * half + 4 * q16) = val;
+                    }
+                    __syncwarp();
+                };
+                if (p.part_sparse) {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                        for (int jl = 0; jl < 8; ++jl) {
+                            const int jj = 8 * half + jl;
+                            put(jl, __uint_as_float(park[2 * jj]), __uint_as_float(park[2 * jj + 1]), __uint_as_float(gpk[2 * jj]),
+                                __uint_as_float(gpk[2 * jj + 1]));
+                        }
+                        flush(p.part_sparse, half);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {   // 32 columns at a time
+                    uint32_t o[16];
+                    TMEM_LDQ16(tmem_o + lane_addr + c * 32, o);
+                    tmem_wait_ld();
+                    if (c == 3) {
+                        // the linear accumulator is in registers: the next item's PV products may overwrite it
+                        tc_fence_before();
+                        warp_arrive(&bar->o_free);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        put(4 * (c & 1) + j, __uint_as_float(o[4 * j]) * inv_linA, __uint_as_float(o[4 * j + 1]) * inv_linA,
+                            __uint_as_float(o[4 * j + 2]) * inv_linB, __uint_as_float(o[4 * j + 3]) * inv_linB);
+                    if (c & 1) flush(p.part_linear, c >> 1);
+                }
+            } else if (ok) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {   // 32 columns at a time
                     uint32_t o[16];
@@ -770,11 +834,6 @@ hsa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         const int jj = 4 * c + j;
                         const float a0 = __uint_as_float(o[4 * j]) * inv_linA, a1 = __uint_as_float(o[4 * j + 1]) * inv_linA;
                         const float b0 = __uint_as_float(o[4 * j + 2]) * inv_linB, b1 = __uint_as_float(o[4 * j + 3]) * inv_linB;
-                        if (p.part_linear) {
-                            if (okA) *reinterpret_cast<float2 *>(p.part_linear + partA + 8 * jj) = make_float2(a0, a1);
-                            if (okB) *reinterpret_cast<float2 *>(p.part_linear + partB + 8 * jj) = make_float2(b0, b1);
-                            continue;
-                        }
                         const uint32_t spA = park[2 * jj], spB = park[2 * jj + 1], gA = gpk[2 * jj], gB = gpk[2 * jj + 1];   // low half = even column
                         __nv_bfloat162 ra = __floats2bfloat162_rn(fmaf(a0, __uint_as_float(gA << 16), __uint_as_float(spA << 16)),
                                                                    fmaf(a1, __uint_as_float(gA & 0xffff0000u), __uint_as_float(spA & 0xffff0000u)));
@@ -1005,6 +1064,10 @@ int hsa_sm100_launch(const wa_hsa_params *p, int Lc, const wa_tensor4 *kc, const
     // default layouts: contiguous [B, Lq, H, 128] vectors and [B, H, Lq] normalisers; the packed exchange layout of the
     // KV-sharded path puts both branches of a (token, head) into one record
     kp.part_stride = p->part_stride > 0 ? p->part_stride : TILE;
+    // packed records [sparse | linear | lse_sparse, lse_linear, 0, 0]: both normalisers leave in one 16-byte store
+    kp.lse_packed = p->part_sparse && p->lse_sparse == p->part_sparse + 2 * TILE && p->lse_linear == p->lse_sparse + 1 &&
+                    kp.part_stride >= 2 * TILE + 4 && p->lse_stride_token > 0 && p->lse_stride_token % 4 == 0 &&
+                    p->lse_stride_head % 4 == 0;
     if (p->lse_stride_token > 0) {
         kp.lse_st = p->lse_stride_token; kp.lse_sh = p->lse_stride_head; kp.lse_sb = (long long)p->Lq * p->lse_stride_token;
     } else {

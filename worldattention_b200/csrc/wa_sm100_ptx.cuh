@@ -319,6 +319,7 @@ struct Params {
     float *lse_sparse, *lse_linear;     // float32: value of (b, head, token) at b * lse_sb + head * lse_sh + token * lse_st
     long long part_stride, lse_sb, lse_sh, lse_st;
     // partial outputs stored into peer ranks' buffers (see wa_hsa_params::peer_rows); peer_rows == 0: off
+    int lse_packed;
     int peer_rows, peer_self;
     long long peer_delta[8];
 };
