@@ -169,6 +169,11 @@ class ClockSampler:
         self.thread = threading.Thread(target=loop, daemon=True)
         self.thread.start()
 
+    def mark(self):
+        """Forget what was sampled so far: the timed region starts here (the thread itself was started earlier, so that
+        NVML's start-up cost and the thread's first samples fall into the warm-up)."""
+        self.sm, self.mask = [], 0
+
     def stop(self):
         if self.thread is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error or "not sampled"]}
@@ -454,6 +459,7 @@ def timed_steps(fn, steps, warmup, flush, lib=None, barrier=None):
     """Per-step milliseconds (CUDA events around each step, L2 flushed before) and, when `lib` profiles, the attention
     kernel's milliseconds per step."""
     for _ in range(warmup):
+        flush()
         fn()
     if barrier:
         barrier()
@@ -999,13 +1005,16 @@ def main():
     used_tuned = work.used_tuned
 
     # ---- device-resident timing ------------------------------------------------------------------
-    for _ in range(args.warmup):
-        forward()
-    barrier()
+    # warm-up steps are what the timed steps are: L2 flushed, the kernel's event bracket on, the clock sampler running
     lib.wa_profile_enable(1)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        flush_l2()
+        forward()
+    barrier()
+    sampler.mark()
     launches0 = lib.wa_launch_count()
     barrier()
     wall0 = time.perf_counter()
@@ -1016,6 +1025,8 @@ def main():
     lib.wa_profile_enable(0)
     total_ms = max_over_ranks(sum(step_ms), dev, world)
     ms_per_step = total_ms / args.steps
+    step_stats = {"median_ms_rank0": float(np.median(step_ms)), "min_ms_rank0": float(np.min(step_ms)),
+                  "max_ms_rank0": float(np.max(step_ms)), "slowest_step": int(np.argmax(step_ms))}     # spread of the timed steps (the headline is their mean)
     wa._lib.raise_if_failed(dev)          # a bounded wait that ran out inside the kernel would have left its code here
 
     # ---- N > 1: the sharded result against the single-GPU call (untimed) ------------------------------
@@ -1204,6 +1215,7 @@ def main():
         "head_split_on_the_same_ranks": head_split_alt,
         "equals_single_gpu": equals_single,
         "exchange": exchange_used,
+        "step_spread": step_stats,
         "clocks": clocks,
         "wall_s": wall,
     }

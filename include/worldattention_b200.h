@@ -257,7 +257,8 @@ typedef struct wa_hsa_params {
      * rank's row peer_self * peer_rows + t % peer_rows, i.e. the record of (t, head) goes to
      * part_sparse + peer_delta[t / peer_rows] + ((peer_self * peer_rows + t % peer_rows) * H + head) * part_stride
      * (likewise part_linear and the normalisers).  peer_delta[r] is the distance IN FLOATS from this rank's buffer to rank
-     * r's buffer as mapped into this process (CUDA IPC / peer access; 0 for the rank itself).  Plain stores over NVLink: the
+     * r's buffer as mapped into this process (CUDA IPC / peer access; 0 for the rank itself; a multiple of 4, since the
+     * records leave in 16-byte stores).  Plain stores over NVLink: the
      * caller orders them against the readers (a collective or an event after the launch).  tcgen05 kernel only. */
     int32_t peer_rows, peer_self;
     int64_t peer_delta[8];
