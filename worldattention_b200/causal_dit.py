@@ -335,8 +335,20 @@ class ChunkPipeline:
         self.stats = _Stats()
         self.reset()
 
-    def reset(self) -> None:
+    def reset(self, keep_buffers: bool = False) -> None:
+        """Empty caches for a new video.  `keep_buffers`: clear the existing cache tensors instead of allocating new
+        ones, so that a graph captured over their addresses stays valid (a serving process captures once)."""
         cfg, dev = self.cfg, self.dev
+        if keep_buffers and getattr(self, "kv_cache", None):
+            for cache in self.kv_cache:
+                for t in cache.values():
+                    t.zero_()
+            for c in self.cross_cache:
+                c["is_init"] = False
+            self.local_end = self.global_end = 0
+            if self.hkv is not None:
+                self.hkv.reset()
+            return
         size = cfg.window_frames * cfg.frame_tokens
         self.kv_cache = []
         for blk in self.model.blocks:
@@ -520,14 +532,29 @@ def time_generation(cfg: DiTConfig, *, chunks: int, switch_every_chunks: int = 0
     switches = [c * cfg.frames_per_chunk for c in range(switch_every_chunks, chunks, switch_every_chunks)] if switch_every_chunks else []
     gp = torch.Generator(device="cpu").manual_seed(seed + 1)
     prompts = [torch.randn((cfg.text_len, cfg.text_dim), generator=gp) for _ in range(len(switches) + 1)]
-    # untimed: three chunks, with a bank one prompt switch among them (store, retrieve, install), so that library
-    # initialisation and first-call set-up are not counted as generation time
+    # untimed: enough chunks to fill the window and run one steady-state chunk (with `cuda_graph` that is where the
+    # graph is captured: once per process, as a serving process would), then with a bank one prompt switch (store,
+    # retrieve, install), so that library initialisation and first-call set-up are not counted as generation time
     fpc = cfg.frames_per_chunk
-    if hkv is not None:
-        pipe.generate(noise[:, :3 * fpc], [prompts[0], prompts[0]], [2 * fpc], generator=g)
+    fill = -(-cfg.window_frames // fpc) + 1
+    warm = min(fill + (1 if hkv is not None else 0), chunks)
+    if hkv is not None and warm > 1:
+        pipe.generate(noise[:, :warm * fpc], [prompts[0], prompts[0]], [(warm - 1) * fpc], generator=g)
     else:
-        pipe.generate(noise[:, :2 * fpc], prompts[:1], generator=g)
-    pipe.reset()
+        pipe.generate(noise[:, :warm * fpc], prompts[:1], generator=g)
+    reserved = 0
+    if hkv is not None:
+        # the bank's HBM: one allocation handed to the caching allocator, which the stored windows then come out of
+        # (growing the pool by one stored window at a time costs a driver allocation of several GB inside a switch);
+        # after the warm-up, because entering a graph capture returns cached blocks to the driver
+        window_bytes = 2 * cfg.layers * cfg.window_frames * cfg.frame_tokens * cfg.heads * cfg.head_dim * 2
+        banked = min(len(switches), int((hkv_kwargs or {}).get("hbm_max_chunks", 0)) + 1)
+        free_bytes, _ = torch.cuda.mem_get_info(dev)
+        reserved = min(banked * window_bytes, max(0, free_bytes - (32 << 30)))
+        if reserved > 0:
+            del_me = torch.empty(reserved, dtype=torch.uint8, device=dev)
+            del del_me
+    pipe.reset(keep_buffers=True)
     pipe.stats = _Stats()
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
@@ -545,7 +572,9 @@ def time_generation(cfg: DiTConfig, *, chunks: int, switch_every_chunks: int = 0
         "switch_ms": [round(v, 3) for v in st.switch_ms if v > 0.05],
         "switch_store_retrieve_apply_ms": st.switch_parts_ms,
         "finite": bool(torch.isfinite(out.float()).all()),
-        "cuda_graph": {"asked": bool(cuda_graph), "replayed_chunks": st.graph_replays, "error": st.graph_error},
+        "cuda_graph": {"asked": bool(cuda_graph), "replayed_chunks": st.graph_replays, "error": st.graph_error,
+                       "captured": "in the untimed warm-up (once per process)"},
+        "warmup_chunks": warm, "bank_hbm_reserved_gb": round(reserved / 2 ** 30, 1),
         "window_frames": cfg.window_frames, "hsa_block": cfg.hsa_block,
         "hsa_topk": "cumulative-mass" if cfg.hsa_topk is None else list(cfg.hsa_topk),
     }
