@@ -197,3 +197,44 @@ def test_install_plan_matches_the_oracle_plan():
         assert [(int(r["chunk"]), int(r["src"]), int(r["src"] + r["count"])) for r in rows] == installed
         assert [(int(r["frame_from"]), int(r["frame_to"])) for r in rows] == moves
         assert [int(r["dst"]) for r in rows] == list(np.cumsum([0] + [e - s for _, s, e in installed])[:-1])
+
+
+def test_chunk_loop_window_bookkeeping_on_the_host():
+    """The chunk loop's cache plan (causal_model.py:331-343, 395-399) as properties: rows are written at the tail, the
+    window never overflows, a chunk that runs again rewrites the same rows, and once the window is full every chunk
+    evicts exactly one chunk; `reset(keep_buffers=True)` clears the caches without moving them."""
+    from worldattention_b200.causal_dit import CausalDiT, ChunkPipeline, DiTConfig
+    cfg = DiTConfig(dim=256, heads=2, ffn_dim=512, layers=2, latent_hw=(16, 32), text_dim=64, text_len=16, window_frames=7,
+                    hsa_block=64, denoising_steps=(1000, 500))
+    torch.manual_seed(0)
+    pipe = ChunkPipeline(CausalDiT(cfg), device="cpu", dtype=torch.float32)
+    s, size = cfg.frames_per_chunk * cfg.frame_tokens, cfg.window_frames * cfg.frame_tokens
+    seen_roll = 0
+    for chunk in range(6):
+        frame = chunk * cfg.frames_per_chunk
+        plan = pipe._plan(frame)
+        assert 0 <= plan["write"] and plan["write"] + s <= size                 # the chunk's rows fit behind what is kept
+        assert plan["local_end"] == plan["write"] + s and plan["local_end"] <= size
+        assert plan["global_end"] == (frame + cfg.frames_per_chunk) * cfg.frame_tokens
+        if plan["roll"]:
+            seen_roll += 1
+            assert plan["keep"] + plan["evict"] == pipe.local_end and plan["keep"] == plan["write"]
+            assert plan["local_end"] == size                                    # a rolled window is exactly full
+        else:
+            assert plan["write"] == pipe.local_end                              # appended right behind the valid rows
+        again = pipe._plan(frame)                                               # planning is pure
+        assert again == plan
+        pipe._commit(plan)
+        # the later forwards of the same chunk (and its clean-context forward) see the committed state: same rows again
+        repeat = pipe._plan(frame)
+        assert not repeat["roll"] and repeat["write"] == plan["write"] and repeat["local_end"] == plan["local_end"]
+        assert int(pipe.kv_cache[0]["local_end_index"]) == pipe.local_end
+        assert int(pipe.kv_cache[1]["global_end_index"]) == pipe.global_end
+    assert seen_roll == 4 and pipe.local_end == size      # 7-frame window, 3-frame chunks: two chunks fit, the third rolls
+    addresses = [t.data_ptr() for c in pipe.kv_cache for t in c.values()]
+    pipe.kv_cache[0]["k"].fill_(1.0)
+    pipe.reset(keep_buffers=True)
+    assert [t.data_ptr() for c in pipe.kv_cache for t in c.values()] == addresses
+    assert pipe.local_end == 0 and pipe.global_end == 0 and not pipe.kv_cache[0]["k"].any()
+    pipe.reset()
+    assert pipe._plan(0)["write"] == 0
