@@ -1083,7 +1083,15 @@ def main():
     # of the resident cache and compressed into the tail of the compressed cache, the layer runs, and the output returns
     # to page-locked host memory.
     new = q_len
-    out_h = torch.empty(tuple(forward().shape), dtype=torch.bfloat16, pin_memory=True)
+    out_shape = tuple(forward().shape)
+    out_rows = slice(0, out_shape[1])
+    if mode == "kv":
+        # every rank ends up with the whole output; the rows a rank merged are the ones it hands back, so that the output
+        # reaches the host once (the head split returns each rank's heads in the same way)
+        first_row, n_rows = work.sharded.exchange_rows(q_len, world)[1][rank]
+        out_rows = slice(first_row, first_row + n_rows)
+        out_shape = (out_shape[0], n_rows) + out_shape[2:]
+    out_h = torch.empty(out_shape, dtype=torch.bfloat16, pin_memory=True)
     q_new_h, k_new_h, v_new_h = q_h, k_h[:, kv_len - new:].contiguous().pin_memory(), v_h[:, kv_len - new:].contiguous().pin_memory()
     h2d = (q_new_h.numel() + (k_new_h.numel() + v_new_h.numel() if mode != "kv" else 0)) * 2
     d2h = out_h.numel() * 2
@@ -1100,6 +1108,9 @@ def main():
     # rows cross PCIe while group g computes and group g-1's output returns (the copies are most of the step).
     E2E_GROUPS = int(os.environ.get("WA_E2E_GROUPS", "3")) if mode == "single" else 1
     e2e_note = "one stream: copy in, compress the new segments (one fused launch), layer, copy out"
+    if mode == "kv":
+        e2e_note = ("one stream per rank: q copied in on every rank (the shards' K/V rows are resident), the sharded layer, each "
+                    "rank copies out the rows it merged; bytes are rank 0's")
     if E2E_GROUPS > 1:
         hg = HEADS // E2E_GROUPS
         e2e_note = (f"{E2E_GROUPS} head groups of {hg} heads, each with its own resident cache tensors and stream: copy in, "
@@ -1157,7 +1168,7 @@ def main():
             with torch.no_grad():
                 append_chunk(k, v, kc, vc, k_new_h, v_new_h)
         out = forward()
-        out_h.copy_(out, non_blocking=True)
+        out_h.copy_(out[:, out_rows], non_blocking=True)
 
     e2e_ms, _ = timed_steps(e2e_step, args.steps, 2, flush_l2)
     e2e_same = None
