@@ -238,3 +238,24 @@ def test_chunk_loop_window_bookkeeping_on_the_host():
     assert pipe.local_end == 0 and pipe.global_end == 0 and not pipe.kv_cache[0]["k"].any()
     pipe.reset()
     assert pipe._plan(0)["write"] == 0
+
+
+def test_peer_store_addressing_delivers_what_the_all_to_all_delivers():
+    """The address rule of the peer-store exchange (`wa_hsa_params.peer_rows / peer_self / peer_delta`), restated on the
+    host: storing query row t of rank s as row `s * rows + t % rows` of rank `t // rows`'s buffer fills every receive
+    buffer exactly as `all_to_all_single` of the ranks' records does, ragged last slice included."""
+    from worldattention_b200 import sharded
+    rng = np.random.default_rng(5)
+    for q_len, world in ((333, 3), (10, 4), (4680, 8), (5, 8)):
+        rows, plan = sharded.exchange_rows(q_len, world)
+        assert rows * world >= q_len and sum(c for _, c in plan) == q_len
+        assert all(first == r * rows for r, (first, _) in enumerate(plan))
+        sent = rng.integers(1, 1 << 30, size=(world, rows * world))            # one word per record; rows >= q_len are padding
+        sent[:, q_len:] = 0
+        # the collective: rank r's slice j lands in slot r of rank j
+        want = np.stack([np.concatenate([sent[r, j * rows:(j + 1) * rows] for r in range(world)]) for j in range(world)])
+        got = np.zeros_like(want)
+        for s in range(world):
+            for t in range(q_len):
+                got[min(t // rows, 7), s * rows + t % rows] = sent[s, t]
+        assert np.array_equal(got, want)
