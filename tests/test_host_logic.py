@@ -3,6 +3,7 @@ import math
 import shutil
 import tempfile
 
+import numpy as np
 import pytest
 import torch
 
