@@ -1106,7 +1106,8 @@ def main():
 
     # One GPU: the heads are independent, so the step is pipelined over head groups on separate streams -- group g+1's
     # rows cross PCIe while group g computes and group g-1's output returns (the copies are most of the step).
-    E2E_GROUPS = int(os.environ.get("WA_E2E_GROUPS", "3")) if mode == "single" else 1
+    # (four groups of three heads measured 1.16 ms on a box where three groups took 1.22-1.25 and six 1.23)
+    E2E_GROUPS = int(os.environ.get("WA_E2E_GROUPS", "4")) if mode == "single" else 1
     e2e_note = "one stream: copy in, compress the new segments (one fused launch), layer, copy out"
     if mode == "kv":
         e2e_note = ("one stream per rank: q copied in on every rank (the shards' K/V rows are resident), the sharded layer, each "
