@@ -1108,6 +1108,9 @@ def main():
     # rows cross PCIe while group g computes and group g-1's output returns (the copies are most of the step).
     # (four groups of three heads measured 1.16 ms on a box where three groups took 1.22-1.25 and six 1.23)
     E2E_GROUPS = int(os.environ.get("WA_E2E_GROUPS", "4")) if mode == "single" else 1
+    # outputs leave as soon as they exist (0: only after the last group's rows have arrived; with four groups that
+    # measured 1.12-1.14 ms against 1.10-1.12 ms, pairwise on one box)
+    E2E_EARLY_OUT = os.environ.get("WA_E2E_EARLY_OUT", "1") == "1"
     e2e_note = "one stream: copy in, compress the new segments (one fused launch), layer, copy out"
     if mode == "kv":
         e2e_note = ("one stream per rank: q copied in on every rank (the shards' K/V rows are resident), the sharded layer, each "
@@ -1150,12 +1153,12 @@ def main():
                                            block_size=block, proj_segment_len=FRAME_TOKENS, topk_per_head=d["topk"],
                                            force_generic=args.force_generic)
                 d["out"] = out
-        # outputs leave after the last group's rows have arrived (sending each group's output as soon as it is computed
-        # measured the same: 1.09-1.12 ms either way; large copies in both directions do overlap on this link)
+        # the copies out: large copies in both directions overlap on this link
         for g, st in enumerate(streams):
             d = grp[g]
             with torch.cuda.stream(st):
-                st.wait_event(arrived[E2E_GROUPS - 1])
+                if not E2E_EARLY_OUT:
+                    st.wait_event(arrived[E2E_GROUPS - 1])
                 d["out_h"].copy_(d["out"], non_blocking=True)
                 done[g].record(st)
         for ev in done:
