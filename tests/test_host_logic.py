@@ -260,3 +260,11 @@ def test_peer_store_addressing_delivers_what_the_all_to_all_delivers():
             for t in range(q_len):
                 got[min(t // rows, 7), s * rows + t % rows] = sent[s, t]
         assert np.array_equal(got, want)
+
+
+def test_sharded_forward_rejects_unknown_options_before_touching_tensors():
+    hsa = wa.hsa.HSAAttention(2, 128, block_size=64, proj_segment_len=128)
+    q = torch.zeros(1, 64, 2, 128)
+    for bad in (dict(exchange="ring"), dict(routing="everything"), dict(routing="candidates")):   # the last: no fixed top-k given
+        with pytest.raises(ValueError):
+            sharded.hsa_attention_kv_sharded(hsa, q, q, q, q, q, kv_len=64, shards=[(0, 64)], **bad)

@@ -381,6 +381,10 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     the rank that merges its row (`PeerExchange`: CUDA IPC, plain stores over NVLink during the kernel), and a one-element
     all-reduce behind the kernel tells every rank that its rows have arrived.  `exchange="nccl"` keeps the all-to-all.
     """
+    if exchange not in ("auto", "nccl", "peer"):
+        raise ValueError("exchange must be 'auto', 'nccl' or 'peer'")
+    if routing not in ("auto", "gather", "candidates") or (routing == "candidates" and topk_per_head is None):
+        raise ValueError("routing must be 'auto', 'gather' or (with a fixed top-k) 'candidates'")
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     bs = hsa_module.block_size
@@ -395,8 +399,6 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     blocks_total = sum(blocks_per_rank)
     block_lo = sum(blocks_per_rank[:rank])
     by_candidates = topk_per_head is not None and (routing == "candidates" or (routing == "auto" and blocks_total >= 4096))
-    if routing not in ("auto", "gather", "candidates") or (routing == "candidates" and topk_per_head is None):
-        raise ValueError("routing must be 'auto', 'gather' or (with a fixed top-k) 'candidates'")
     if by_candidates:
         if topk_max is None:
             topk_max = int(topk_per_head.max().item())       # a host read: pass topk_max to avoid it
@@ -414,8 +416,6 @@ def hsa_attention_kv_sharded(hsa_module, q, k_local, v_local, kc_local, vc_local
     records = None
     recv = None
     o_s = l_s = o_l = l_l = None
-    if exchange not in ("auto", "nccl", "peer"):
-        raise ValueError("exchange must be 'auto', 'nccl' or 'peer'")
     if world > 1 and bsz == 1:
         rp, row_plan = exchange_rows(q_len, world)
         # every rank takes the same decision from what every rank knows: the shard plan and the shapes
